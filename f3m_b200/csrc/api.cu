@@ -1,0 +1,411 @@
+// extern "C" entry points of libf3m.so and the level loop of the treecode.
+//
+// The loop below is the control flow of FFM_XY<float,d> (F3M_src/n_tree.cu:1056-1125) and
+// far_field_run (n_tree.cu:982-1053), split into a part that does not depend on b (plan) and a part
+// that does (apply).
+#include <stdarg.h>
+#include <math.h>
+#include <algorithm>
+#include <mutex>
+#include "common.cuh"
+
+namespace f3m {
+
+long long g_launches = 0;
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+void ensure_pool_configured() {
+    static std::mutex mu;
+    static bool done[64] = {false};
+    int dev = 0;
+    F3M_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev < 64 && done[dev]) return;
+    cudaMemPool_t pool;
+    F3M_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+    uint64_t thr = UINT64_MAX;   // keep freed blocks in the pool
+    F3M_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thr));
+    if (dev < 64) done[dev] = true;
+}
+
+}  // namespace f3m
+
+using namespace f3m;
+
+f3m_plan::~f3m_plan() {
+    last.resolve();
+    if (h_pinned) cudaFreeHost(h_pinned);
+    if (d_flags) cudaFree(d_flags);
+}
+
+template <typename F>
+static int guarded(F &&f) {
+    try {
+        g_err[0] = 0;
+        f();
+        return F3M_OK;
+    } catch (const Fail &e) {
+        return e.code;
+    } catch (const std::exception &e) {
+        set_error("%s", e.what());
+        return F3M_ERR_INTERNAL;
+    }
+}
+
+static void check_common(const void *X, int64_t N, const void *Y, int64_t M, int d, const f3m_params *prm) {
+    F3M_REQUIRE(X && Y && prm, F3M_ERR_ARG, "null pointer argument");
+    F3M_REQUIRE(N > 0 && M > 0, F3M_ERR_ARG, "empty point set (N=%lld, M=%lld)", (long long)N, (long long)M);
+    F3M_REQUIRE(d >= 1 && d <= F3M_MAX_DIM, F3M_ERR_ARG, "dimension %d outside 1..%d", d, F3M_MAX_DIM);
+    F3M_REQUIRE(prm->ls > 0.f, F3M_ERR_ARG, "lengthscale must be positive");
+    F3M_REQUIRE(prm->nr_interpolation >= 1, F3M_ERR_ARG, "nr_interpolation must be >= 1");
+    F3M_REQUIRE(X != Y || N == M, F3M_ERR_ARG, "X and Y share a pointer but N != M");
+}
+
+static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, int64_t M, int d, const f3m_params *prm,
+                       cudaStream_t s) {
+    ensure_pool_configured();
+    F3M_CUDA(cudaGetDevice(&pl->device));
+    pl->d = d;
+    pl->prm = *prm;
+    pl->same = (X == Y);                                  // n_tree.cu:1072
+    pl->lcs = 1 / (2 * prm->ls * prm->ls);                // n_tree.cu:1060
+    F3M_CUDA(cudaHostAlloc((void **)&pl->h_pinned, 64 * sizeof(int), cudaHostAllocDefault));
+    F3M_CUDA(cudaMalloc((void **)&pl->d_flags, 64 * sizeof(int)));
+    F3M_CUDA(cudaMemsetAsync(pl->d_flags, 0, 64 * sizeof(int), s));
+    pl->last.begin(ST_BUILD, s);
+
+    // bounding cube: calculate_edge_X / calculate_edge (n_tree.cu:25-46), float32 throughout
+    float xmin[MAXD], xmax[MAXD], ymin[MAXD], ymax[MAXD];
+    bounding_box(X, N, d, xmin, xmax, pl, s);
+    float range = 0.f;
+    for (int k = 0; k < d; k++) range = std::max(range, xmax[k] - xmin[k]);
+    if (!pl->same) {
+        bounding_box(Y, M, d, ymin, ymax, pl, s);
+        float ry = 0.f;
+        for (int k = 0; k < d; k++) ry = std::max(ry, ymax[k] - ymin[k]);
+        range = std::max(range, ry);
+    }
+    float edge0 = range * 1.01f;
+    F3M_REQUIRE(edge0 > 0.f && std::isfinite(edge0), F3M_ERR_ARG, "degenerate or non-finite bounding cube (edge %g)", edge0);
+
+    build_sorted_tree(pl->tx, X, N, d, xmin, edge0, prm->math_mode, pl, s);
+    build_root(pl->tx, s);
+    if (pl->same) pl->ty = &pl->tx;
+    else {
+        build_sorted_tree(pl->ty_store, Y, M, d, ymin, edge0, prm->math_mode, pl, s);
+        build_root(pl->ty_store, s);
+        pl->ty = &pl->ty_store;
+    }
+    Tree &tx = pl->tx, &ty = *pl->ty;
+
+    // root pair list (n_tree.cu:1071)
+    pl->lists.clear();
+    pl->lists.emplace_back();
+    {
+        PairCSR &k = pl->lists[0].keep;
+        k.ptr.alloc(2, s); k.idx.alloc(1, s);
+        int h[2] = {0, 1};
+        F3M_CUDA(cudaMemcpyAsync(k.ptr.p, h, sizeof(h), cudaMemcpyHostToDevice, s));
+        F3M_CUDA(cudaMemsetAsync(k.idx.p, 0, 4, s));
+        F3M_CUDA(cudaStreamSynchronize(s));
+        k.count = 1;
+    }
+    pl->stats = f3m_plan_stats{};
+    int level = 0;
+    auto go_on = [&]() {
+        if (pl->lists[level].keep.count == 0) return false;
+        bool gx = (float)tx.levels[level].max_count > prm->min_points;     // n_tree.cu:1075
+        if (pl->same) return gx;
+        return gx && (float)ty.levels[level].max_count > prm->min_points;  // n_tree.cu:1099
+    };
+    const int p_full = nodes_per_dim(d, prm->nr_interpolation);
+    int p_small = nodes_per_dim(d, std::min((int)lround(pow(3.0, d)), prm->nr_interpolation));
+    while (go_on()) {
+        build_next_level(tx, pl, s);
+        if (!pl->same) build_next_level(ty, pl, s);
+        level++;
+        pl->lists.emplace_back();
+        build_level_lists(pl, level, s);
+        LevelLists &ll = pl->lists[level];
+        // nodes for this level: get_interpolation_rule (n_tree.cu:971-978, 1022-1028)
+        ll.p = p_full;
+        if (prm->var_compression) {
+            float e = tx.levels[level].edge;
+            float eff = e * e * pl->lcs;
+            if (eff < 0.01f) ll.p = p_small;
+        }
+        int P = 1;
+        for (int k = 0; k < d; k++) P *= ll.p;
+        pl->stats.far_box_pairs += ll.far.count;
+        pl->stats.node_pairs += ll.far.count * (int64_t)P * P;
+        pl->stats.near_box_pairs += ll.small.count;
+        accumulate_pair_work(pl, level, ll.small, &pl->stats.direct_pairs, s);
+    }
+    pl->levels = level;
+    if (level > 0) {
+        pl->stats.near_box_pairs += pl->lists[level].keep.count;
+        accumulate_pair_work(pl, level, pl->lists[level].keep, &pl->stats.direct_pairs, s);
+    } else {
+        // no level was built: the root pair is summed directly
+        pl->stats.near_box_pairs = 1;
+        pl->stats.direct_pairs = N * M;
+    }
+    pl->stats.levels = level;
+    pl->stats.shared_tree = pl->same;
+    pl->stats.edge0 = edge0;
+    pl->last.end(s);
+    F3M_CUDA(cudaStreamSynchronize(s));
+    pl->last.ms[ST_BUILD] = 0.f;
+    pl->last.resolve();
+    pl->stats.build_ms = pl->last.ms[ST_BUILD];
+}
+
+static void plan_apply(f3m_plan *pl, const float *b, int R, float *out, int64_t row_begin, int64_t row_end,
+                       cudaStream_t s) {
+    F3M_REQUIRE(b && out && R >= 1, F3M_ERR_ARG, "bad right-hand side (R=%d)", R);
+    int dev;
+    F3M_CUDA(cudaGetDevice(&dev));
+    F3M_REQUIRE(dev == pl->device, F3M_ERR_ARG, "plan was built on device %d, current device is %d", pl->device, dev);
+    Tree &tx = pl->tx, &ty = *pl->ty;
+    const int64_t N = tx.n, M = ty.n;
+    row_begin = std::max<int64_t>(0, row_begin);
+    row_end = std::min<int64_t>(N, row_end);
+    for (float &m : pl->last.ms) m = 0.f;
+    pl->last.ms[ST_BUILD] = pl->stats.build_ms;
+    pl->last.direct_launches = 0;
+    pl->last.begin(ST_TOTAL, s);
+
+    pl->last.begin(ST_PERMUTE, s);
+    DevBuf<float> bs, outs, packed1;
+    bs.alloc((size_t)M * R, s);
+    gather_rows(b, ty.perm.p, bs.p, M, R, s);
+    outs.alloc((size_t)N * R, s);
+    outs.zero();
+    if (R == 1) build_packed_sources(pl, bs.p, packed1, s);
+    pl->last.end(s);
+
+    const int L = pl->levels;
+    if (L == 0) {
+        // largest box already small enough: one direct product over the root pair
+        direct_sums(pl, 0, pl->lists[0].keep, packed1.p, bs.p, R, outs.p, row_begin, row_end, s);
+    }
+    for (int level = 1; level <= L; level++) {
+        LevelLists &ll = pl->lists[level];
+        direct_sums(pl, level, ll.small, packed1.p, bs.p, R, outs.p, row_begin, row_end, s);   // n_tree.cu:1018-1020
+        far_field_level(pl, level, bs.p, R, outs.p, row_begin, row_end, s);                    // n_tree.cu:1021-1051
+    }
+    if (L > 0) direct_sums(pl, L, pl->lists[L].keep, packed1.p, bs.p, R, outs.p, row_begin, row_end, s);   // n_tree.cu:1092-1094
+
+    pl->last.begin(ST_UNPERMUTE, s);
+    scatter_rows(outs.p, tx.perm.p, out, N, R, s);
+    pl->last.end(s);
+    F3M_CUDA(cudaEventRecord(pl->last.spans[0].b, s));   // closes the ST_TOTAL span opened first
+    F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, pl->d_flags, sizeof(int), cudaMemcpyDeviceToHost, s));
+    F3M_CUDA(cudaStreamSynchronize(s));
+    pl->last.resolve();
+    F3M_REQUIRE(pl->h_pinned[0] == 0, F3M_ERR_INTERNAL, "device-side consistency check failed (code %d)", pl->h_pinned[0]);
+}
+
+extern "C" {
+
+int f3m_version(void) { return 100; }
+
+const char *f3m_status_string(int st) {
+    switch (st) {
+        case F3M_OK: return "ok";
+        case F3M_ERR_ARG: return "invalid argument";
+        case F3M_ERR_CUDA: return "CUDA error";
+        case F3M_ERR_DEPTH: return "tree deeper than a 30-bit cell index";
+        case F3M_ERR_OVERFLOW: return "list or offset exceeds 31 bits";
+        case F3M_ERR_UNSUPPORTED: return "unsupported configuration";
+        case F3M_ERR_INTERNAL: return "internal consistency check failed";
+        case F3M_ERR_TOO_LARGE: return "problem exceeds the fixed capacity of this entry point";
+        default: return "unknown status";
+    }
+}
+
+const char *f3m_last_error(void) { return g_err; }
+long long f3m_launch_count(void) { return g_launches; }
+
+int f3m_plan_create(f3m_plan **plan, const float *X, int64_t N, const float *Y, int64_t M, int32_t d,
+                    const f3m_params *prm, void *stream) {
+    if (!plan) return F3M_ERR_ARG;
+    *plan = nullptr;
+    f3m_plan *pl = nullptr;
+    int st = guarded([&] {
+        check_common(X, N, Y, M, d, prm);
+        pl = new f3m_plan();
+        plan_build(pl, X, N, Y, M, d, prm, (cudaStream_t)stream);
+    });
+    if (st != F3M_OK) {
+        if (pl) { cudaStreamSynchronize((cudaStream_t)stream); delete pl; }
+        return st;
+    }
+    *plan = pl;
+    return F3M_OK;
+}
+
+int f3m_plan_apply_range(f3m_plan *plan, const float *b, int32_t R, float *out, int64_t row_begin, int64_t row_end,
+                         void *stream) {
+    if (!plan) return F3M_ERR_ARG;
+    int st = guarded([&] { plan_apply(plan, b, R, out, row_begin, row_end, (cudaStream_t)stream); });
+    if (st != F3M_OK) { cudaStreamSynchronize((cudaStream_t)stream); plan->last.resolve(); }
+    return st;
+}
+
+int f3m_plan_apply(f3m_plan *plan, const float *b, int32_t R, float *out, void *stream) {
+    if (!plan) return F3M_ERR_ARG;
+    return f3m_plan_apply_range(plan, b, R, out, 0, plan->tx.n, stream);
+}
+
+int f3m_plan_destroy(f3m_plan *plan) {
+    if (!plan) return F3M_OK;
+    cudaDeviceSynchronize();
+    delete plan;
+    return F3M_OK;
+}
+
+int f3m_kmvm_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R, int32_t d,
+                 const f3m_params *prm, float *out, void *stream) {
+    f3m_plan *pl = nullptr;
+    int st = f3m_plan_create(&pl, X, N, Y, M, d, prm, stream);
+    if (st != F3M_OK) return st;
+    st = f3m_plan_apply(pl, b, R, out, stream);
+    f3m_plan_destroy(pl);
+    return st;
+}
+
+int f3m_kmvm_host_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R, int32_t d,
+                      const f3m_params *prm, float *out) {
+    int st = guarded([&] {
+        check_common(X, N, Y, M, d, prm);
+        F3M_REQUIRE(b && out && R >= 1, F3M_ERR_ARG, "bad right-hand side");
+        ensure_pool_configured();
+        cudaStream_t s = nullptr;
+        const bool same = (X == Y);
+        DevBuf<float> dX, dY, db, dout;
+        dX.alloc((size_t)N * d, s);
+        F3M_CUDA(cudaMemcpyAsync(dX.p, X, (size_t)N * d * sizeof(float), cudaMemcpyHostToDevice, s));
+        if (!same) {
+            dY.alloc((size_t)M * d, s);
+            F3M_CUDA(cudaMemcpyAsync(dY.p, Y, (size_t)M * d * sizeof(float), cudaMemcpyHostToDevice, s));
+        }
+        db.alloc((size_t)M * R, s);
+        F3M_CUDA(cudaMemcpyAsync(db.p, b, (size_t)M * R * sizeof(float), cudaMemcpyHostToDevice, s));
+        dout.alloc((size_t)N * R, s);
+        int st2 = f3m_kmvm_f32(dX.p, N, same ? dX.p : dY.p, M, db.p, R, d, prm, dout.p, s);
+        if (st2 != F3M_OK) throw Fail{st2};
+        F3M_CUDA(cudaMemcpyAsync(out, dout.p, (size_t)N * R * sizeof(float), cudaMemcpyDeviceToHost, s));
+        F3M_CUDA(cudaStreamSynchronize(s));
+    });
+    return st;
+}
+
+int f3m_plan_get_stats(const f3m_plan *plan, f3m_plan_stats *stats) {
+    if (!plan || !stats) return F3M_ERR_ARG;
+    *stats = plan->stats;
+    return F3M_OK;
+}
+
+int f3m_plan_get_level(const f3m_plan *plan, int32_t level, f3m_level_info *info) {
+    if (!plan || !info || level < 1 || level > plan->levels) return F3M_ERR_ARG;
+    const Level &lx = plan->tx.levels[level], &ly = plan->ty->levels[level];
+    const LevelLists &ll = plan->lists[level];
+    info->level = level;
+    info->boxes_x = lx.nb; info->boxes_y = ly.nb;
+    info->max_count_x = lx.max_count; info->max_count_y = ly.max_count;
+    info->n_far = ll.far.count; info->n_small = ll.small.count; info->n_keep = ll.keep.count;
+    info->edge = lx.edge;
+    info->nodes_per_dim = ll.p;
+    return F3M_OK;
+}
+
+int f3m_plan_copy_array(const f3m_plan *plan, int32_t level, int32_t tree, int32_t what, void *host_dst, size_t dst_bytes) {
+    if (!plan || !host_dst) return F3M_ERR_ARG;
+    return guarded([&] {
+        const Tree &t = tree == 0 ? plan->tx : *plan->ty;
+        const void *src = nullptr;
+        size_t bytes = 0;
+        if (what == F3M_ARR_SORTED_INDEX) { src = t.perm.p; bytes = (size_t)t.n * 4; }
+        else {
+            F3M_REQUIRE(level >= 0 && level <= plan->levels, F3M_ERR_ARG, "level %d outside 0..%d", level, plan->levels);
+            const Level &L = t.levels[level];
+            const LevelLists &ll = plan->lists[level];
+            const int nbx = plan->tx.levels[level].nb;
+            switch (what) {
+                case F3M_ARR_BOX_OFFSETS: src = L.off.p; bytes = ((size_t)L.nb + 1) * 4; break;
+                case F3M_ARR_BOX_CENTERS: src = L.ctr.p; bytes = (size_t)L.nb * plan->d * 4; break;
+                case F3M_ARR_BOX_CODES: src = L.code.p; bytes = (size_t)L.nb * 4; break;
+                case F3M_ARR_FAR_PTR: src = ll.far.ptr.p; bytes = ((size_t)nbx + 1) * 4; break;
+                case F3M_ARR_FAR_IDX: src = ll.far.idx.p; bytes = (size_t)ll.far.count * 4; break;
+                case F3M_ARR_SMALL_PTR: src = ll.small.ptr.p; bytes = ((size_t)nbx + 1) * 4; break;
+                case F3M_ARR_SMALL_IDX: src = ll.small.idx.p; bytes = (size_t)ll.small.count * 4; break;
+                case F3M_ARR_KEEP_PTR: src = ll.keep.ptr.p; bytes = ((size_t)nbx + 1) * 4; break;
+                case F3M_ARR_KEEP_IDX: src = ll.keep.idx.p; bytes = (size_t)ll.keep.count * 4; break;
+                default: F3M_REQUIRE(false, F3M_ERR_ARG, "unknown array id %d", what);
+            }
+            F3M_REQUIRE(level >= 1 || what == F3M_ARR_BOX_OFFSETS || what == F3M_ARR_BOX_CENTERS || what == F3M_ARR_BOX_CODES ||
+                            what == F3M_ARR_KEEP_PTR || what == F3M_ARR_KEEP_IDX,
+                        F3M_ERR_ARG, "level 0 has no far/small lists");
+        }
+        F3M_REQUIRE(dst_bytes >= bytes, F3M_ERR_ARG, "destination holds %zu bytes, array needs %zu", dst_bytes, bytes);
+        if (bytes) F3M_CUDA(cudaMemcpy(host_dst, src, bytes, cudaMemcpyDeviceToHost));
+    });
+}
+
+int f3m_rbf_dense_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R, int32_t d, float ls,
+                      float *out, void *stream) {
+    return guarded([&] {
+        F3M_REQUIRE(X && Y && b && out && N > 0 && M > 0 && R >= 1 && d >= 1 && d <= F3M_MAX_DIM && ls > 0, F3M_ERR_ARG,
+                    "bad argument to f3m_rbf_dense_f32");
+        ensure_pool_configured();
+        dense_f32<false>(X, N, Y, M, b, R, d, ls, out, (cudaStream_t)stream);
+        F3M_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    });
+}
+
+int f3m_rbf_dense_grad_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R, int32_t d,
+                           float ls, float *out, void *stream) {
+    return guarded([&] {
+        F3M_REQUIRE(X && Y && b && out && N > 0 && M > 0 && R >= 1 && d >= 1 && d <= F3M_MAX_DIM && ls > 0, F3M_ERR_ARG,
+                    "bad argument to f3m_rbf_dense_grad_f32");
+        ensure_pool_configured();
+        dense_f32<true>(X, N, Y, M, b, R, d, ls, out, (cudaStream_t)stream);
+        F3M_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    });
+}
+
+int f3m_rbf_dense_f64(const double *X, int64_t N, const double *Y, int64_t M, const double *b, int32_t R, int32_t d,
+                      double ls, double *out, void *stream) {
+    return guarded([&] {
+        F3M_REQUIRE(X && Y && b && out && N > 0 && M > 0 && R >= 1 && d >= 1 && d <= F3M_MAX_DIM && ls > 0, F3M_ERR_ARG,
+                    "bad argument to f3m_rbf_dense_f64");
+        dense_f64(X, N, Y, M, b, R, d, ls, out, (cudaStream_t)stream);
+        F3M_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    });
+}
+
+int f3m_measure_peaks(double *gexp_per_s, double *gfma_per_s, void *stream) {
+    if (!gexp_per_s || !gfma_per_s) return F3M_ERR_ARG;
+    return guarded([&] {
+        ensure_pool_configured();
+        measure_peaks(gexp_per_s, gfma_per_s, (cudaStream_t)stream);
+    });
+}
+
+int f3m_plan_last_timings(const f3m_plan *plan, float ms[8]) {
+    if (!plan || !ms) return F3M_ERR_ARG;
+    for (int i = 0; i < 8; i++) ms[i] = plan->last.ms[i];
+    return F3M_OK;
+}
+
+int f3m_plan_last_direct_launches(const f3m_plan *plan) { return plan ? plan->last.direct_launches : 0; }
+
+}  // extern "C"

@@ -1,0 +1,198 @@
+// Internal declarations shared by the translation units of libf3m.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+#include <vector>
+#include "f3m.h"
+
+namespace f3m {
+
+constexpr int MAXD = F3M_MAX_DIM;
+constexpr int MAXP = 16;   // interpolation nodes per dimension the kernels hold
+constexpr int NUM_SMS_HINT = 148;
+
+// ---- error handling: every CUDA call is checked, the message is kept per thread --------------
+void set_error(const char *fmt, ...);
+struct Fail {
+    int code;
+};
+#define F3M_CUDA(call)                                                                           \
+    do {                                                                                         \
+        cudaError_t e__ = (call);                                                                \
+        if (e__ != cudaSuccess) {                                                                \
+            f3m::set_error("%s failed at %s:%d: %s", #call, __FILE__, __LINE__,                  \
+                           cudaGetErrorString(e__));                                             \
+            throw f3m::Fail{F3M_ERR_CUDA};                                                       \
+        }                                                                                        \
+    } while (0)
+extern long long g_launches;   // kernels launched by this library (all threads; informational)
+#define F3M_LAUNCH_CHECK()                                                                       \
+    do {                                                                                         \
+        ++f3m::g_launches;                                                                       \
+        F3M_CUDA(cudaGetLastError());                                                            \
+    } while (0)
+#define F3M_REQUIRE(cond, code, ...)                                                             \
+    do {                                                                                         \
+        if (!(cond)) {                                                                           \
+            f3m::set_error(__VA_ARGS__);                                                         \
+            throw f3m::Fail{code};                                                               \
+        }                                                                                        \
+    } while (0)
+
+// ---- stream-ordered device buffer ------------------------------------------------------------
+// Memory comes from the device's default stream-ordered pool (cudaMallocAsync); the pool keeps
+// freed blocks, so repeated products do not go back to the driver.
+void ensure_pool_configured();
+
+template <typename T>
+struct DevBuf {
+    T *p = nullptr;
+    size_t n = 0;
+    cudaStream_t s = nullptr;
+    DevBuf() = default;
+    DevBuf(const DevBuf &) = delete;
+    DevBuf &operator=(const DevBuf &) = delete;
+    DevBuf(DevBuf &&o) noexcept : p(o.p), n(o.n), s(o.s) { o.p = nullptr; o.n = 0; }
+    DevBuf &operator=(DevBuf &&o) noexcept {
+        if (this != &o) {
+            release();
+            p = o.p; n = o.n; s = o.s;
+            o.p = nullptr; o.n = 0;
+        }
+        return *this;
+    }
+    void alloc(size_t count, cudaStream_t stream) {
+        release();
+        s = stream;
+        n = count;
+        if (count == 0) count = 1;
+        F3M_CUDA(cudaMallocAsync((void **)&p, count * sizeof(T), stream));
+    }
+    void zero() { F3M_CUDA(cudaMemsetAsync(p, 0, (n ? n : 1) * sizeof(T), s)); }
+    void release() {
+        if (p) cudaFreeAsync(p, s);
+        p = nullptr;
+        n = 0;
+    }
+    ~DevBuf() { release(); }
+};
+
+// ---- tree ------------------------------------------------------------------------------------
+struct Level {
+    int nb = 0;             // occupied boxes
+    float edge = 0.f;       // box edge at this level
+    int max_count = 0;
+    DevBuf<int> off;        // (nb+1) offsets into the sorted point order
+    DevBuf<uint32_t> code;  // (nb) Morton prefix
+    DevBuf<int> parent;     // (nb) compact id of the parent box one level up
+    DevBuf<int> child_start;// (nb+1) first child (compact id one level down); filled when that level exists
+    DevBuf<float> ctr;      // (nb,d) centres
+};
+
+struct Tree {
+    int64_t n = 0;
+    int d = 0;
+    const float *data = nullptr;   // caller's rows
+    float origin[MAXD] = {0};      // per-dimension minimum
+    float edge0 = 0.f;             // cube edge
+    int lmax = 0;                  // depth of the sort key
+    DevBuf<uint32_t> keys;         // (n) sorted Morton keys at depth lmax
+    DevBuf<int> perm;              // (n) sorted position -> input row
+    DevBuf<float> pts;             // (d,n) sorted coordinates, one plane per dimension
+    std::vector<Level> levels;     // levels[0] is the root
+};
+
+struct PairCSR {
+    DevBuf<int> ptr;  // (boxes_x+1)
+    DevBuf<int> idx;  // source box per pair
+    int64_t count = 0;
+};
+
+struct LevelLists {
+    PairCSR far, small, keep;
+    int p = 0;        // nodes per dimension used for the far field of this level
+};
+
+// Device time per stage, from CUDA events recorded on the product's stream and read after its
+// final synchronisation (no extra synchronisation inside the product).
+enum Stage { ST_PERMUTE = 0, ST_DIRECT = 1, ST_P2M = 2, ST_M2L = 3, ST_L2P = 4, ST_UNPERMUTE = 5, ST_TOTAL = 6, ST_BUILD = 7 };
+struct Timings {
+    float ms[8] = {0};
+    int direct_launches = 0;
+    struct Span { int stage; cudaEvent_t a, b; };
+    std::vector<Span> spans;
+    void begin(int stage, cudaStream_t s) {
+        Span sp{stage, nullptr, nullptr};
+        F3M_CUDA(cudaEventCreate(&sp.a));
+        F3M_CUDA(cudaEventCreate(&sp.b));
+        F3M_CUDA(cudaEventRecord(sp.a, s));
+        spans.push_back(sp);
+    }
+    void end(cudaStream_t s) { F3M_CUDA(cudaEventRecord(spans.back().b, s)); }
+    void resolve() {   // call after the stream has been synchronised
+        for (auto &sp : spans) {
+            float t = 0.f;
+            if (cudaEventElapsedTime(&t, sp.a, sp.b) == cudaSuccess) ms[sp.stage] += t;
+            cudaEventDestroy(sp.a);
+            cudaEventDestroy(sp.b);
+        }
+        spans.clear();
+    }
+};
+
+}  // namespace f3m
+
+struct f3m_plan {
+    int device = 0;
+    int d = 0;
+    bool same = false;
+    f3m_params prm{};
+    float lcs = 0.f;
+    f3m::Tree tx, ty_store;
+    f3m::Tree *ty = nullptr;
+    std::vector<f3m::LevelLists> lists;   // lists[l] for level l (index 0 unused)
+    int levels = 0;
+    f3m_plan_stats stats{};
+    f3m::Timings last;
+    int *h_pinned = nullptr;              // pinned host words for count read-back
+    int *d_flags = nullptr;               // device status / counters (64 ints)
+    ~f3m_plan();
+};
+
+namespace f3m {
+
+// ---- sort.cu ---------------------------------------------------------------------------------
+void bounding_box(const float *X, int64_t n, int d, float *h_min, float *h_max, f3m_plan *pl, cudaStream_t s);
+void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *origin, float edge0,
+                       int math_mode, f3m_plan *pl, cudaStream_t s);
+void exclusive_scan_i32(const int *in, int *out, int64_t n, cudaStream_t s);  // out may alias in; writes n+1? no: n values
+void gather_rows(const float *src, const int *perm, float *dst, int64_t n, int cols, cudaStream_t s);
+void scatter_rows(const float *src, const int *perm, float *dst, int64_t n, int cols, cudaStream_t s);
+
+// ---- tree.cu ---------------------------------------------------------------------------------
+void build_root(Tree &t, cudaStream_t s);
+void build_next_level(Tree &t, f3m_plan *pl, cudaStream_t s);        // appends levels[l+1]
+void build_level_lists(f3m_plan *pl, int level, cudaStream_t s);     // uses lists[level-1].keep
+void accumulate_pair_work(f3m_plan *pl, int level, const PairCSR &csr, int64_t *h_pairs, cudaStream_t s);
+
+// ---- far.cu ----------------------------------------------------------------------------------
+int nodes_per_dim(int d, int nr_interpolation);   // get_node_list for perfect powers, floor otherwise
+void far_field_level(f3m_plan *pl, int level, const float *b_sorted, int R, float *out_sorted,
+                     int64_t row_begin, int64_t row_end, cudaStream_t s);
+
+// ---- near.cu ---------------------------------------------------------------------------------
+// packed1: rows [s*y, b] of a single-column product (shared by every list of the product), or null;
+// b_sorted (M,R) is used to pack per column block when R > 1.
+void build_packed_sources(f3m_plan *pl, const float *b_sorted, DevBuf<float> &packed1, cudaStream_t s);
+void direct_sums(f3m_plan *pl, int level, const PairCSR &csr, const float *packed1, const float *b_sorted, int R,
+                 float *out_sorted, int64_t row_begin, int64_t row_end, cudaStream_t s);
+template <bool GRAD>
+void dense_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int R, int d, float ls, float *out,
+               cudaStream_t s);
+void dense_f64(const double *X, int64_t N, const double *Y, int64_t M, const double *b, int R, int d, double ls, double *out,
+               cudaStream_t s);
+void measure_peaks(double *gexp, double *gfma, cudaStream_t s);
+
+}  // namespace f3m

@@ -1,0 +1,424 @@
+// Direct Gaussian sums: the near / small field of the treecode and the exact dense product.
+//
+// Replaces near_field_run (F3M_src/n_tree.cu:831-902) with skip_conv_1d_shared
+// (F3M_src/1_d_conv.cu:255-335) and rbf_call / rbf_call_grad (n_tree.cu:185-241) with
+// rbf_1d_reduce_shared_torch(_grad) (1_d_conv.cu:126-214).
+//
+// The reference gathers every x, y and b through the permutation on every use, runs one target per
+// thread over a block-wide tile with two barriers per tile and repeats all exponentials for every
+// column of b.  Here the points are already in box order, sources are packed as rows
+// [s*y_0 .. s*y_{d-1}, b_0 .. b_{RB-1}] padded to a multiple of four floats with
+// s = sqrt(log2(e)/(2 ls^2)), so that a source is one or two 16-byte shared-memory reads broadcast to
+// the warp and a pair costs d subtractions, d multiply-adds, one ex2 and RB multiply-adds.  This kernel
+// is bound by the SM's FP32 issue rate and its exponential (MUFU) rate, not by HBM: a source row is
+// reused by every target of the tile.
+#include "common.cuh"
+
+namespace f3m {
+
+constexpr int NT = 128;        // threads per CTA
+constexpr int ST = 512;        // source rows per shared-memory tile
+
+__host__ __device__ constexpr int row_width(int D, int RB) { return (D + RB + 3) / 4 * 4; }
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+template <int D, int RB>
+__global__ void __launch_bounds__(256) pack_sources(const float *__restrict__ pts, int64_t n, const float *__restrict__ bs,
+                                                   int R, int r0, float scale, float *packed) {
+    constexpr int W = row_width(D, RB);
+    int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    float row[W];
+#pragma unroll
+    for (int k = 0; k < D; k++) row[k] = scale * pts[(size_t)k * n + j];
+#pragma unroll
+    for (int r = 0; r < RB; r++) row[D + r] = (r0 + r < R) ? bs[(size_t)j * R + r0 + r] : 0.f;
+#pragma unroll
+    for (int c = D + RB; c < W; c++) row[c] = 0.f;
+    float4 *dst = reinterpret_cast<float4 *>(packed + (size_t)j * W);
+#pragma unroll
+    for (int c = 0; c < W / 4; c++) dst[c] = make_float4(row[4 * c], row[4 * c + 1], row[4 * c + 2], row[4 * c + 3]);
+}
+
+// inner product of one target tile with `cnt` packed source rows held in shared memory
+template <int D, int RB, int TI, bool GRAD>
+__device__ __forceinline__ void tile_accumulate(const float *__restrict__ smem, int cnt, const float (&tx)[TI][D],
+                                                float (&acc)[TI][RB]) {
+    constexpr int W = row_width(D, RB);
+#pragma unroll 4
+    for (int j = 0; j < cnt; j++) {
+        float row[W];
+        const float4 *src = reinterpret_cast<const float4 *>(smem + j * W);
+#pragma unroll
+        for (int c = 0; c < W / 4; c++) {
+            float4 v = src[c];
+            row[4 * c] = v.x; row[4 * c + 1] = v.y; row[4 * c + 2] = v.z; row[4 * c + 3] = v.w;
+        }
+#pragma unroll
+        for (int u = 0; u < TI; u++) {
+            float d0 = tx[u][0] - row[0];
+            float r2 = d0 * d0;
+#pragma unroll
+            for (int k = 1; k < D; k++) {
+                float dk = tx[u][k] - row[k];
+                r2 = fmaf(dk, dk, r2);
+            }
+            float e = ex2_approx(-r2);
+            if (GRAD) e *= r2;
+#pragma unroll
+            for (int r = 0; r < RB; r++) acc[u][r] = fmaf(e, row[D + r], acc[u][r]);
+        }
+    }
+}
+
+// items: (target box, tile) ; tile_off[b] = first item of box b (exclusive scan of tiles per box)
+template <int D, int RB, int TI>
+__global__ void __launch_bounds__(NT) near_kernel(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
+                                                 int nbx, const int *__restrict__ tile_off,
+                                                 const int *__restrict__ ptr, const int *__restrict__ idx,
+                                                 const int *__restrict__ off_y, const float *__restrict__ packed,
+                                                 float scale, int R, int r0, float *out) {
+    constexpr int W = row_width(D, RB);
+    __shared__ __align__(16) float smem[ST * W];
+    // item -> box: largest b with tile_off[b] <= item
+    const int item = blockIdx.x;
+    int lo = 0, hi = nbx;
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (tile_off[mid] <= item) lo = mid; else hi = mid;
+    }
+    const int box = lo;
+    const int tile = item - tile_off[box], ntiles = tile_off[box + 1] - tile_off[box];
+    const int a = off_x[box], nb = off_x[box + 1] - a;
+    const int t0 = a + (int)(((long long)nb * tile) / ntiles), t1 = a + (int)(((long long)nb * (tile + 1)) / ntiles);
+    float tx[TI][D], tot[TI][RB];
+    int ti[TI];
+#pragma unroll
+    for (int u = 0; u < TI; u++) {
+        ti[u] = t0 + threadIdx.x + u * NT;
+        int ii = ti[u] < t1 ? ti[u] : t0;
+#pragma unroll
+        for (int k = 0; k < D; k++) tx[u][k] = scale * xpts[(size_t)k * n_x + ii];
+#pragma unroll
+        for (int r = 0; r < RB; r++) tot[u][r] = 0.f;
+    }
+    const int e0 = ptr[box], e1 = ptr[box + 1];
+    for (int e = e0; e < e1; e++) {
+        const int by = idx[e];
+        const int s0 = off_y[by], s1 = off_y[by + 1];
+        float acc[TI][RB];
+#pragma unroll
+        for (int u = 0; u < TI; u++)
+#pragma unroll
+            for (int r = 0; r < RB; r++) acc[u][r] = 0.f;
+        for (int base = s0; base < s1; base += ST) {
+            const int cnt = min(ST, s1 - base);
+            __syncthreads();
+            const float4 *g = reinterpret_cast<const float4 *>(packed + (size_t)base * W);
+            float4 *sdst = reinterpret_cast<float4 *>(smem);
+            for (int q = threadIdx.x; q < cnt * (W / 4); q += NT) sdst[q] = __ldg(g + q);
+            __syncthreads();
+            tile_accumulate<D, RB, TI, false>(smem, cnt, tx, acc);
+        }
+#pragma unroll
+        for (int u = 0; u < TI; u++)
+#pragma unroll
+            for (int r = 0; r < RB; r++) tot[u][r] += acc[u][r];
+    }
+#pragma unroll
+    for (int u = 0; u < TI; u++)
+        if (ti[u] < t1) {
+#pragma unroll
+            for (int r = 0; r < RB; r++)
+                if (r0 + r < R) out[(size_t)ti[u] * R + r0 + r] += tot[u][r];
+        }
+}
+
+__global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__restrict__ off_x, const int *__restrict__ ptr,
+                                                         int row_begin, int row_end, int tile_pts, int *tiles) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b > nbx) return;
+    int t = 0;
+    if (b < nbx && ptr[b + 1] > ptr[b]) {
+        int o = off_x[b];
+        if (o >= row_begin && o < row_end) t = (off_x[b + 1] - o + tile_pts - 1) / tile_pts;
+    }
+    tiles[b] = t;
+}
+
+template <int D, int RB>
+static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float *packed, int R, int r0, float *out,
+                        int row_begin, int row_end, float scale, cudaStream_t s) {
+    Tree &tx = pl->tx, &ty = *pl->ty;
+    Level &lx = tx.levels[level], &ly = ty.levels[level];
+    constexpr int TI = 1;
+    DevBuf<int> tiles;
+    tiles.alloc((size_t)lx.nb + 1, s);
+    near_tiles_per_box<<<(unsigned)((lx.nb + 1 + 255) / 256), 256, 0, s>>>(lx.nb, lx.off.p, csr.ptr.p, row_begin, row_end,
+                                                                           NT * TI, tiles.p);
+    F3M_LAUNCH_CHECK();
+    exclusive_scan_i32(tiles.p, tiles.p, (int64_t)lx.nb + 1, s);
+    F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, tiles.p + lx.nb, sizeof(int), cudaMemcpyDeviceToHost, s));
+    F3M_CUDA(cudaStreamSynchronize(s));
+    const int items = pl->h_pinned[0];
+    if (items <= 0) return;
+    pl->last.begin(ST_DIRECT, s);
+    near_kernel<D, RB, TI><<<items, NT, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, csr.idx.p, ly.off.p,
+                                                packed, scale, R, r0, out);
+    pl->last.end(s);
+    pl->last.direct_launches++;
+    F3M_LAUNCH_CHECK();
+}
+
+static inline float near_scale(float lcs) { return sqrtf(lcs * 1.4426950408889634f); }
+
+template <int D>
+static void direct_d(f3m_plan *pl, int level, const PairCSR &csr, const float *bs, int R, float *out, int rb, int re,
+                     cudaStream_t s) {
+    Tree &ty = *pl->ty;
+    const float scale = near_scale(pl->lcs);
+    const unsigned g = (unsigned)((ty.n + 255) / 256);
+    for (int r0 = 0; r0 < R;) {
+        int left = R - r0;
+        DevBuf<float> packed;
+        if (left >= 5) {
+            packed.alloc((size_t)ty.n * row_width(D, 8), s);
+            pack_sources<D, 8><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
+            F3M_LAUNCH_CHECK();
+            direct_impl<D, 8>(pl, level, csr, packed.p, R, r0, out, rb, re, scale, s);
+            r0 += 8;
+        } else if (left >= 2) {
+            packed.alloc((size_t)ty.n * row_width(D, 4), s);
+            pack_sources<D, 4><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
+            F3M_LAUNCH_CHECK();
+            direct_impl<D, 4>(pl, level, csr, packed.p, R, r0, out, rb, re, scale, s);
+            r0 += 4;
+        } else {
+            packed.alloc((size_t)ty.n * row_width(D, 1), s);
+            pack_sources<D, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
+            F3M_LAUNCH_CHECK();
+            direct_impl<D, 1>(pl, level, csr, packed.p, R, r0, out, rb, re, scale, s);
+            r0 += 1;
+        }
+    }
+}
+
+// b-dependent packing is redone per call of direct_sums; the packed rows depend only on (b, column block),
+// so callers that run several lists per product pass the same packed buffer (see api.cu).
+void build_packed_sources(f3m_plan *pl, const float *b_sorted, DevBuf<float> &packed, cudaStream_t s) {
+    Tree &ty = *pl->ty;
+    const float scale = near_scale(pl->lcs);
+    const unsigned g = (unsigned)((ty.n + 255) / 256);
+    const int R = 1;
+    switch (pl->d) {
+        case 1: packed.alloc((size_t)ty.n * row_width(1, 1), s); pack_sources<1, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, b_sorted, R, 0, scale, packed.p); break;
+        case 2: packed.alloc((size_t)ty.n * row_width(2, 1), s); pack_sources<2, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, b_sorted, R, 0, scale, packed.p); break;
+        case 3: packed.alloc((size_t)ty.n * row_width(3, 1), s); pack_sources<3, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, b_sorted, R, 0, scale, packed.p); break;
+        case 4: packed.alloc((size_t)ty.n * row_width(4, 1), s); pack_sources<4, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, b_sorted, R, 0, scale, packed.p); break;
+        default: packed.alloc((size_t)ty.n * row_width(5, 1), s); pack_sources<5, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, b_sorted, R, 0, scale, packed.p); break;
+    }
+    F3M_LAUNCH_CHECK();
+}
+
+void direct_sums(f3m_plan *pl, int level, const PairCSR &csr, const float *packed, const float *bs, int R,
+                 float *out_sorted, int64_t row_begin, int64_t row_end, cudaStream_t s) {
+    if (csr.count == 0) return;
+    const int rb = (int)row_begin, re = (int)row_end;
+    const float scale = near_scale(pl->lcs);
+    if (R == 1 && packed) {   // single column: packed rows shared by every list of the product
+        switch (pl->d) {
+            case 1: direct_impl<1, 1>(pl, level, csr, packed, 1, 0, out_sorted, rb, re, scale, s); break;
+            case 2: direct_impl<2, 1>(pl, level, csr, packed, 1, 0, out_sorted, rb, re, scale, s); break;
+            case 3: direct_impl<3, 1>(pl, level, csr, packed, 1, 0, out_sorted, rb, re, scale, s); break;
+            case 4: direct_impl<4, 1>(pl, level, csr, packed, 1, 0, out_sorted, rb, re, scale, s); break;
+            default: direct_impl<5, 1>(pl, level, csr, packed, 1, 0, out_sorted, rb, re, scale, s); break;
+        }
+        return;
+    }
+    // multi-column: rows are packed per column block from the sorted b (M,R)
+    switch (pl->d) {
+        case 1: direct_d<1>(pl, level, csr, bs, R, out_sorted, rb, re, s); break;
+        case 2: direct_d<2>(pl, level, csr, bs, R, out_sorted, rb, re, s); break;
+        case 3: direct_d<3>(pl, level, csr, bs, R, out_sorted, rb, re, s); break;
+        case 4: direct_d<4>(pl, level, csr, bs, R, out_sorted, rb, re, s); break;
+        default: direct_d<5>(pl, level, csr, bs, R, out_sorted, rb, re, s); break;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// exact dense products
+// ---------------------------------------------------------------------------------------------
+template <int D, int RB>
+__global__ void __launch_bounds__(256) pack_rows_dense(const float *__restrict__ Y, int64_t n, const float *__restrict__ b, int R,
+                                                      int r0, float scale, float *packed) {
+    constexpr int W = row_width(D, RB);
+    int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    float *dst = packed + (size_t)j * W;
+#pragma unroll
+    for (int k = 0; k < D; k++) dst[k] = scale * Y[j * D + k];
+#pragma unroll
+    for (int r = 0; r < RB; r++) dst[D + r] = (r0 + r < R) ? b[(size_t)j * R + r0 + r] : 0.f;
+#pragma unroll
+    for (int c = D + RB; c < W; c++) dst[c] = 0.f;
+}
+
+template <int D, int RB, bool GRAD>
+__global__ void __launch_bounds__(NT) dense_kernel(const float *__restrict__ X, int64_t n, const float *__restrict__ packed,
+                                                  int64_t m, float scale, float post, int R, int r0, float *out) {
+    constexpr int W = row_width(D, RB);
+    __shared__ __align__(16) float smem[ST * W];
+    const int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x;
+    const int64_t ii = i < n ? i : n - 1;
+    float tx[1][D], tot[1][RB];
+#pragma unroll
+    for (int k = 0; k < D; k++) tx[0][k] = scale * X[ii * D + k];
+#pragma unroll
+    for (int r = 0; r < RB; r++) tot[0][r] = 0.f;
+    for (int64_t base = 0; base < m; base += ST) {
+        const int cnt = (int)min((int64_t)ST, m - base);
+        __syncthreads();
+        const float4 *g = reinterpret_cast<const float4 *>(packed + (size_t)base * W);
+        float4 *sdst = reinterpret_cast<float4 *>(smem);
+        for (int q = threadIdx.x; q < cnt * (W / 4); q += NT) sdst[q] = __ldg(g + q);
+        __syncthreads();
+        float acc[1][RB];
+#pragma unroll
+        for (int r = 0; r < RB; r++) acc[0][r] = 0.f;
+        tile_accumulate<D, RB, 1, GRAD>(smem, cnt, tx, acc);
+#pragma unroll
+        for (int r = 0; r < RB; r++) tot[0][r] += acc[0][r];
+    }
+    if (i < n)
+#pragma unroll
+        for (int r = 0; r < RB; r++)
+            if (r0 + r < R) out[(size_t)i * R + r0 + r] = tot[0][r] * post;
+}
+
+template <int D, bool GRAD>
+static void dense_d(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int R, float ls, float *out,
+                    cudaStream_t s) {
+    const float lcs = 1.f / (2.f * ls * ls);
+    const float scale = near_scale(lcs);
+    // GRAD: sum r^2 exp(..) b / ls^3 with r^2 = (scaled r^2) / scale^2   (n_tree.cu:222-239)
+    const float post = GRAD ? 1.f / (scale * scale) / (ls * ls * ls) : 1.f;
+    const unsigned gy = (unsigned)((M + 255) / 256), gx = (unsigned)((N + NT - 1) / NT);
+    for (int r0 = 0; r0 < R;) {
+        DevBuf<float> packed;
+        if (R - r0 >= 2) {
+            packed.alloc((size_t)M * row_width(D, 4), s);
+            pack_rows_dense<D, 4><<<gy, 256, 0, s>>>(Y, M, b, R, r0, scale, packed.p);
+            F3M_LAUNCH_CHECK();
+            dense_kernel<D, 4, GRAD><<<gx, NT, 0, s>>>(X, N, packed.p, M, scale, post, R, r0, out);
+            r0 += 4;
+        } else {
+            packed.alloc((size_t)M * row_width(D, 1), s);
+            pack_rows_dense<D, 1><<<gy, 256, 0, s>>>(Y, M, b, R, r0, scale, packed.p);
+            F3M_LAUNCH_CHECK();
+            dense_kernel<D, 1, GRAD><<<gx, NT, 0, s>>>(X, N, packed.p, M, scale, post, R, r0, out);
+            r0 += 1;
+        }
+        F3M_LAUNCH_CHECK();
+    }
+}
+
+template <bool GRAD>
+void dense_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int R, int d, float ls, float *out,
+               cudaStream_t s) {
+    switch (d) {
+        case 1: dense_d<1, GRAD>(X, N, Y, M, b, R, ls, out, s); break;
+        case 2: dense_d<2, GRAD>(X, N, Y, M, b, R, ls, out, s); break;
+        case 3: dense_d<3, GRAD>(X, N, Y, M, b, R, ls, out, s); break;
+        case 4: dense_d<4, GRAD>(X, N, Y, M, b, R, ls, out, s); break;
+        default: dense_d<5, GRAD>(X, N, Y, M, b, R, ls, out, s); break;
+    }
+}
+template void dense_f32<false>(const float *, int64_t, const float *, int64_t, const float *, int, int, float, float *, cudaStream_t);
+template void dense_f32<true>(const float *, int64_t, const float *, int64_t, const float *, int, int, float, float *, cudaStream_t);
+
+// float64 dense product with a double-precision exponential (accuracy reference on the device)
+__global__ void __launch_bounds__(128) dense_f64_kernel(const double *__restrict__ X, int64_t n, const double *__restrict__ Y,
+                                                       int64_t m, const double *__restrict__ b, int R, int d, double lcs,
+                                                       double *out) {
+    __shared__ double sy[128 * F3M_MAX_DIM];
+    const int64_t i = (int64_t)blockIdx.x * 128 + threadIdx.x;
+    double xi[F3M_MAX_DIM];
+    for (int k = 0; k < d; k++) xi[k] = X[(i < n ? i : n - 1) * d + k];
+    for (int r = 0; r < R; r++) {
+        double acc = 0.;
+        for (int64_t base = 0; base < m; base += 128) {
+            int cnt = (int)min((int64_t)128, m - base);
+            __syncthreads();
+            for (int q = threadIdx.x; q < cnt * d; q += 128) sy[q] = Y[base * d + q];
+            __syncthreads();
+            for (int j = 0; j < cnt; j++) {
+                double r2 = 0.;
+                for (int k = 0; k < d; k++) { double dk = xi[k] - sy[j * d + k]; r2 += dk * dk; }
+                acc += exp(-r2 * lcs) * b[(base + j) * R + r];
+            }
+        }
+        if (i < n) out[i * R + r] = acc;
+    }
+}
+
+void dense_f64(const double *X, int64_t N, const double *Y, int64_t M, const double *b, int R, int d, double ls, double *out,
+               cudaStream_t s) {
+    dense_f64_kernel<<<(unsigned)((N + 127) / 128), 128, 0, s>>>(X, N, Y, M, b, R, d, 1.0 / (2.0 * ls * ls), out);
+    F3M_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// issue-rate probes: register-only loops of ex2 and of fma
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) probe_ex2(float *out, int iters) {
+    float a = threadIdx.x * 1e-3f, b = a + 0.1f, c = a + 0.2f, d = a + 0.3f;
+    for (int i = 0; i < iters; i++) {
+        a = ex2_approx(-a); b = ex2_approx(-b); c = ex2_approx(-c); d = ex2_approx(-d);
+    }
+    if (a + b + c + d == 12345.f) out[0] = a;
+}
+__global__ void __launch_bounds__(256) probe_fma(float *out, int iters) {
+    float a = threadIdx.x * 1e-3f, b = a + 0.1f, c = a + 0.2f, d = a + 0.3f, e = a + 0.4f, f = a + 0.5f, g = a + 0.6f, h = a + 0.7f;
+    const float m = 0.999f, q = 1e-3f;
+    for (int i = 0; i < iters; i++) {
+        a = fmaf(a, m, q); b = fmaf(b, m, q); c = fmaf(c, m, q); d = fmaf(d, m, q);
+        e = fmaf(e, m, q); f = fmaf(f, m, q); g = fmaf(g, m, q); h = fmaf(h, m, q);
+    }
+    if (a + b + c + d + e + f + g + h == 12345.f) out[0] = a;
+}
+
+void measure_peaks(double *gexp, double *gfma, cudaStream_t s) {
+    DevBuf<float> o;
+    o.alloc(4, s);
+    cudaEvent_t e0, e1;
+    F3M_CUDA(cudaEventCreate(&e0));
+    F3M_CUDA(cudaEventCreate(&e1));
+    int dev, sms;
+    F3M_CUDA(cudaGetDevice(&dev));
+    F3M_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int grid = sms * 8, iters = 1 << 14;
+    float ms;
+    for (int rep = 0; rep < 2; rep++) {   // first repetition warms up
+        F3M_CUDA(cudaEventRecord(e0, s));
+        probe_ex2<<<grid, 256, 0, s>>>(o.p, iters);
+        F3M_CUDA(cudaEventRecord(e1, s));
+        F3M_CUDA(cudaEventSynchronize(e1));
+        F3M_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        *gexp = (double)grid * 256 * iters * 4 / (ms * 1e-3) * 1e-9;
+        F3M_CUDA(cudaEventRecord(e0, s));
+        probe_fma<<<grid, 256, 0, s>>>(o.p, iters);
+        F3M_CUDA(cudaEventRecord(e1, s));
+        F3M_CUDA(cudaEventSynchronize(e1));
+        F3M_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        *gfma = (double)grid * 256 * iters * 8 / (ms * 1e-3) * 1e-9;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+}
+
+}  // namespace f3m

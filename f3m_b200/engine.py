@@ -1,0 +1,202 @@
+"""Thin Python layer over the C ABI: plans, products, introspection.  torch supplies device
+memory and the current stream; all arithmetic happens in libf3m.so."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import Params, LevelInfo, PlanStats, check
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _as_f32(t: torch.Tensor) -> torch.Tensor:
+    if t.dtype != torch.float32 or not t.is_contiguous():
+        t = t.float().contiguous()
+    return t
+
+
+def make_params(ls, min_points, nr_of_interpolation, var_compression, eff_var_limit, small_field_points,
+                math_mode=_lib.MATH_FASTMATH) -> Params:
+    return Params(float(ls), float(min_points), int(nr_of_interpolation), int(bool(var_compression)),
+                  float(eff_var_limit), int(small_field_points), int(math_mode), 0)
+
+
+class Plan:
+    """Tree and interaction lists of one (X, Y) pair (f3m_plan); apply() multiplies by any b."""
+
+    def __init__(self, X: torch.Tensor, Y: Optional[torch.Tensor], params: Params):
+        if not X.is_cuda:
+            raise ValueError("Plan needs CUDA tensors: the engine has no CPU path")
+        self.X = _as_f32(X)
+        self.same = Y is None or (Y.data_ptr() == X.data_ptr() and Y.shape == X.shape)
+        self.Y = self.X if self.same else _as_f32(Y)
+        if self.Y.device != self.X.device:
+            raise ValueError("X and Y must be on the same device")
+        self.params = params
+        self.device = self.X.device
+        self.N, self.d = self.X.shape
+        self.M = self.Y.shape[0]
+        self._h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            st = _lib.lib().f3m_plan_create(C.byref(self._h), self.X.data_ptr(), self.N, self.Y.data_ptr(), self.M,
+                                            self.d, C.byref(self.params), _stream_ptr(self.device))
+        check(st, "f3m_plan_create")
+
+    def apply(self, b: torch.Tensor, row_range=None) -> torch.Tensor:
+        b = _as_f32(b.to(self.device))
+        if b.dim() == 1:
+            b = b[:, None]
+        if b.shape[0] != self.M:
+            raise AssertionError(f"b has {b.shape[0]} rows, Y has {self.M}")
+        out = torch.empty(self.N, b.shape[1], device=self.device, dtype=torch.float32)
+        with torch.cuda.device(self.device):
+            if row_range is None:
+                st = _lib.lib().f3m_plan_apply(self._h, b.data_ptr(), b.shape[1], out.data_ptr(), _stream_ptr(self.device))
+            else:
+                st = _lib.lib().f3m_plan_apply_range(self._h, b.data_ptr(), b.shape[1], out.data_ptr(), int(row_range[0]),
+                                                     int(row_range[1]), _stream_ptr(self.device))
+        check(st, "f3m_plan_apply")
+        return out
+
+    # ---- introspection ---------------------------------------------------------------------
+    def stats(self) -> Dict:
+        s = PlanStats()
+        check(_lib.lib().f3m_plan_get_stats(self._h, C.byref(s)), "f3m_plan_get_stats")
+        return {k: getattr(s, k) for k, _ in PlanStats._fields_}
+
+    def level(self, level: int) -> Dict:
+        s = LevelInfo()
+        check(_lib.lib().f3m_plan_get_level(self._h, level, C.byref(s)), "f3m_plan_get_level")
+        return {k: getattr(s, k) for k, _ in LevelInfo._fields_}
+
+    def timings(self) -> Dict:
+        ms = (C.c_float * 8)()
+        check(_lib.lib().f3m_plan_last_timings(self._h, ms), "f3m_plan_last_timings")
+        names = ["permute", "direct", "p2m", "m2l", "l2p", "unpermute", "total", "build"]
+        d = {n: float(ms[i]) for i, n in enumerate(names)}
+        d["direct_launches"] = int(_lib.lib().f3m_plan_last_direct_launches(self._h))
+        return d
+
+    def array(self, level: int, tree: int, what: int) -> np.ndarray:
+        info = self.level(level) if level >= 1 else None
+        nb = (info["boxes_x"] if tree == 0 else info["boxes_y"]) if info else 1
+        nbx = info["boxes_x"] if info else 1
+        if what == _lib.ARR_SORTED_INDEX:
+            shape, dt = ((self.N if tree == 0 else self.M),), np.int32
+        elif what == _lib.ARR_BOX_OFFSETS:
+            shape, dt = (nb + 1,), np.int32
+        elif what == _lib.ARR_BOX_CENTERS:
+            shape, dt = (nb, self.d), np.float32
+        elif what == _lib.ARR_BOX_CODES:
+            shape, dt = (nb,), np.uint32
+        elif what in (_lib.ARR_FAR_PTR, _lib.ARR_SMALL_PTR, _lib.ARR_KEEP_PTR):
+            shape, dt = (nbx + 1,), np.int32
+        else:
+            key = {_lib.ARR_FAR_IDX: "n_far", _lib.ARR_SMALL_IDX: "n_small", _lib.ARR_KEEP_IDX: "n_keep"}[what]
+            shape, dt = ((info[key] if info else 1),), np.int32
+        out = np.empty(shape, dtype=dt)
+        check(_lib.lib().f3m_plan_copy_array(self._h, level, tree, what, out.ctypes.data_as(C.c_void_p), out.nbytes),
+              "f3m_plan_copy_array")
+        return out
+
+    def pairs(self, level: int, cls: str) -> np.ndarray:
+        """(n,2) int array of (target box, source box) of one class ('far', 'small', 'keep'), sorted."""
+        pid, iid = {"far": (_lib.ARR_FAR_PTR, _lib.ARR_FAR_IDX), "small": (_lib.ARR_SMALL_PTR, _lib.ARR_SMALL_IDX),
+                    "keep": (_lib.ARR_KEEP_PTR, _lib.ARR_KEEP_IDX)}[cls]
+        ptr, idx = self.array(level, 0, pid), self.array(level, 0, iid)
+        left = np.repeat(np.arange(ptr.size - 1), np.diff(ptr))
+        return np.stack([left, idx], 1).astype(np.int64)
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            _lib.lib().f3m_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def kmvm(X, Y, b, params: Params) -> torch.Tensor:
+    """One-shot product through f3m_kmvm_f32 (tree built and dropped inside the call)."""
+    X = _as_f32(X)
+    same = Y is None or Y.data_ptr() == X.data_ptr()
+    Y = X if same else _as_f32(Y)
+    b = _as_f32(b)
+    if b.dim() == 1:
+        b = b[:, None]
+    if not (X.is_cuda and Y.is_cuda and b.is_cuda):
+        raise ValueError("kmvm needs CUDA tensors: the engine has no CPU path (use kmvm_host for host buffers)")
+    out = torch.empty(X.shape[0], b.shape[1], device=X.device, dtype=torch.float32)
+    with torch.cuda.device(X.device):
+        st = _lib.lib().f3m_kmvm_f32(X.data_ptr(), X.shape[0], Y.data_ptr(), Y.shape[0], b.data_ptr(), b.shape[1],
+                                     X.shape[1], C.byref(params), out.data_ptr(), _stream_ptr(X.device))
+    check(st, "f3m_kmvm_f32")
+    return out
+
+
+def kmvm_host(X, Y, b, params: Params, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Product with HOST tensors through f3m_kmvm_host_f32: H2D copies, product, D2H copy in one call."""
+    X = _as_f32(X)
+    same = Y is None or Y.data_ptr() == X.data_ptr()
+    Y = X if same else _as_f32(Y)
+    b = _as_f32(b)
+    if b.dim() == 1:
+        b = b[:, None]
+    if X.is_cuda or Y.is_cuda or b.is_cuda:
+        raise ValueError("kmvm_host takes CPU tensors")
+    if out is None:
+        out = torch.empty(X.shape[0], b.shape[1], dtype=torch.float32)
+    st = _lib.lib().f3m_kmvm_host_f32(X.data_ptr(), X.shape[0], Y.data_ptr(), Y.shape[0], b.data_ptr(), b.shape[1],
+                                      X.shape[1], C.byref(params), out.data_ptr())
+    check(st, "f3m_kmvm_host_f32")
+    return out
+
+
+def rbf_dense(X, Y, b, ls: float, grad: bool = False) -> torch.Tensor:
+    """Exact dense product (f3m_rbf_dense_f32 / _f64 / _grad_f32), dtype taken from X."""
+    if not X.is_cuda:
+        raise ValueError("rbf_dense needs CUDA tensors")
+    dt = X.dtype
+    if dt not in (torch.float32, torch.float64):
+        X, dt = X.float(), torch.float32
+    X, Y, b = X.contiguous(), Y.to(dt).contiguous(), b.to(dt).contiguous()
+    if b.dim() == 1:
+        b = b[:, None]
+    assert Y.shape[1] == X.shape[1] and Y.shape[0] == b.shape[0]
+    out = torch.empty(X.shape[0], b.shape[1], device=X.device, dtype=dt)
+    L = _lib.lib()
+    with torch.cuda.device(X.device):
+        if dt == torch.float64:
+            if grad:
+                raise NotImplementedError("the gradient op exists in float32 only")
+            st = L.f3m_rbf_dense_f64(X.data_ptr(), X.shape[0], Y.data_ptr(), Y.shape[0], b.data_ptr(), b.shape[1],
+                                     X.shape[1], float(ls), out.data_ptr(), _stream_ptr(X.device))
+        else:
+            fn = L.f3m_rbf_dense_grad_f32 if grad else L.f3m_rbf_dense_f32
+            st = fn(X.data_ptr(), X.shape[0], Y.data_ptr(), Y.shape[0], b.data_ptr(), b.shape[1], X.shape[1], float(ls),
+                    out.data_ptr(), _stream_ptr(X.device))
+    check(st, "f3m_rbf_dense")
+    return out
+
+
+def measure_peaks(device=None) -> Dict:
+    """Measured exponential (MUFU.EX2) and FP32 FMA issue peaks of the current GPU, in G ops/s."""
+    a, b = C.c_double(), C.c_double()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        check(_lib.lib().f3m_measure_peaks(C.byref(a), C.byref(b), _stream_ptr(dev)), "f3m_measure_peaks")
+    return {"gexp_per_s": a.value, "gfma_per_s": b.value}
+
+
+def launch_count() -> int:
+    return int(_lib.lib().f3m_launch_count())

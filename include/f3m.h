@@ -1,0 +1,167 @@
+/*
+ * f3m.h -- C ABI of libf3m.so, a B200 (sm_100a) engine for Gaussian kernel matrix-vector
+ * products  out = K(X,Y) b,  K_ij = exp(-|x_i - y_j|^2 / (2 ls^2)),  computed with the F3M
+ * treecode (2^d-tree, near/far interaction lists, Chebyshev/Lagrange interpolation).
+ *
+ * Every entry point is plain C: raw pointers, sizes, an opaque handle and an int status
+ * (0 = ok).  No exceptions cross the boundary, nothing is printed, and there is no CPU fallback:
+ * a call on a machine without a usable CUDA device returns F3M_ERR_CUDA.
+ *
+ * Unless stated otherwise, pointers are DEVICE pointers on the current CUDA device, arrays are
+ * dense row-major float32, and `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ * stream).  Work is enqueued on that stream; the call returns after the stream has been
+ * synchronised, because list sizes are read back on the host while the tree is built.
+ *
+ * Each declaration names the interface of the reference implementation (MrHuff/F3M) that it
+ * replaces, as path:line inside that repository.
+ */
+#ifndef F3M_H
+#define F3M_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define F3M_MAX_DIM 5           /* dimensions 1..5 are built (reference table: 1..10, F3M_src/pybinder_setup.cu:17-36) */
+#define F3M_MAX_LEVELS 24
+
+enum f3m_status {
+    F3M_OK = 0,
+    F3M_ERR_ARG = 1,        /* bad pointer / size / dimension */
+    F3M_ERR_CUDA = 2,       /* a CUDA runtime call or kernel launch failed; see f3m_last_error() */
+    F3M_ERR_DEPTH = 3,      /* the tree would need more levels than a 30-bit cell index holds */
+    F3M_ERR_OVERFLOW = 4,   /* a list or offset does not fit in 31 bits */
+    F3M_ERR_UNSUPPORTED = 5,/* e.g. more interpolation nodes per dimension than the kernels hold */
+    F3M_ERR_INTERNAL = 6,   /* a device-side consistency check failed */
+    F3M_ERR_TOO_LARGE = 7   /* problem larger than a fixed-capacity entry point allows */
+};
+
+/* numeric flavour of the box index and of the far test */
+#define F3M_MATH_FASTMATH 0 /* div.approx / sqrt.approx / fused multiply-add: the instructions the reference's
+                               --use_fast_math build executes (F3M_src/setup.py:16) -- default */
+#define F3M_MATH_IEEE 1     /* IEEE divide, sqrt, no contraction: what a CPU restatement computes */
+
+/* Parameters of FFM_XY<float,d> (F3M_src/n_tree.cu:1056-1059) / FFM.__init__ (experiments/FFM_classes.py:9-19). */
+typedef struct f3m_params {
+    float ls;                 /* lengthscale l;  K = exp(-r^2/(2 l^2)) */
+    float min_points;         /* refine while the largest box holds more points than this (n_tree.cu:1075,1099) */
+    int32_t nr_interpolation; /* interpolation nodes per box, p^d */
+    int32_t var_compression;  /* 0/1: extra far rules of boolean_separate_interactions_small_var_comp (1_d_conv.cu:955-1029) */
+    float eff_var_limit;
+    int32_t small_field_points;
+    int32_t math_mode;        /* F3M_MATH_FASTMATH or F3M_MATH_IEEE */
+    int32_t reserved;
+} f3m_params;
+
+typedef struct f3m_plan f3m_plan;   /* tree + interaction lists of one (X, Y) pair; reusable for many b */
+
+/* -------- library ------------------------------------------------------------------------- */
+int f3m_version(void);
+const char *f3m_status_string(int status);
+/* Message of the last failing call made by this thread ("" if none). */
+const char *f3m_last_error(void);
+
+/* -------- the hot path ------------------------------------------------------------------- */
+
+/* One complete product: replaces FFM_XY<float,d> (F3M_src/n_tree.cu:1056-1125), which
+ * ffm_3d_float.FFM_XY_FLOAT_d binds (F3M_src/pybinder_setup.cu:17-36).
+ * X (N,d), Y (M,d), b (M,R), out (N,R).  Pass Y == X (same pointer) for the shared-tree case,
+ * exactly as the reference detects it (n_tree.cu:1072).  out is overwritten. */
+int f3m_kmvm_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R,
+                 int32_t d, const f3m_params *prm, float *out, void *stream);
+
+/* Same product with HOST buffers: copies X, Y, b to the device, runs f3m_kmvm_f32 and copies the
+ * result back, all inside the call.  This is what a caller holding CPU tensors pays end to end
+ * (FFM.__init__/__matmul__ move X, Y, b to the device, experiments/FFM_classes.py:23-50). */
+int f3m_kmvm_host_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R,
+                      int32_t d, const f3m_params *prm, float *out);
+
+/* Split form: everything that does not depend on b (bounding cube, sort, box division,
+ * interaction lists -- n_tree.cu:25-180, 594-811, 903-969) is done once ...                  */
+int f3m_plan_create(f3m_plan **plan, const float *X, int64_t N, const float *Y, int64_t M, int32_t d,
+                    const f3m_params *prm, void *stream);
+/* ... and applied to any number of right-hand sides (far_field_compute_v2 n_tree.cu:489-593,
+ * near_field_run n_tree.cu:831-902).  b (M,R), out (N,R) overwritten.
+ * row_begin/row_end restrict the product to the target boxes whose sorted point range starts
+ * inside [row_begin,row_end) (a slice of the sorted target order, used to shard target boxes
+ * over GPUs); rows outside the slice are written as 0.  Use 0, N for the whole product. */
+int f3m_plan_apply(f3m_plan *plan, const float *b, int32_t R, float *out, void *stream);
+int f3m_plan_apply_range(f3m_plan *plan, const float *b, int32_t R, float *out, int64_t row_begin,
+                         int64_t row_end, void *stream);
+int f3m_plan_destroy(f3m_plan *plan);
+
+/* -------- introspection (parity checks and work accounting) ------------------------------ */
+
+typedef struct f3m_level_info {
+    int32_t level;        /* 1-based depth */
+    int32_t boxes_x;      /* occupied target boxes */
+    int32_t boxes_y;      /* occupied source boxes */
+    int32_t max_count_x, max_count_y;
+    int64_t n_far, n_small, n_keep; /* pairs per class at this level (separate_interactions n_tree.cu:701-787) */
+    float edge;           /* box edge at this level */
+    int32_t nodes_per_dim;/* p used at this level */
+} f3m_level_info;
+
+typedef struct f3m_plan_stats {
+    int32_t levels;            /* levels built */
+    int32_t shared_tree;       /* 1 if X is Y */
+    int64_t direct_pairs;      /* sum over small + final-near box pairs of n_x*n_y */
+    int64_t node_pairs;        /* sum over far box pairs of P^2 (the reference's M2L work) */
+    int64_t far_box_pairs;
+    int64_t near_box_pairs;    /* small + final near */
+    float edge0;               /* cube edge */
+    float build_ms;            /* device time of f3m_plan_create */
+} f3m_plan_stats;
+
+int f3m_plan_get_stats(const f3m_plan *plan, f3m_plan_stats *stats);
+int f3m_plan_get_level(const f3m_plan *plan, int32_t level, f3m_level_info *info);
+
+/* Copy one array of the plan into a HOST buffer the caller sized from f3m_plan_get_level.
+ * tree: 0 = target (X) tree, 1 = source (Y) tree.  `what`:                                  */
+#define F3M_ARR_SORTED_INDEX 0  /* int32 (n)        sorted position -> input row    (n_tree.cu:59 sorted_index) */
+#define F3M_ARR_BOX_OFFSETS 1   /* int32 (boxes+1)  per level                       (n_tree.cu:70 unique_counts_cum_reindexed) */
+#define F3M_ARR_BOX_CENTERS 2   /* float (boxes,d)  per level                       (n_tree.cu:65 centers) */
+#define F3M_ARR_FAR_PTR 3       /* int32 (boxes_x+1) CSR row pointers of the far list of the level */
+#define F3M_ARR_FAR_IDX 4       /* int32 (n_far)     source box of every far pair, grouped by target box */
+#define F3M_ARR_SMALL_PTR 5
+#define F3M_ARR_SMALL_IDX 6
+#define F3M_ARR_KEEP_PTR 7      /* pairs handed to the next level; at the last level: the final near list */
+#define F3M_ARR_KEEP_IDX 8
+#define F3M_ARR_BOX_CODES 9     /* uint32 (boxes) Morton prefix of every box */
+int f3m_plan_copy_array(const f3m_plan *plan, int32_t level, int32_t tree, int32_t what, void *host_dst,
+                        size_t dst_bytes);
+
+/* -------- exact dense op ------------------------------------------------------------------ */
+
+/* out[i] = sum_j exp(-|x_i-y_j|^2/(2 ls^2)) b_j : replaces rbf_call<float,d> / rbf_call<double,d>
+ * (F3M_src/n_tree.cu:185-211; rbf_float_d / rbf_double_d, pybinder_setup.cu:40-62).  The f64 entry
+ * uses a double-precision exponential (the reference evaluates expf even for double, 1_d_conv.cu:72). */
+int f3m_rbf_dense_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R,
+                      int32_t d, float ls, float *out, void *stream);
+int f3m_rbf_dense_f64(const double *X, int64_t N, const double *Y, int64_t M, const double *b, int32_t R,
+                      int32_t d, double ls, double *out, void *stream);
+/* out[i] = ls^-3 sum_j r_ij^2 exp(-r_ij^2/(2 ls^2)) b_j : replaces rbf_call_grad<float,d>
+ * (n_tree.cu:213-241; rbf_float_d_grad, pybinder_setup.cu:64-73). */
+int f3m_rbf_dense_grad_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R,
+                           int32_t d, float ls, float *out, void *stream);
+
+/* -------- measurement helpers -------------------------------------------------------------- */
+
+/* Measures the SM's exponential (MUFU.EX2) and FP32 FMA issue peaks with two register-only
+ * kernels: results in giga-operations per second for the whole device. */
+int f3m_measure_peaks(double *gexp_per_s, double *gfma_per_s, void *stream);
+/* Device time (ms) of the stages of the last f3m_plan_apply: [0]=sort/permute of b, [1]=small+near
+ * direct sums, [2]=P2M, [3]=M2L, [4]=L2P, [5]=output un-permute, [6]=total, [7]=f3m_plan_create of this plan. */
+int f3m_plan_last_timings(const f3m_plan *plan, float ms[8]);
+/* Number of direct-sum kernel launches inside the last f3m_plan_apply, and kernels launched by the
+ * library since it was loaded (all entry points). */
+int f3m_plan_last_direct_launches(const f3m_plan *plan);
+long long f3m_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* F3M_H */

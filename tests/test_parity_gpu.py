@@ -1,0 +1,156 @@
+"""GPU parity tests: the CUDA engine (through the C ABI) against the CPU oracle on seeded inputs.
+
+Bit-exact: per-level box offsets / counts, box centres, far / small / keep pair lists (engine in
+IEEE mode vs the oracle's IEEE float32 arithmetic).  Floating point: KMVM output within rel-L2
+1e-5 of the oracle's output and no worse than the oracle against the exact float64 product
+(tolerances are the ones BASELINE.json's north_star states)."""
+import numpy as np
+import pytest
+import torch
+
+from cases import CASES, make_case, oracle_kwargs, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+TOL_VS_ORACLE = 1e-5
+
+
+def _run_engine(c, dev, math_mode):
+    from f3m_b200 import engine, _lib
+    prm = engine.make_params(c["ls"], c["min_points"], c["P"], c["var_comp"], c["eff"], c["small"], math_mode)
+    X = c["X"].to(dev)
+    Y = None if c["Y"] is None else c["Y"].to(dev)
+    plan = engine.Plan(X, Y, prm)
+    out = plan.apply(c["b"].to(dev))
+    return plan, out
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_engine_matches_oracle(name, cuda):
+    from f3m_b200 import _lib
+    from oracle.f3m_oracle import f3m_kmvm, dense_kmvm_f64
+    c = make_case(name)
+    trace, stats = [], {}
+    ref = f3m_kmvm(c["X"], c["Y"], c["b"], trace=trace, stats=stats, **oracle_kwargs(c))
+    plan, out = _run_engine(c, cuda, _lib.MATH_IEEE)
+    st = plan.stats()
+    levels = [t for t in trace if "far" in t]
+    assert st["levels"] == len(levels)
+    # ---- box assignment and interaction lists: bit-exact ------------------------------------
+    for t in levels:
+        l = t["level"]
+        for tree, key in ((0, "x"), (1, "y")):
+            off = plan.array(l, tree, _lib.ARR_BOX_OFFSETS)
+            assert np.array_equal(off, t[key]["offsets"].numpy().astype(np.int32)), f"box offsets differ at level {l}"
+            ctr = plan.array(l, tree, _lib.ARR_BOX_CENTERS)
+            assert np.array_equal(ctr, t[key]["centers"].numpy()), f"box centres differ at level {l}"
+            perm = plan.array(l, tree, _lib.ARR_SORTED_INDEX).astype(np.int64)
+            box_of_sorted = np.repeat(np.arange(off.size - 1), np.diff(off))
+            box_of_point = np.empty_like(box_of_sorted)
+            box_of_point[perm] = box_of_sorted
+            assert np.array_equal(box_of_point, t[key]["box_of_point"].numpy()), f"box of point differs at level {l}"
+        for cls in ("far", "small", "keep"):
+            assert np.array_equal(plan.pairs(l, cls), t[cls].numpy()), f"{cls} list differs at level {l}"
+    assert st["direct_pairs"] == stats.get("direct_pairs", 0)
+    assert st["node_pairs"] == stats.get("node_pairs", 0)
+    # ---- output -------------------------------------------------------------------------------
+    out = out.cpu()
+    err_ref = rel_l2(out, ref)
+    assert err_ref <= TOL_VS_ORACLE, f"rel-L2 vs oracle {err_ref:.3e}"
+    rows = torch.arange(min(c["N"], 3000))
+    Ysrc = c["X"] if c["Y"] is None else c["Y"]
+    exact = dense_kmvm_f64(c["X"], Ysrc, c["b"], c["ls"], rows=rows)
+    e_engine, e_oracle = rel_l2(out[rows], exact), rel_l2(ref[rows], exact)
+    assert e_engine <= max(1.2 * e_oracle, e_oracle + 2e-6), f"engine {e_engine:.3e} vs oracle {e_oracle:.3e} against float64"
+
+
+@pytest.mark.parametrize("name", ["u3_shared", "u3_xy", "n4_r8"])
+def test_fastmath_mode_close_to_ieee(name, cuda):
+    """The default (fast-math) box index / far test differs from IEEE only for points within a few
+    ulp of a cell face or pairs on the distance threshold: box counts differ by a handful of points."""
+    from f3m_b200 import _lib
+    c = make_case(name)
+    p0, o0 = _run_engine(c, cuda, _lib.MATH_IEEE)
+    p1, o1 = _run_engine(c, cuda, _lib.MATH_FASTMATH)
+    assert p0.stats()["levels"] == p1.stats()["levels"]
+    for l in range(1, p0.stats()["levels"] + 1):
+        a, b = p0.array(l, 0, _lib.ARR_BOX_OFFSETS), p1.array(l, 0, _lib.ARR_BOX_OFFSETS)
+        assert a.size == b.size
+        assert np.abs(np.diff(a) - np.diff(b)).sum() <= max(4, c["N"] // 5000)
+    assert rel_l2(o1.cpu(), o0.cpu()) <= 1e-4
+
+
+def test_one_shot_and_plan_agree(cuda):
+    from f3m_b200 import engine, _lib
+    c = make_case("u3_shared")
+    prm = engine.make_params(c["ls"], c["min_points"], c["P"], c["var_comp"], c["eff"], c["small"])
+    X, b = c["X"].to(cuda), c["b"].to(cuda)
+    a = engine.kmvm(X, None, b, prm)
+    plan = engine.Plan(X, None, prm)
+    b1 = plan.apply(b)
+    b2 = plan.apply(b)
+    assert rel_l2(a.cpu(), b1.cpu()) <= 2e-6
+    assert rel_l2(b2.cpu(), b1.cpu()) <= 2e-6
+    host = engine.kmvm_host(c["X"], None, c["b"], prm)
+    assert rel_l2(host, b1.cpu()) <= 2e-6
+
+
+def test_row_range_shards_sum_to_full(cuda):
+    """Target boxes sharded over row ranges (the multi-GPU split) add up to the full product."""
+    from f3m_b200 import engine
+    c = make_case("u3_shared")
+    prm = engine.make_params(c["ls"], c["min_points"], c["P"], c["var_comp"], c["eff"], c["small"])
+    plan = engine.Plan(c["X"].to(cuda), None, prm)
+    b = c["b"].to(cuda)
+    full = plan.apply(b)
+    N = c["N"]
+    cuts = [0, N // 3, N // 2, N]
+    parts = sum(plan.apply(b, row_range=(cuts[i], cuts[i + 1])) for i in range(3))
+    assert rel_l2(parts.cpu(), full.cpu()) <= 1e-6
+
+
+def test_dense_ops(cuda):
+    from f3m_b200 import engine
+    from oracle.f3m_oracle import dense_kmvm_f64
+    g = torch.Generator().manual_seed(5)
+    for d in (1, 2, 3, 4, 5):
+        X, Y = torch.rand(700, d, generator=g), torch.rand(900, d, generator=g)
+        b = torch.randn(900, 3, generator=g)
+        exact = dense_kmvm_f64(X, Y, b, 0.6)
+        out32 = engine.rbf_dense(X.to(cuda), Y.to(cuda), b.to(cuda), 0.6).cpu()
+        out64 = engine.rbf_dense(X.double().to(cuda), Y.double().to(cuda), b.double().to(cuda), 0.6).cpu()
+        assert rel_l2(out32, exact) <= 5e-6
+        assert rel_l2(out64, exact) <= 1e-13
+        # gradient op: ls^-3 sum r^2 exp(-r^2/(2 ls^2)) b   (n_tree.cu:213-241)
+        r2 = torch.cdist(X.double(), Y.double()) ** 2
+        gexact = (r2 * torch.exp(-r2 / (2 * 0.6 ** 2))) @ b.double() / 0.6 ** 3
+        gout = engine.rbf_dense(X.to(cuda), Y.to(cuda), b.to(cuda), 0.6, grad=True).cpu()
+        assert rel_l2(gout, gexact) <= 1e-5
+
+
+def test_operator_surface(cuda):
+    """FFM(X, ...) @ b, forward, chunked products and the ffm_3d_float function table."""
+    import ffm_3d_float
+    from F3M_src.FFM_classes import FFM, benchmark_matmul, benchmark_matmul_double
+    torch.manual_seed(0)
+    X = torch.rand(20000, 3)
+    Y = torch.rand(6000, 3)
+    b = torch.randn(20000, 1)
+    op = FFM(X, ls=1.0, min_points=500, nr_of_interpolation=64, small_field_points=64, device="cuda:0")
+    res = op @ b
+    assert res.shape == (20000, 1) and res.is_cuda
+    exact = benchmark_matmul_double(X[:2000], X, ls=1.0, device="cuda:0") @ b
+    assert rel_l2(res[:2000].cpu(), exact.cpu()) <= 1e-4
+    exact32 = benchmark_matmul(X[:2000], X, ls=1.0, device="cuda:0") @ b
+    assert rel_l2(exact32.cpu(), exact.cpu()) <= 5e-6
+    res2 = ffm_3d_float.FFM_XY_FLOAT_3(op.X, op.X, b.to("cuda:0"), "cuda:0", 1.0, 500.0, 64, False, 0.15, 64)
+    assert rel_l2(res2.cpu(), res.cpu()) <= 2e-6
+    opxy = FFM(X, Y, ls=1.0, min_points=500, nr_of_interpolation=64, small_field_points=64, device="cuda:0")
+    by = torch.randn(6000, 2)
+    full = opxy @ by
+    chunked = opxy.chunk_forward_example(by, chunks=3)
+    assert rel_l2(chunked.cpu(), full.cpu()) <= 1e-4
+    with pytest.raises(AssertionError):
+        opxy.forward(opxy.X, opxy.Y, torch.randn(5, 1, device="cuda:0"))
+    with pytest.raises(AssertionError):
+        op.forward(op.X.cpu(), op.X.cpu(), b)

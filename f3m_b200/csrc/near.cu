@@ -12,6 +12,7 @@
 // the warp and a pair costs d subtractions, d multiply-adds, one ex2 and RB multiply-adds.  This kernel
 // is bound by the SM's FP32 issue rate and its exponential (MUFU) rate, not by HBM: a source row is
 // reused by every target of the tile.
+#include <algorithm>
 #include "common.cuh"
 
 namespace f3m {
@@ -341,18 +342,22 @@ void dense_f32(const float *X, int64_t N, const float *Y, int64_t M, const float
 template void dense_f32<false>(const float *, int64_t, const float *, int64_t, const float *, int, int, float, float *, cudaStream_t);
 template void dense_f32<true>(const float *, int64_t, const float *, int64_t, const float *, int, int, float, float *, cudaStream_t);
 
-// float64 dense product with a double-precision exponential (accuracy reference on the device)
+// float64 dense product with a double-precision exponential (accuracy reference on the device).
+// grid.y slices the sources so that a few thousand target rows still fill the GPU; slices are combined
+// with double atomics into a zeroed output.
 __global__ void __launch_bounds__(128) dense_f64_kernel(const double *__restrict__ X, int64_t n, const double *__restrict__ Y,
                                                        int64_t m, const double *__restrict__ b, int R, int d, double lcs,
                                                        double *out) {
     __shared__ double sy[128 * F3M_MAX_DIM];
     const int64_t i = (int64_t)blockIdx.x * 128 + threadIdx.x;
+    const int64_t per = (m + gridDim.y - 1) / gridDim.y;
+    const int64_t m0 = (int64_t)blockIdx.y * per, m1 = min(m, m0 + per);
     double xi[F3M_MAX_DIM];
     for (int k = 0; k < d; k++) xi[k] = X[(i < n ? i : n - 1) * d + k];
     for (int r = 0; r < R; r++) {
         double acc = 0.;
-        for (int64_t base = 0; base < m; base += 128) {
-            int cnt = (int)min((int64_t)128, m - base);
+        for (int64_t base = m0; base < m1; base += 128) {
+            int cnt = (int)min((int64_t)128, m1 - base);
             __syncthreads();
             for (int q = threadIdx.x; q < cnt * d; q += 128) sy[q] = Y[base * d + q];
             __syncthreads();
@@ -362,13 +367,17 @@ __global__ void __launch_bounds__(128) dense_f64_kernel(const double *__restrict
                 acc += exp(-r2 * lcs) * b[(base + j) * R + r];
             }
         }
-        if (i < n) out[i * R + r] = acc;
+        if (i < n) atomicAdd(&out[i * R + r], acc);
     }
 }
 
 void dense_f64(const double *X, int64_t N, const double *Y, int64_t M, const double *b, int R, int d, double ls, double *out,
                cudaStream_t s) {
-    dense_f64_kernel<<<(unsigned)((N + 127) / 128), 128, 0, s>>>(X, N, Y, M, b, R, d, 1.0 / (2.0 * ls * ls), out);
+    F3M_CUDA(cudaMemsetAsync(out, 0, (size_t)N * R * sizeof(double), s));
+    const unsigned gx = (unsigned)((N + 127) / 128);
+    int64_t want = (int64_t)NUM_SMS_HINT * 16 / gx;
+    unsigned gy = (unsigned)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, (M + 4095) / 4096), 4096));
+    dense_f64_kernel<<<dim3(gx, gy), 128, 0, s>>>(X, N, Y, M, b, R, d, 1.0 / (2.0 * ls * ls), out);
     F3M_LAUNCH_CHECK();
 }
 
@@ -377,6 +386,7 @@ void dense_f64(const double *X, int64_t N, const double *Y, int64_t M, const dou
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) probe_ex2(float *out, int iters) {
     float a = threadIdx.x * 1e-3f, b = a + 0.1f, c = a + 0.2f, d = a + 0.3f;
+#pragma unroll 8
     for (int i = 0; i < iters; i++) {
         a = ex2_approx(-a); b = ex2_approx(-b); c = ex2_approx(-c); d = ex2_approx(-d);
     }
@@ -385,6 +395,7 @@ __global__ void __launch_bounds__(256) probe_ex2(float *out, int iters) {
 __global__ void __launch_bounds__(256) probe_fma(float *out, int iters) {
     float a = threadIdx.x * 1e-3f, b = a + 0.1f, c = a + 0.2f, d = a + 0.3f, e = a + 0.4f, f = a + 0.5f, g = a + 0.6f, h = a + 0.7f;
     const float m = 0.999f, q = 1e-3f;
+#pragma unroll 8
     for (int i = 0; i < iters; i++) {
         a = fmaf(a, m, q); b = fmaf(b, m, q); c = fmaf(c, m, q); d = fmaf(d, m, q);
         e = fmaf(e, m, q); f = fmaf(f, m, q); g = fmaf(g, m, q); h = fmaf(h, m, q);

@@ -183,25 +183,24 @@ static void plan_apply(f3m_plan *pl, const float *b, int R, float *out, int64_t 
     pl->last.begin(ST_TOTAL, s);
 
     pl->last.begin(ST_PERMUTE, s);
-    DevBuf<float> bs, outs, packed1;
+    DevBuf<float> bs, outs;
     bs.alloc((size_t)M * R, s);
     gather_rows(b, ty.perm.p, bs.p, M, R, s);
     outs.alloc((size_t)N * R, s);
     outs.zero();
-    if (R == 1) build_packed_sources(pl, bs.p, packed1, s);
     pl->last.end(s);
 
     const int L = pl->levels;
     if (L == 0) {
         // largest box already small enough: one direct product over the root pair
-        direct_sums(pl, 0, pl->lists[0].keep, packed1.p, bs.p, R, outs.p, row_begin, row_end, s);
+        direct_sums(pl, 0, pl->lists[0].keep, bs.p, R, outs.p, row_begin, row_end, s);
     }
     for (int level = 1; level <= L; level++) {
         LevelLists &ll = pl->lists[level];
-        direct_sums(pl, level, ll.small, packed1.p, bs.p, R, outs.p, row_begin, row_end, s);   // n_tree.cu:1018-1020
-        far_field_level(pl, level, bs.p, R, outs.p, row_begin, row_end, s);                    // n_tree.cu:1021-1051
+        direct_sums(pl, level, ll.small, bs.p, R, outs.p, row_begin, row_end, s);   // n_tree.cu:1018-1020
     }
-    if (L > 0) direct_sums(pl, L, pl->lists[L].keep, packed1.p, bs.p, R, outs.p, row_begin, row_end, s);   // n_tree.cu:1092-1094
+    far_field(pl, bs.p, R, outs.p, row_begin, row_end, s);                          // n_tree.cu:1021-1051, all levels
+    if (L > 0) direct_sums(pl, L, pl->lists[L].keep, bs.p, R, outs.p, row_begin, row_end, s);   // n_tree.cu:1092-1094
 
     pl->last.begin(ST_UNPERMUTE, s);
     scatter_rows(outs.p, tx.perm.p, out, N, R, s);

@@ -10,7 +10,7 @@
 namespace f3m {
 
 constexpr int MAXD = F3M_MAX_DIM;
-constexpr int MAXP = 16;   // interpolation nodes per dimension the kernels hold
+constexpr int MAXP = 64;   // interpolation nodes per dimension the kernels hold
 constexpr int NUM_SMS_HINT = 148;
 
 // ---- error handling: every CUDA call is checked, the message is kept per thread --------------
@@ -180,14 +180,13 @@ void accumulate_pair_work(f3m_plan *pl, int level, const PairCSR &csr, int64_t *
 // ---- far.cu ----------------------------------------------------------------------------------
 int nodes_per_dim(int d, int nr_interpolation);   // get_node_list for perfect powers, floor otherwise
 void far_field_level(f3m_plan *pl, int level, const float *b_sorted, int R, float *out_sorted,
-                     int64_t row_begin, int64_t row_end, cudaStream_t s);
+                     int64_t row_begin, int64_t row_end, cudaStream_t s);   // per-level path (far.cu)
+void far_field(f3m_plan *pl, const float *b_sorted, int R, float *out_sorted, int64_t row_begin, int64_t row_end,
+               cudaStream_t s);                                               // whole product (far_fast.cu)
 
 // ---- near.cu ---------------------------------------------------------------------------------
-// packed1: rows [s*y, b] of a single-column product (shared by every list of the product), or null;
-// b_sorted (M,R) is used to pack per column block when R > 1.
-void build_packed_sources(f3m_plan *pl, const float *b_sorted, DevBuf<float> &packed1, cudaStream_t s);
-void direct_sums(f3m_plan *pl, int level, const PairCSR &csr, const float *packed1, const float *b_sorted, int R,
-                 float *out_sorted, int64_t row_begin, int64_t row_end, cudaStream_t s);
+void direct_sums(f3m_plan *pl, int level, const PairCSR &csr, const float *b_sorted, int R, float *out_sorted,
+                 int64_t row_begin, int64_t row_end, cudaStream_t s);
 template <bool GRAD>
 void dense_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int R, int d, float ls, float *out,
                cudaStream_t s);

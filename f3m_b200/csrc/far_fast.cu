@@ -1,0 +1,549 @@
+// Far field, fast path: one pass over the points, box-to-box translations in between.
+//
+// The reference interpolates every level directly from and to the points: P2M and L2P touch all N
+// points at every level, and the node-to-node step evaluates P^2 exponentials per box pair
+// (far_field_compute_v2, F3M_src/n_tree.cu:489-593; kernels F3M_src/1_d_conv.cu:451-659, 741-817).
+// Here, with p nodes per dimension and P = p^d:
+//
+//   P2M   only at the finest level (one CTA per box, no atomics);
+//   M2M   moments of a box = sum over its children of (A_s0 x A_s1 x ..) child moments, where
+//         A_s[i][j] = L_i(s/2 + t_j/2) is the parent's 1-D Lagrange basis at the child's nodes.  A
+//         parent basis function restricted to a child is a polynomial of degree p-1 per dimension, so
+//         interpolating it on the child's p nodes is exact: these are the moments the reference
+//         computes from the points, up to rounding;
+//   M2L   per far pair the P x P Gaussian block is the Kronecker product of d tabulated p x p
+//         matrices that depend only on the integer box offset per dimension: d*p*P multiply-adds and
+//         no exponential per pair;
+//   L2L   the transpose of M2M, pushing local expansions down to the finest level;
+//   L2P   only at the finest level.
+//
+// All three translations are "apply d small matrices along the d axes of a p^d array"; a warp does
+// that for one box (pair) at a time with the array in its own shared-memory buffers.  Every kernel
+// here is bound by shared-memory / L2 bandwidth and FP32 issue, not HBM: the moment arrays of the
+// finest level (boxes * P floats) are read a few times from L2/HBM, the points once.
+#include <math.h>
+#include <algorithm>
+#include <vector>
+#include "common.cuh"
+
+namespace f3m {
+
+constexpr int NOFF2 = 16;     // tabulated box offsets per dimension
+constexpr int PMAX_FAST = 8;  // nodes per dimension handled by this path
+
+struct NodeTab2 {
+    int p;
+    float node[PMAX_FAST];
+    float w[PMAX_FAST];
+};
+
+struct Geom2 {
+    int dqmin[MAXD];
+    double shift[MAXD];
+};
+
+__host__ __device__ constexpr int mat_stride(int p) { return (p * p + 3) / 4 * 4; }
+
+// chebyshev_nodes_1D / get_w_j_first_kind (n_tree.cu:265-285)
+static NodeTab2 make_nodes2(int p) {
+    NodeTab2 t{};
+    t.p = p;
+    const float PI = (float)(atan(1.) * 4.);
+    for (int i = 0; i < p; i++) {
+        float arg = ((float)i * 2.f + 1.f) * PI / (float)(2 * (p - 1) + 2);
+        t.node[i] = (float)cos((double)arg);
+        t.w[i] = (float)(pow(-1.0, i) * sin(((2. * (float)i + 1.) * PI) / (2. * (float)(p - 1.0) + 2.)));
+    }
+    return t;
+}
+
+// ---------------------------------------------------------------------------------------------
+// tables
+// ---------------------------------------------------------------------------------------------
+// T[k][o][i*p+j] = exp(-lcs (g_i - g_j - delta)^2), delta = (o + dqmin_k) edge + shift_k, g = node*edge/2
+// (setup_skip_conv n_tree.cu:433-486 adds the centres to the scaled nodes; the +edge/2 of n_tree.cu:510 cancels)
+__global__ void m2l_table2(NodeTab2 nt, int d, double edge, double lcs, Geom2 geo, float *T) {
+    const int p = nt.p, MS = mat_stride(p);
+    const int tot = d * NOFF2 * MS;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < tot; e += gridDim.x * blockDim.x) {
+        int q = e % MS, o = (e / MS) % NOFF2, k = e / (MS * NOFF2);
+        float v = 0.f;
+        if (q < p * p) {
+            int in = q / p, jn = q % p;
+            double delta = (double)(o + geo.dqmin[k]) * edge + geo.shift[k];
+            double diff = ((double)nt.node[in] - (double)nt.node[jn]) * edge * 0.5 - delta;
+            v = (float)exp(-lcs * diff * diff);
+        }
+        T[e] = v;
+    }
+}
+
+// A[s][i*p+j] = L_i(xi), xi = (s ? +0.5 : -0.5) + 0.5 t_j ; AT is its transpose.  Exact Lagrange products in double.
+static void make_shift_tables(const NodeTab2 &nt, std::vector<float> &A, std::vector<float> &AT) {
+    const int p = nt.p, MS = mat_stride(p);
+    A.assign(2 * MS, 0.f);
+    AT.assign(2 * MS, 0.f);
+    for (int s = 0; s < 2; s++)
+        for (int j = 0; j < p; j++) {
+            double xi = (s ? 0.5 : -0.5) + 0.5 * (double)nt.node[j];
+            for (int i = 0; i < p; i++) {
+                double L = 1.0;
+                for (int l = 0; l < p; l++)
+                    if (l != i) L *= (xi - (double)nt.node[l]) / ((double)nt.node[i] - (double)nt.node[l]);
+                A[s * MS + i * p + j] = (float)L;
+                AT[s * MS + j * p + i] = (float)L;
+            }
+        }
+}
+
+// ---------------------------------------------------------------------------------------------
+// warp-level "apply d matrices along the d axes"
+// Array layout: index = m*RB + r, m = sum_k m_k p^k (dimension 0 fastest), r the column.
+// Stage k transforms axis k: out[.., i, ..] = sum_j M_k[i][j] in[.., j, ..].  The last stage adds into acc.
+// ---------------------------------------------------------------------------------------------
+template <int PP>
+__device__ __forceinline__ void warp_kron(const float *src0, float *bufA, float *bufB, float *acc,
+                                          const float *const *mats, int d, int RB, int P, int lane) {
+    const float *src = src0;
+    float *dst = bufA;
+    int st = RB;
+    const int nf = (P / PP) * RB;
+    for (int k = 0; k < d; k++) {
+        const bool last = (k == d - 1);
+        float M[PP * PP];
+        const float *Mk = mats[k];
+#pragma unroll
+        for (int q = 0; q < PP * PP; q++) M[q] = Mk[q];
+        for (int f = lane; f < nf; f += 32) {
+            const int hi = f / st, lo = f - hi * st;
+            const int base = hi * st * PP + lo;
+            float v[PP];
+#pragma unroll
+            for (int j = 0; j < PP; j++) v[j] = src[base + j * st];
+#pragma unroll
+            for (int i = 0; i < PP; i++) {
+                float o = 0.f;
+#pragma unroll
+                for (int j = 0; j < PP; j++) o = fmaf(M[i * PP + j], v[j], o);
+                if (last) acc[base + i * st] += o;
+                else dst[base + i * st] = o;
+            }
+        }
+        __syncwarp();
+        src = dst;
+        dst = (dst == bufA) ? bufB : bufA;
+        st *= PP;
+    }
+}
+
+__device__ __forceinline__ void decode_cell2(uint32_t code, int level, int d, int *q) {
+    for (int k = 0; k < d; k++) q[k] = 0;
+    for (int jb = 0; jb < level; jb++)
+        for (int k = 0; k < d; k++) q[k] |= (int)((code >> (d * jb + k)) & 1u) << jb;
+}
+
+// ---------------------------------------------------------------------------------------------
+// M2L: one CTA per target box, its warps share the far row
+// ---------------------------------------------------------------------------------------------
+template <int PP>
+__global__ void __launch_bounds__(128) m2l_fast(int nbx, int level, int d, const int *__restrict__ fptr,
+                                               const int *__restrict__ fidx, const uint32_t *__restrict__ code_x,
+                                               const uint32_t *__restrict__ code_y, const int *__restrict__ off_x,
+                                               int row_begin, int row_end, const float *__restrict__ T, Geom2 geo, int P,
+                                               int RB, const float *__restrict__ mom, float *loc, int *err) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int MS = mat_stride(PP);
+    const int bx = blockIdx.x;
+    const int e0 = fptr[bx], e1 = fptr[bx + 1];
+    if (e0 == e1) return;
+    if (off_x[bx + 1] <= row_begin || off_x[bx] >= row_end) return;   // box has no point in this rank's slice
+    const int nw = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int PR = P * RB, ntab = d * NOFF2 * MS;
+    float *Tsm = sm;
+    float *wbuf = sm + ntab + (size_t)w * 3 * PR;
+    float *bufA = wbuf, *bufB = wbuf + PR, *acc = wbuf + 2 * PR;
+    for (int q = threadIdx.x; q < ntab; q += blockDim.x) Tsm[q] = T[q];
+    for (int q = lane; q < PR; q += 32) acc[q] = 0.f;
+    __syncthreads();
+    int qx[MAXD];
+    decode_cell2(code_x[bx], level, d, qx);
+    for (int e = e0 + w; e < e1; e += nw) {
+        const int by = fidx[e];
+        int qy[MAXD];
+        decode_cell2(code_y[by], level, d, qy);
+        const float *mats[MAXD];
+        bool ok = true;
+        for (int k = 0; k < d; k++) {
+            int o = qy[k] - qx[k] - geo.dqmin[k];
+            if (o < 0 || o >= NOFF2) { ok = false; o = 0; }
+            mats[k] = Tsm + (k * NOFF2 + o) * MS;
+        }
+        if (!ok) { if (lane == 0) atomicExch(err, 2); continue; }
+        warp_kron<PP>(mom + (size_t)by * PR, bufA, bufB, acc, mats, d, RB, P, lane);
+    }
+    __syncthreads();
+    for (int q = threadIdx.x; q < PR; q += blockDim.x) {
+        float s = 0.f;
+        for (int ww = 0; ww < nw; ww++) s += sm[ntab + (size_t)ww * 3 * PR + 2 * PR + q];
+        loc[(size_t)bx * PR + q] = s;
+    }
+}
+
+// M2M: one CTA per parent box, warps share the children
+template <int PP>
+__global__ void __launch_bounds__(128) m2m_fast(int nbp, int d, const int *__restrict__ child_start,
+                                               const uint32_t *__restrict__ code_child, const float *__restrict__ A, int P,
+                                               int RB, const float *__restrict__ mom_child, float *mom_parent) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int MS = mat_stride(PP);
+    const int pb = blockIdx.x;
+    const int nw = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int PR = P * RB, ntab = 2 * MS;
+    float *Asm = sm;
+    float *wbuf = sm + ntab + (size_t)w * 3 * PR;
+    float *bufA = wbuf, *bufB = wbuf + PR, *acc = wbuf + 2 * PR;
+    for (int q = threadIdx.x; q < ntab; q += blockDim.x) Asm[q] = A[q];
+    for (int q = lane; q < PR; q += 32) acc[q] = 0.f;
+    __syncthreads();
+    const int c0 = child_start[pb], c1 = child_start[pb + 1];
+    for (int c = c0 + w; c < c1; c += nw) {
+        const uint32_t code = code_child[c];
+        const float *mats[MAXD];
+        for (int k = 0; k < d; k++) mats[k] = Asm + ((code >> k) & 1u) * MS;
+        warp_kron<PP>(mom_child + (size_t)c * PR, bufA, bufB, acc, mats, d, RB, P, lane);
+    }
+    __syncthreads();
+    for (int q = threadIdx.x; q < PR; q += blockDim.x) {
+        float s = 0.f;
+        for (int ww = 0; ww < nw; ww++) s += sm[ntab + (size_t)ww * 3 * PR + 2 * PR + q];
+        mom_parent[(size_t)pb * PR + q] = s;
+    }
+}
+
+// L2L: one warp per child box
+template <int PP>
+__global__ void __launch_bounds__(128) l2l_fast(int nbc, int d, const int *__restrict__ parent,
+                                               const uint32_t *__restrict__ code_child, const int *__restrict__ off_c,
+                                               int row_begin, int row_end, const float *__restrict__ AT, int P, int RB,
+                                               const float *__restrict__ loc_parent, float *loc_child) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int MS = mat_stride(PP);
+    const int nw = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int PR = P * RB, ntab = 2 * MS;
+    float *Asm = sm;
+    float *wbuf = sm + ntab + (size_t)w * 3 * PR;
+    float *bufA = wbuf, *bufB = wbuf + PR, *acc = wbuf + 2 * PR;
+    for (int q = threadIdx.x; q < ntab; q += blockDim.x) Asm[q] = AT[q];
+    __syncthreads();
+    const int c = blockIdx.x * nw + w;
+    if (c >= nbc) return;
+    if (off_c[c + 1] <= row_begin || off_c[c] >= row_end) return;
+    for (int q = lane; q < PR; q += 32) acc[q] = 0.f;
+    __syncwarp();
+    const uint32_t code = code_child[c];
+    const float *mats[MAXD];
+    for (int k = 0; k < d; k++) mats[k] = Asm + ((code >> k) & 1u) * MS;
+    warp_kron<PP>(loc_parent + (size_t)parent[c] * PR, bufA, bufB, acc, mats, d, RB, P, lane);
+    for (int q = lane; q < PR; q += 32) loc_child[(size_t)c * PR + q] += acc[q];
+}
+
+// ---------------------------------------------------------------------------------------------
+// P2M / L2P at the finest level: one CTA per (box, split)
+// ---------------------------------------------------------------------------------------------
+// Barycentric Lagrange basis (lagrange_data_load + calculate_barycentric_lagrange, 1_d_conv.cu:217-238, 418-448)
+template <int PP>
+__device__ __forceinline__ void lagrange_pp(float t, const NodeTab2 &nt, float *L) {
+    int hit = -1;
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < PP; i++) {
+        float diff = t - nt.node[i];
+        if (diff == 0.f) hit = i;
+        else sum += nt.w[i] / diff;
+    }
+    if (hit >= 0) {
+#pragma unroll
+        for (int i = 0; i < PP; i++) L[i] = (i == hit) ? 1.f : 0.f;
+    } else {
+        const float lx = 1.f / sum;
+#pragma unroll
+        for (int i = 0; i < PP; i++) L[i] = (lx * nt.w[i]) / (t - nt.node[i]);
+    }
+}
+
+template <int PP, int RB>
+__global__ void p2m_leaf(const float *__restrict__ pts, int n, int d, const float *__restrict__ bs, int R, int r0,
+                         const int *__restrict__ off, const float *__restrict__ ctr, float factor, NodeTab2 nt, int P,
+                         int nsplit, float *mom) {
+    extern __shared__ __align__(16) float sm[];
+    const int TP = blockDim.x;
+    float *Ls = sm;                                   // [d*PP][TP+1]
+    float *bsm = Ls + (size_t)d * PP * (TP + 1);      // [TP][RB]
+    float *accsm = bsm + (size_t)TP * RB;             // [P][RB]
+    const int box = blockIdx.x;
+    const int a = off[box], b = off[box + 1];
+    // this CTA's share of the box
+    const int len = b - a;
+    const int s0 = a + (int)(((long long)len * blockIdx.y) / nsplit), s1 = a + (int)(((long long)len * (blockIdx.y + 1)) / nsplit);
+    if (s0 >= s1) return;
+    const int PR = P * RB;
+    for (int q = threadIdx.x; q < PR; q += TP) accsm[q] = 0.f;
+    float c[MAXD];
+    for (int k = 0; k < d; k++) c[k] = ctr[box * d + k];
+    for (int base = s0; base < s1; base += TP) {
+        const int cnt = min(TP, s1 - base);
+        __syncthreads();
+        if ((int)threadIdx.x < cnt) {
+            const int i = base + threadIdx.x;
+            for (int k = 0; k < d; k++) {
+                float L[PP];
+                lagrange_pp<PP>(factor * (pts[(size_t)k * n + i] - c[k]), nt, L);
+#pragma unroll
+                for (int q = 0; q < PP; q++) Ls[(k * PP + q) * (TP + 1) + threadIdx.x] = L[q];
+            }
+#pragma unroll
+            for (int r = 0; r < RB; r++) bsm[threadIdx.x * RB + r] = (r0 + r < R) ? bs[(size_t)i * R + r0 + r] : 0.f;
+        }
+        __syncthreads();
+        for (int m = threadIdx.x; m < P; m += TP) {
+            const float *lp[MAXD];
+            int rem = m;
+            for (int k = 0; k < d; k++) {
+                lp[k] = Ls + (size_t)(k * PP + rem % PP) * (TP + 1);
+                rem /= PP;
+            }
+            float acc[RB];
+#pragma unroll
+            for (int r = 0; r < RB; r++) acc[r] = 0.f;
+            for (int j = 0; j < cnt; j++) {
+                float prod = lp[0][j];
+                for (int k = 1; k < d; k++) prod *= lp[k][j];
+#pragma unroll
+                for (int r = 0; r < RB; r++) acc[r] = fmaf(prod, bsm[j * RB + r], acc[r]);
+            }
+#pragma unroll
+            for (int r = 0; r < RB; r++) accsm[m * RB + r] += acc[r];
+        }
+    }
+    __syncthreads();
+    float *dst = mom + (size_t)box * PR;
+    if (nsplit == 1) for (int q = threadIdx.x; q < PR; q += TP) dst[q] = accsm[q];
+    else for (int q = threadIdx.x; q < PR; q += TP) atomicAdd(dst + q, accsm[q]);
+}
+
+template <int PP, int RB>
+__global__ void __launch_bounds__(128) l2p_leaf(const float *__restrict__ pts, int n, int d, const int *__restrict__ off,
+                                               const float *__restrict__ ctr, float factor, NodeTab2 nt, int P, int nsplit,
+                                               int row_begin, int row_end, const float *__restrict__ loc, int R, int r0,
+                                               float *out) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int TP = 128;
+    const int PR = P * RB;
+    float *locsm = sm;                 // [P][RB]
+    float *Ls = sm + PR;               // [(d-1)*PP][TP]
+    const int box = blockIdx.x;
+    const int a = off[box], b = off[box + 1];
+    if (a < row_begin || a >= row_end) return;    // finest-level boxes belong to the slice their first point is in
+    const int len = b - a;
+    const int s0 = a + (int)(((long long)len * blockIdx.y) / nsplit), s1 = a + (int)(((long long)len * (blockIdx.y + 1)) / nsplit);
+    if (s0 >= s1) return;
+    for (int q = threadIdx.x; q < PR; q += TP) locsm[q] = loc[(size_t)box * PR + q];
+    __syncthreads();
+    float c[MAXD];
+    for (int k = 0; k < d; k++) c[k] = ctr[box * d + k];
+    const int outer = P / PP;
+    for (int i = s0 + threadIdx.x; i < s1; i += TP) {
+        float l0[PP];
+        lagrange_pp<PP>(factor * (pts[i] - c[0]), nt, l0);
+        for (int k = 1; k < d; k++) {
+            float L[PP];
+            lagrange_pp<PP>(factor * (pts[(size_t)k * n + i] - c[k]), nt, L);
+#pragma unroll
+            for (int q = 0; q < PP; q++) Ls[((k - 1) * PP + q) * TP + threadIdx.x] = L[q];
+        }
+        float acc[RB];
+#pragma unroll
+        for (int r = 0; r < RB; r++) acc[r] = 0.f;
+        for (int o = 0; o < outer; o++) {
+            float wgt = 1.f;
+            int rem = o;
+            for (int k = 1; k < d; k++) {
+                wgt *= Ls[((k - 1) * PP + rem % PP) * TP + threadIdx.x];
+                rem /= PP;
+            }
+            float sacc[RB];
+#pragma unroll
+            for (int r = 0; r < RB; r++) sacc[r] = 0.f;
+            const float *lp = locsm + (size_t)o * PP * RB;
+#pragma unroll
+            for (int i0 = 0; i0 < PP; i0++)
+#pragma unroll
+                for (int r = 0; r < RB; r++) sacc[r] = fmaf(l0[i0], lp[i0 * RB + r], sacc[r]);
+#pragma unroll
+            for (int r = 0; r < RB; r++) acc[r] = fmaf(wgt, sacc[r], acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < RB; r++)
+            if (r0 + r < R) out[(size_t)i * R + r0 + r] += acc[r];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host driver
+// ---------------------------------------------------------------------------------------------
+template <int PP, int RB>
+static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *out, int rb, int re, int lmin,
+                           cudaStream_t s) {
+    Tree &tx = pl->tx, &ty = *pl->ty;
+    const int d = pl->d, L = pl->levels;
+    int P = 1;
+    for (int k = 0; k < d; k++) P *= PP;
+    const int PR = P * RB;
+    constexpr int MS = mat_stride(PP);
+    NodeTab2 nt = make_nodes2(PP);
+    const int n_x = (int)tx.n, n_y = (int)ty.n;
+
+    std::vector<DevBuf<float>> mom(L + 1), loc(L + 1);
+    for (int l = lmin; l <= L; l++) {
+        mom[l].alloc((size_t)ty.levels[l].nb * PR, s);
+        loc[l].alloc((size_t)tx.levels[l].nb * PR, s);
+        loc[l].zero();
+    }
+    std::vector<float> hA, hAT;
+    make_shift_tables(nt, hA, hAT);
+    DevBuf<float> A, AT;
+    A.alloc(hA.size(), s); AT.alloc(hAT.size(), s);
+    F3M_CUDA(cudaMemcpyAsync(A.p, hA.data(), hA.size() * sizeof(float), cudaMemcpyHostToDevice, s));
+    F3M_CUDA(cudaMemcpyAsync(AT.p, hAT.data(), hAT.size() * sizeof(float), cudaMemcpyHostToDevice, s));
+    F3M_CUDA(cudaStreamSynchronize(s));   // hA / hAT are pageable host vectors
+
+    // warps per CTA of the translation kernels, limited by shared memory
+    const size_t per_warp = (size_t)3 * PR * sizeof(float);
+    auto warps_for = [&](size_t table_bytes) {
+        size_t avail = 200 * 1024 - table_bytes;
+        int nw = (int)std::min<size_t>(4, avail / per_warp);
+        return nw;
+    };
+
+    // ---- P2M at the finest level, M2M upwards ---------------------------------------------------
+    pl->last.begin(ST_P2M, s);
+    {
+        Level &ly = ty.levels[L];
+        const float factor = 2.f / ly.edge;          // 1_d_conv.cu:473
+        const int TP = P <= 128 ? 128 : 256;
+        int nsplit = std::max(1, std::min(64, (ly.max_count + 8191) / 8192));
+        if (nsplit > 1) mom[L].zero();
+        size_t smem = ((size_t)d * PP * (TP + 1) + (size_t)TP * RB + (size_t)PR) * sizeof(float);
+        F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        p2m_leaf<PP, RB><<<dim3(ly.nb, nsplit), TP, smem, s>>>(ty.pts.p, n_y, d, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt, P,
+                                                              nsplit, mom[L].p);
+        F3M_LAUNCH_CHECK();
+        const int nw = warps_for(2 * MS * sizeof(float));
+        size_t sm2 = (size_t)2 * MS * sizeof(float) + nw * per_warp;
+        F3M_CUDA(cudaFuncSetAttribute(m2m_fast<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2));
+        for (int l = L - 1; l >= lmin; l--) {
+            Level &lp = ty.levels[l], &lc = ty.levels[l + 1];
+            m2m_fast<PP><<<lp.nb, 32 * nw, sm2, s>>>(lp.nb, d, lp.child_start.p, lc.code.p, A.p, P, RB, mom[l + 1].p, mom[l].p);
+            F3M_LAUNCH_CHECK();
+        }
+    }
+    pl->last.end(s);
+    // ---- M2L at every level that has far pairs -------------------------------------------------
+    pl->last.begin(ST_M2L, s);
+    {
+        DevBuf<float> T;
+        T.alloc((size_t)d * NOFF2 * MS, s);
+        const size_t tab = (size_t)d * NOFF2 * MS * sizeof(float);
+        const int nw = warps_for(tab);
+        size_t smem = tab + nw * per_warp;
+        F3M_CUDA(cudaFuncSetAttribute(m2l_fast<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        for (int l = lmin; l <= L; l++) {
+            LevelLists &ll = pl->lists[l];
+            if (ll.far.count == 0) continue;
+            Level &lx = tx.levels[l], &ly = ty.levels[l];
+            Geom2 geo{};
+            for (int k = 0; k < d; k++) {
+                double sh = pl->same ? 0.0 : (double)ty.origin[k] - (double)tx.origin[k];
+                geo.shift[k] = sh;
+                // pairs of level >= 2 descend from parent pairs closer than two parent edges, so their offset lies
+                // within a few boxes of -shift/edge; level-1 pairs are children of the root pair: offsets -1, 0, 1
+                geo.dqmin[k] = (l == 1 ? 0 : (int)floor(-sh / (double)lx.edge)) - NOFF2 / 2 + 1;
+            }
+            m2l_table2<<<8, 256, 0, s>>>(nt, d, (double)lx.edge, (double)pl->lcs, geo, T.p);
+            F3M_LAUNCH_CHECK();
+            m2l_fast<PP><<<lx.nb, 32 * nw, smem, s>>>(lx.nb, l, d, ll.far.ptr.p, ll.far.idx.p, lx.code.p, ly.code.p, lx.off.p, rb,
+                                                     re, T.p, geo, P, RB, mom[l].p, loc[l].p, pl->d_flags);
+            F3M_LAUNCH_CHECK();
+        }
+    }
+    pl->last.end(s);
+    // ---- L2L downwards, L2P at the finest level -------------------------------------------------
+    pl->last.begin(ST_L2P, s);
+    {
+        const int nw = warps_for(2 * MS * sizeof(float));
+        size_t sm2 = (size_t)2 * MS * sizeof(float) + nw * per_warp;
+        F3M_CUDA(cudaFuncSetAttribute(l2l_fast<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2));
+        for (int l = lmin; l < L; l++) {
+            Level &lc = tx.levels[l + 1];
+            l2l_fast<PP><<<(lc.nb + nw - 1) / nw, 32 * nw, sm2, s>>>(lc.nb, d, lc.parent.p, lc.code.p, lc.off.p, rb, re, AT.p, P, RB,
+                                                                    loc[l].p, loc[l + 1].p);
+            F3M_LAUNCH_CHECK();
+        }
+        Level &lx = tx.levels[L];
+        const float factor = 2.f / lx.edge;
+        int nsplit = std::max(1, std::min(64, (lx.max_count + 8191) / 8192));
+        size_t smem = ((size_t)PR + (size_t)std::max(1, d - 1) * PP * 128) * sizeof(float);
+        F3M_CUDA(cudaFuncSetAttribute(l2p_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        l2p_leaf<PP, RB><<<dim3(lx.nb, nsplit), 128, smem, s>>>(tx.pts.p, n_x, d, lx.off.p, lx.ctr.p, factor, nt, P, nsplit, rb, re,
+                                                               loc[L].p, R, r0, out);
+        F3M_LAUNCH_CHECK();
+    }
+    pl->last.end(s);
+}
+
+template <int PP>
+static void far_fast_p(f3m_plan *pl, const float *bs, int R, float *out, int rb, int re, int lmin, cudaStream_t s) {
+    int P = 1;
+    for (int k = 0; k < pl->d; k++) P *= PP;
+    // 8 columns at a time when the three per-warp buffers of the translation kernels fit, else one
+    const bool wide = R > 1 && (size_t)3 * P * 8 * sizeof(float) + (size_t)pl->d * NOFF2 * mat_stride(PP) * sizeof(float) <= 200 * 1024;
+    for (int r0 = 0; r0 < R;) {
+        if (wide) { far_fast_block<PP, 8>(pl, bs, R, r0, out, rb, re, lmin, s); r0 += 8; }
+        else { far_fast_block<PP, 1>(pl, bs, R, r0, out, rb, re, lmin, s); r0 += 1; }
+    }
+}
+
+// Far field of the whole product.  Fast path when every level with far pairs uses the same p <= 8;
+// otherwise (var_compression switching node counts between levels, or more nodes per dimension) the
+// per-level path of far.cu.
+void far_field(f3m_plan *pl, const float *b_sorted, int R, float *out_sorted, int64_t row_begin, int64_t row_end,
+               cudaStream_t s) {
+    const int L = pl->levels;
+    int lmin = 0, p = 0;
+    bool uniform = true;
+    for (int l = 1; l <= L; l++) {
+        if (pl->lists[l].far.count == 0) continue;
+        if (!lmin) { lmin = l; p = pl->lists[l].p; }
+        else if (pl->lists[l].p != p) uniform = false;
+    }
+    if (!lmin) return;
+    int P = 1;
+    for (int k = 0; k < pl->d; k++) P *= p;
+    const bool fits = (size_t)3 * P * sizeof(float) + (size_t)pl->d * NOFF2 * mat_stride(p) * sizeof(float) <= 200 * 1024;
+    if (!uniform || p > PMAX_FAST || p < 2 || !fits) {
+        for (int l = lmin; l <= L; l++) far_field_level(pl, l, b_sorted, R, out_sorted, row_begin, row_end, s);
+        return;
+    }
+    const int rb = (int)row_begin, re = (int)row_end;
+    switch (p) {
+        case 2: far_fast_p<2>(pl, b_sorted, R, out_sorted, rb, re, lmin, s); break;
+        case 3: far_fast_p<3>(pl, b_sorted, R, out_sorted, rb, re, lmin, s); break;
+        case 4: far_fast_p<4>(pl, b_sorted, R, out_sorted, rb, re, lmin, s); break;
+        case 5: far_fast_p<5>(pl, b_sorted, R, out_sorted, rb, re, lmin, s); break;
+        case 6: far_fast_p<6>(pl, b_sorted, R, out_sorted, rb, re, lmin, s); break;
+        case 7: far_fast_p<7>(pl, b_sorted, R, out_sorted, rb, re, lmin, s); break;
+        default: far_fast_p<8>(pl, b_sorted, R, out_sorted, rb, re, lmin, s); break;
+    }
+}
+
+}  // namespace f3m

@@ -63,21 +63,39 @@ __device__ __forceinline__ void tile_accumulate(const float *__restrict__ smem, 
 #pragma unroll
         for (int u = 0; u < TI; u++) {
             float d0 = tx[u][0] - row[0];
-            float r2 = d0 * d0;
+            float nr2 = -d0 * d0;                       // minus the squared distance, built negated
 #pragma unroll
             for (int k = 1; k < D; k++) {
                 float dk = tx[u][k] - row[k];
-                r2 = fmaf(dk, dk, r2);
+                nr2 = fmaf(-dk, dk, nr2);
             }
-            float e = ex2_approx(-r2);
-            if (GRAD) e *= r2;
+            float e = ex2_approx(nr2);
+            if (GRAD) e *= -nr2;
 #pragma unroll
             for (int r = 0; r < RB; r++) acc[u][r] = fmaf(e, row[D + r], acc[u][r]);
         }
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Direct form: pair = d subtractions, d multiply-adds, ex2, RB multiply-adds.  Used when the boxes
+// are wide compared with the lengthscale (see near_kernel_exp below for the usual case).
 // items: (target box, tile) ; tile_off[b] = first item of box b (exclusive scan of tiles per box)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void item_to_tile(int item, const int *__restrict__ tile_off, int nbx,
+                                             const int *__restrict__ off_x, int &box, int &t0, int &t1) {
+    int lo = 0, hi = nbx;   // largest b with tile_off[b] <= item
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (tile_off[mid] <= item) lo = mid; else hi = mid;
+    }
+    box = lo;
+    const int tile = item - tile_off[box], ntiles = tile_off[box + 1] - tile_off[box];
+    const int a = off_x[box], nb = off_x[box + 1] - a;
+    t0 = a + (int)(((long long)nb * tile) / ntiles);          // tiles of one box are equally full
+    t1 = a + (int)(((long long)nb * (tile + 1)) / ntiles);
+}
+
 template <int D, int RB, int TI>
 __global__ void __launch_bounds__(NT) near_kernel(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
                                                  int nbx, const int *__restrict__ tile_off,
@@ -86,17 +104,8 @@ __global__ void __launch_bounds__(NT) near_kernel(const float *__restrict__ xpts
                                                  float scale, int R, int r0, float *out) {
     constexpr int W = row_width(D, RB);
     __shared__ __align__(16) float smem[ST * W];
-    // item -> box: largest b with tile_off[b] <= item
-    const int item = blockIdx.x;
-    int lo = 0, hi = nbx;
-    while (hi - lo > 1) {
-        int mid = (lo + hi) >> 1;
-        if (tile_off[mid] <= item) lo = mid; else hi = mid;
-    }
-    const int box = lo;
-    const int tile = item - tile_off[box], ntiles = tile_off[box + 1] - tile_off[box];
-    const int a = off_x[box], nb = off_x[box + 1] - a;
-    const int t0 = a + (int)(((long long)nb * tile) / ntiles), t1 = a + (int)(((long long)nb * (tile + 1)) / ntiles);
+    int box, t0, t1;
+    item_to_tile(blockIdx.x, tile_off, nbx, off_x, box, t0, t1);
     float tx[TI][D], tot[TI][RB];
     int ti[TI];
 #pragma unroll
@@ -112,7 +121,7 @@ __global__ void __launch_bounds__(NT) near_kernel(const float *__restrict__ xpts
     for (int e = e0; e < e1; e++) {
         const int by = idx[e];
         const int s0 = off_y[by], s1 = off_y[by + 1];
-        float acc[TI][RB];
+        float acc[TI][RB];   // per source box, then added to the running total (blocked accumulation)
 #pragma unroll
         for (int u = 0; u < TI; u++)
 #pragma unroll
@@ -140,6 +149,135 @@ __global__ void __launch_bounds__(NT) near_kernel(const float *__restrict__ xpts
         }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Expanded form, the usual case (box edge not much larger than the lengthscale).  With c the centre
+// of the SOURCE box and s the scale above,
+//     2^(-s^2 |x-y|^2) = 2^(-|xr|^2) * 2^(2 xr.yr) * 2^(-|yr|^2),   xr = s (x-c), yr = s (y-c).
+// The last factor is folded into the source's weight when the rows are packed
+// (row = [2 yr_0 .. 2 yr_{d-1}, b_0 2^(-|yr|^2) ..]), the first is applied once per (target, source
+// box), so that a pair costs d multiply-adds, one ex2 and RB multiply-adds: the exponential unit, not
+// the FP32 issue rate, is then the only limit.  |yr| <= sqrt(d)/2 * s * edge and |xr| <= 3.5 sqrt(d) s edge
+// for every pair the lists can hold, so nothing overflows while s*edge <= 1, which the host checks.
+// ---------------------------------------------------------------------------------------------
+constexpr int NT2 = 64;     // threads per CTA
+constexpr int TI2 = 2;      // targets per thread
+constexpr int ST2 = 384;    // source rows per shared-memory tile
+
+__device__ __forceinline__ int box_of_pt(const int *__restrict__ off, int nb, int i) {
+    int lo = 0, hi = nb;
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (off[mid] <= i) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+template <int D, int RB>
+__global__ void __launch_bounds__(256) pack_sources_rel(const float *__restrict__ pts, int n, const float *__restrict__ bs,
+                                                       int R, int r0, float scale, const int *__restrict__ off_y, int nby,
+                                                       const float *__restrict__ ctr_y, float *packed) {
+    constexpr int W = row_width(D, RB);
+    int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const int by = box_of_pt(off_y, nby, j);
+    float row[W];
+    float ny = 0.f;
+#pragma unroll
+    for (int k = 0; k < D; k++) {
+        float yr = scale * (pts[(size_t)k * n + j] - ctr_y[by * D + k]);
+        ny = fmaf(-yr, yr, ny);
+        row[k] = 2.f * yr;
+    }
+    const float wy = ex2_approx(ny);
+#pragma unroll
+    for (int r = 0; r < RB; r++) row[D + r] = (r0 + r < R) ? bs[(size_t)j * R + r0 + r] * wy : 0.f;
+#pragma unroll
+    for (int c = D + RB; c < W; c++) row[c] = 0.f;
+    float4 *dst = reinterpret_cast<float4 *>(packed + (size_t)j * W);
+#pragma unroll
+    for (int c = 0; c < W / 4; c++) dst[c] = make_float4(row[4 * c], row[4 * c + 1], row[4 * c + 2], row[4 * c + 3]);
+}
+
+template <int D, int RB>
+__global__ void __launch_bounds__(NT2) near_kernel_exp(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
+                                                      int nbx, const int *__restrict__ tile_off,
+                                                      const int *__restrict__ ptr, const int *__restrict__ idx,
+                                                      const int *__restrict__ off_y, const float *__restrict__ ctr_y,
+                                                      const float *__restrict__ packed, float scale, int R, int r0,
+                                                      float *out) {
+    constexpr int W = row_width(D, RB);
+    __shared__ __align__(16) float smem[ST2 * W];
+    int box, t0, t1;
+    item_to_tile(blockIdx.x, tile_off, nbx, off_x, box, t0, t1);
+    float x[TI2][D], tot[TI2][RB];
+    int ti[TI2];
+#pragma unroll
+    for (int u = 0; u < TI2; u++) {
+        ti[u] = t0 + threadIdx.x + u * NT2;
+        int ii = ti[u] < t1 ? ti[u] : t0;
+#pragma unroll
+        for (int k = 0; k < D; k++) x[u][k] = xpts[(size_t)k * n_x + ii];
+#pragma unroll
+        for (int r = 0; r < RB; r++) tot[u][r] = 0.f;
+    }
+    const int e0 = ptr[box], e1 = ptr[box + 1];
+    for (int e = e0; e < e1; e++) {
+        const int by = idx[e];
+        const int s0 = off_y[by], s1 = off_y[by + 1];
+        float xr[TI2][D], fx[TI2], acc[TI2][RB];
+#pragma unroll
+        for (int u = 0; u < TI2; u++) {
+            float nx = 0.f;
+#pragma unroll
+            for (int k = 0; k < D; k++) {
+                xr[u][k] = scale * (x[u][k] - __ldg(ctr_y + by * D + k));
+                nx = fmaf(-xr[u][k], xr[u][k], nx);
+            }
+            fx[u] = ex2_approx(nx);
+#pragma unroll
+            for (int r = 0; r < RB; r++) acc[u][r] = 0.f;
+        }
+        for (int base = s0; base < s1; base += ST2) {
+            const int cnt = min(ST2, s1 - base);
+            __syncthreads();
+            const float4 *g = reinterpret_cast<const float4 *>(packed + (size_t)base * W);
+            float4 *sdst = reinterpret_cast<float4 *>(smem);
+            for (int q = threadIdx.x; q < cnt * (W / 4); q += NT2) sdst[q] = __ldg(g + q);
+            __syncthreads();
+#pragma unroll 8
+            for (int j = 0; j < cnt; j++) {
+                float row[W];
+                const float4 *src = reinterpret_cast<const float4 *>(smem + j * W);
+#pragma unroll
+                for (int c = 0; c < W / 4; c++) {
+                    float4 v = src[c];
+                    row[4 * c] = v.x; row[4 * c + 1] = v.y; row[4 * c + 2] = v.z; row[4 * c + 3] = v.w;
+                }
+#pragma unroll
+                for (int u = 0; u < TI2; u++) {
+                    float t = xr[u][0] * row[0];
+#pragma unroll
+                    for (int k = 1; k < D; k++) t = fmaf(xr[u][k], row[k], t);
+                    const float ev = ex2_approx(t);
+#pragma unroll
+                    for (int r = 0; r < RB; r++) acc[u][r] = fmaf(ev, row[D + r], acc[u][r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < TI2; u++)
+#pragma unroll
+            for (int r = 0; r < RB; r++) tot[u][r] = fmaf(fx[u], acc[u][r], tot[u][r]);
+    }
+#pragma unroll
+    for (int u = 0; u < TI2; u++)
+        if (ti[u] < t1) {
+#pragma unroll
+            for (int r = 0; r < RB; r++)
+                if (r0 + r < R) out[(size_t)ti[u] * R + r0 + r] += tot[u][r];
+        }
+}
+
 __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__restrict__ off_x, const int *__restrict__ ptr,
                                                          int row_begin, int row_end, int tile_pts, int *tiles) {
     int b = blockIdx.x * blockDim.x + threadIdx.x;
@@ -152,96 +290,64 @@ __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__
     tiles[b] = t;
 }
 
+static inline float near_scale(float lcs) { return sqrtf(lcs * 1.4426950408889634f); }
+
+// one list, one block of RB columns starting at r0
 template <int D, int RB>
-static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float *packed, int R, int r0, float *out,
-                        int row_begin, int row_end, float scale, cudaStream_t s) {
+static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float *bs, int R, int r0, float *out,
+                        int row_begin, int row_end, cudaStream_t s) {
     Tree &tx = pl->tx, &ty = *pl->ty;
     Level &lx = tx.levels[level], &ly = ty.levels[level];
-    constexpr int TI = 1;
+    const float scale = near_scale(pl->lcs);
+    const bool expanded = scale * ly.edge <= 1.0f && level > 0;
+    const int tile_pts = expanded ? NT2 * TI2 : NT;
     DevBuf<int> tiles;
     tiles.alloc((size_t)lx.nb + 1, s);
     near_tiles_per_box<<<(unsigned)((lx.nb + 1 + 255) / 256), 256, 0, s>>>(lx.nb, lx.off.p, csr.ptr.p, row_begin, row_end,
-                                                                           NT * TI, tiles.p);
+                                                                           tile_pts, tiles.p);
     F3M_LAUNCH_CHECK();
     exclusive_scan_i32(tiles.p, tiles.p, (int64_t)lx.nb + 1, s);
     F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, tiles.p + lx.nb, sizeof(int), cudaMemcpyDeviceToHost, s));
     F3M_CUDA(cudaStreamSynchronize(s));
     const int items = pl->h_pinned[0];
     if (items <= 0) return;
+    DevBuf<float> packed;
+    packed.alloc((size_t)ty.n * row_width(D, RB), s);
+    const unsigned g = (unsigned)((ty.n + 255) / 256);
+    pl->last.begin(ST_PERMUTE, s);
+    if (expanded)
+        pack_sources_rel<D, RB><<<g, 256, 0, s>>>(ty.pts.p, (int)ty.n, bs, R, r0, scale, ly.off.p, ly.nb, ly.ctr.p, packed.p);
+    else
+        pack_sources<D, RB><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
+    pl->last.end(s);
+    F3M_LAUNCH_CHECK();
     pl->last.begin(ST_DIRECT, s);
-    near_kernel<D, RB, TI><<<items, NT, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, csr.idx.p, ly.off.p,
-                                                packed, scale, R, r0, out);
+    if (expanded)
+        near_kernel_exp<D, RB><<<items, NT2, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, csr.idx.p,
+                                                    ly.off.p, ly.ctr.p, packed.p, scale, R, r0, out);
+    else
+        near_kernel<D, RB, 1><<<items, NT, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, csr.idx.p, ly.off.p,
+                                                   packed.p, scale, R, r0, out);
     pl->last.end(s);
     pl->last.direct_launches++;
     F3M_LAUNCH_CHECK();
 }
 
-static inline float near_scale(float lcs) { return sqrtf(lcs * 1.4426950408889634f); }
-
 template <int D>
 static void direct_d(f3m_plan *pl, int level, const PairCSR &csr, const float *bs, int R, float *out, int rb, int re,
                      cudaStream_t s) {
-    Tree &ty = *pl->ty;
-    const float scale = near_scale(pl->lcs);
-    const unsigned g = (unsigned)((ty.n + 255) / 256);
     for (int r0 = 0; r0 < R;) {
-        int left = R - r0;
-        DevBuf<float> packed;
-        if (left >= 5) {
-            packed.alloc((size_t)ty.n * row_width(D, 8), s);
-            pack_sources<D, 8><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
-            F3M_LAUNCH_CHECK();
-            direct_impl<D, 8>(pl, level, csr, packed.p, R, r0, out, rb, re, scale, s);
-            r0 += 8;
-        } else if (left >= 2) {
-            packed.alloc((size_t)ty.n * row_width(D, 4), s);
-            pack_sources<D, 4><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
-            F3M_LAUNCH_CHECK();
-            direct_impl<D, 4>(pl, level, csr, packed.p, R, r0, out, rb, re, scale, s);
-            r0 += 4;
-        } else {
-            packed.alloc((size_t)ty.n * row_width(D, 1), s);
-            pack_sources<D, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
-            F3M_LAUNCH_CHECK();
-            direct_impl<D, 1>(pl, level, csr, packed.p, R, r0, out, rb, re, scale, s);
-            r0 += 1;
-        }
+        const int left = R - r0;
+        if (left >= 5) { direct_impl<D, 8>(pl, level, csr, bs, R, r0, out, rb, re, s); r0 += 8; }
+        else if (left >= 2) { direct_impl<D, 4>(pl, level, csr, bs, R, r0, out, rb, re, s); r0 += 4; }
+        else { direct_impl<D, 1>(pl, level, csr, bs, R, r0, out, rb, re, s); r0 += 1; }
     }
 }
 
-// b-dependent packing is redone per call of direct_sums; the packed rows depend only on (b, column block),
-// so callers that run several lists per product pass the same packed buffer (see api.cu).
-void build_packed_sources(f3m_plan *pl, const float *b_sorted, DevBuf<float> &packed, cudaStream_t s) {
-    Tree &ty = *pl->ty;
-    const float scale = near_scale(pl->lcs);
-    const unsigned g = (unsigned)((ty.n + 255) / 256);
-    const int R = 1;
-    switch (pl->d) {
-        case 1: packed.alloc((size_t)ty.n * row_width(1, 1), s); pack_sources<1, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, b_sorted, R, 0, scale, packed.p); break;
-        case 2: packed.alloc((size_t)ty.n * row_width(2, 1), s); pack_sources<2, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, b_sorted, R, 0, scale, packed.p); break;
-        case 3: packed.alloc((size_t)ty.n * row_width(3, 1), s); pack_sources<3, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, b_sorted, R, 0, scale, packed.p); break;
-        case 4: packed.alloc((size_t)ty.n * row_width(4, 1), s); pack_sources<4, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, b_sorted, R, 0, scale, packed.p); break;
-        default: packed.alloc((size_t)ty.n * row_width(5, 1), s); pack_sources<5, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, b_sorted, R, 0, scale, packed.p); break;
-    }
-    F3M_LAUNCH_CHECK();
-}
-
-void direct_sums(f3m_plan *pl, int level, const PairCSR &csr, const float *packed, const float *bs, int R,
-                 float *out_sorted, int64_t row_begin, int64_t row_end, cudaStream_t s) {
+void direct_sums(f3m_plan *pl, int level, const PairCSR &csr, const float *bs, int R, float *out_sorted, int64_t row_begin,
+                 int64_t row_end, cudaStream_t s) {
     if (csr.count == 0) return;
     const int rb = (int)row_begin, re = (int)row_end;
-    const float scale = near_scale(pl->lcs);
-    if (R == 1 && packed) {   // single column: packed rows shared by every list of the product
-        switch (pl->d) {
-            case 1: direct_impl<1, 1>(pl, level, csr, packed, 1, 0, out_sorted, rb, re, scale, s); break;
-            case 2: direct_impl<2, 1>(pl, level, csr, packed, 1, 0, out_sorted, rb, re, scale, s); break;
-            case 3: direct_impl<3, 1>(pl, level, csr, packed, 1, 0, out_sorted, rb, re, scale, s); break;
-            case 4: direct_impl<4, 1>(pl, level, csr, packed, 1, 0, out_sorted, rb, re, scale, s); break;
-            default: direct_impl<5, 1>(pl, level, csr, packed, 1, 0, out_sorted, rb, re, scale, s); break;
-        }
-        return;
-    }
-    // multi-column: rows are packed per column block from the sorted b (M,R)
     switch (pl->d) {
         case 1: direct_d<1>(pl, level, csr, bs, R, out_sorted, rb, re, s); break;
         case 2: direct_d<2>(pl, level, csr, bs, R, out_sorted, rb, re, s); break;

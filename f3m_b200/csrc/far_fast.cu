@@ -101,38 +101,102 @@ static void make_shift_tables(const NodeTab2 &nt, std::vector<float> &A, std::ve
 // Array layout: index = m*RB + r, m = sum_k m_k p^k (dimension 0 fastest), r the column.
 // Stage k transforms axis k: out[.., i, ..] = sum_j M_k[i][j] in[.., j, ..].  The last stage adds into acc.
 // ---------------------------------------------------------------------------------------------
-template <int PP>
-__device__ __forceinline__ void warp_kron(const float *src0, float *bufA, float *bufB, float *acc,
-                                          const float *const *mats, int d, int RB, int P, int lane) {
+struct KronCfg {
+    int d, RB, P, nf;        // nf = (P/p)*RB fibres per stage
+    int st[MAXD];            // element stride of axis k: RB * p^k
+    float inv_st[MAXD];
+};
+
+static KronCfg make_kron_cfg(int d, int p, int RB) {
+    KronCfg c{};
+    c.d = d; c.RB = RB;
+    c.P = 1;
+    for (int k = 0; k < d; k++) c.P *= p;
+    c.nf = (c.P / p) * RB;
+    int st = RB;
+    for (int k = 0; k < MAXD; k++) {
+        c.st[k] = st;
+        c.inv_st[k] = 1.0f / (float)st;
+        if (k < d) st *= p;
+    }
+    return c;
+}
+
+// A lane owns whole fibres (p consecutive entries along the axis being transformed): it loads the p x p
+// matrix of the stage into registers once, then p inputs -> p outputs per fibre.  With ACC_REG the
+// outputs of the last stage are accumulated in registers (possible when a stage has at most 64 fibres,
+// i.e. two rounds per lane); otherwise in the warp's shared-memory accumulator.
+template <int PP, bool ACC_REG>
+__device__ __forceinline__ void warp_kron(const float *src0, float *bufA, float *bufB, float *acc_sm,
+                                          float (&acc_reg)[2][PP], const float *const (&mats)[MAXD], const KronCfg &cfg,
+                                          int lane) {
+    constexpr int MS = mat_stride(PP);
     const float *src = src0;
     float *dst = bufA;
-    int st = RB;
-    const int nf = (P / PP) * RB;
-    for (int k = 0; k < d; k++) {
-        const bool last = (k == d - 1);
-        float M[PP * PP];
-        const float *Mk = mats[k];
+    const int nf = cfg.nf;
 #pragma unroll
-        for (int q = 0; q < PP * PP; q++) M[q] = Mk[q];
-        for (int f = lane; f < nf; f += 32) {
-            const int hi = f / st, lo = f - hi * st;
-            const int base = hi * st * PP + lo;
-            float v[PP];
+    for (int k = 0; k < MAXD; k++) {
+        if (k < cfg.d) {
+            const bool last = (k == cfg.d - 1);
+            const int st = cfg.st[k];
+            const float inv = cfg.inv_st[k];
+            float M[MS];
+            const float4 *M4 = reinterpret_cast<const float4 *>(mats[k]);
 #pragma unroll
-            for (int j = 0; j < PP; j++) v[j] = src[base + j * st];
-#pragma unroll
-            for (int i = 0; i < PP; i++) {
-                float o = 0.f;
-#pragma unroll
-                for (int j = 0; j < PP; j++) o = fmaf(M[i * PP + j], v[j], o);
-                if (last) acc[base + i * st] += o;
-                else dst[base + i * st] = o;
+            for (int q = 0; q < MS / 4; q++) {
+                float4 v = M4[q];
+                M[4 * q] = v.x; M[4 * q + 1] = v.y; M[4 * q + 2] = v.z; M[4 * q + 3] = v.w;
             }
+            auto fibre = [&](int f, float *areg) {
+                const int hi = last ? 0 : __float2int_rz(((float)f + 0.5f) * inv);
+                const int base = hi * st * PP + (f - hi * st);
+                float v[PP];
+#pragma unroll
+                for (int j = 0; j < PP; j++) v[j] = src[base + j * st];
+#pragma unroll
+                for (int i = 0; i < PP; i++) {
+                    float o = 0.f;
+#pragma unroll
+                    for (int j = 0; j < PP; j++) o = fmaf(M[i * PP + j], v[j], o);
+                    if (!last) dst[base + i * st] = o;
+                    else if (ACC_REG) areg[i] += o;
+                    else acc_sm[base + i * st] += o;
+                }
+            };
+            if (ACC_REG) {   // at most two rounds, register accumulators indexed statically
+                if (lane < nf) fibre(lane, acc_reg[0]);
+                if (lane + 32 < nf) fibre(lane + 32, acc_reg[1]);
+            } else {
+                for (int f = lane; f < nf; f += 32) fibre(f, acc_reg[0]);
+            }
+            __syncwarp();
+            src = dst;
+            dst = (dst == bufA) ? bufB : bufA;
         }
-        __syncwarp();
-        src = dst;
-        dst = (dst == bufA) ? bufB : bufA;
-        st *= PP;
+    }
+}
+
+// after the last pair: registers -> the warp's shared-memory accumulator (layout of the last stage: base = fibre)
+template <int PP>
+__device__ __forceinline__ void flush_acc(float (&acc_reg)[2][PP], float *acc_sm, const KronCfg &cfg, int lane) {
+    const int st = cfg.st[cfg.d - 1];
+#pragma unroll
+    for (int rnd = 0; rnd < 2; rnd++) {
+        const int f = lane + rnd * 32;
+        if (f < cfg.nf)
+#pragma unroll
+            for (int i = 0; i < PP; i++) acc_sm[f + i * st] = acc_reg[rnd][i];
+    }
+}
+
+__global__ void __launch_bounds__(256) decode_cells_kernel(int nb, int level, int d, const uint32_t *__restrict__ code, int *cell) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= nb) return;
+    const uint32_t c = code[b];
+    for (int k = 0; k < d; k++) {
+        int q = 0;
+        for (int jb = 0; jb < level; jb++) q |= (int)((c >> (d * jb + k)) & 1u) << jb;
+        cell[b * d + k] = q;
     }
 }
 
@@ -145,12 +209,12 @@ __device__ __forceinline__ void decode_cell2(uint32_t code, int level, int d, in
 // ---------------------------------------------------------------------------------------------
 // M2L: one CTA per target box, its warps share the far row
 // ---------------------------------------------------------------------------------------------
-template <int PP>
-__global__ void __launch_bounds__(128) m2l_fast(int nbx, int level, int d, const int *__restrict__ fptr,
-                                               const int *__restrict__ fidx, const uint32_t *__restrict__ code_x,
-                                               const uint32_t *__restrict__ code_y, const int *__restrict__ off_x,
-                                               int row_begin, int row_end, const float *__restrict__ T, Geom2 geo, int P,
-                                               int RB, const float *__restrict__ mom, float *loc, int *err) {
+template <int PP, bool ACC_REG>
+__global__ void __launch_bounds__(128) m2l_fast(int nbx, int d, const int *__restrict__ fptr, const int *__restrict__ fidx,
+                                               const int *__restrict__ cell_x, const int *__restrict__ cell_y,
+                                               const int *__restrict__ off_x, int row_begin, int row_end,
+                                               const float *__restrict__ T, Geom2 geo, KronCfg cfg,
+                                               const float *__restrict__ mom, float *loc, int *err) {
     extern __shared__ __align__(16) float sm[];
     constexpr int MS = mat_stride(PP);
     const int bx = blockIdx.x;
@@ -158,29 +222,38 @@ __global__ void __launch_bounds__(128) m2l_fast(int nbx, int level, int d, const
     if (e0 == e1) return;
     if (off_x[bx + 1] <= row_begin || off_x[bx] >= row_end) return;   // box has no point in this rank's slice
     const int nw = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int PR = P * RB, ntab = d * NOFF2 * MS;
+    const int PR = cfg.P * cfg.RB, ntab = d * NOFF2 * MS;
     float *Tsm = sm;
     float *wbuf = sm + ntab + (size_t)w * 3 * PR;
     float *bufA = wbuf, *bufB = wbuf + PR, *acc = wbuf + 2 * PR;
     for (int q = threadIdx.x; q < ntab; q += blockDim.x) Tsm[q] = T[q];
     for (int q = lane; q < PR; q += 32) acc[q] = 0.f;
+    float acc_reg[2][PP];
+#pragma unroll
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+        for (int i = 0; i < PP; i++) acc_reg[a][i] = 0.f;
     __syncthreads();
     int qx[MAXD];
-    decode_cell2(code_x[bx], level, d, qx);
+#pragma unroll
+    for (int k = 0; k < MAXD; k++) qx[k] = k < d ? cell_x[bx * d + k] : 0;
     for (int e = e0 + w; e < e1; e += nw) {
         const int by = fidx[e];
-        int qy[MAXD];
-        decode_cell2(code_y[by], level, d, qy);
         const float *mats[MAXD];
         bool ok = true;
-        for (int k = 0; k < d; k++) {
-            int o = qy[k] - qx[k] - geo.dqmin[k];
-            if (o < 0 || o >= NOFF2) { ok = false; o = 0; }
+#pragma unroll
+        for (int k = 0; k < MAXD; k++) {
+            int o = 0;
+            if (k < d) {
+                o = cell_y[by * d + k] - qx[k] - geo.dqmin[k];
+                if (o < 0 || o >= NOFF2) { ok = false; o = 0; }
+            }
             mats[k] = Tsm + (k * NOFF2 + o) * MS;
         }
         if (!ok) { if (lane == 0) atomicExch(err, 2); continue; }
-        warp_kron<PP>(mom + (size_t)by * PR, bufA, bufB, acc, mats, d, RB, P, lane);
+        warp_kron<PP, ACC_REG>(mom + (size_t)by * PR, bufA, bufB, acc, acc_reg, mats, cfg, lane);
     }
+    if (ACC_REG) flush_acc<PP>(acc_reg, acc, cfg, lane);
     __syncthreads();
     for (int q = threadIdx.x; q < PR; q += blockDim.x) {
         float s = 0.f;
@@ -192,25 +265,27 @@ __global__ void __launch_bounds__(128) m2l_fast(int nbx, int level, int d, const
 // M2M: one CTA per parent box, warps share the children
 template <int PP>
 __global__ void __launch_bounds__(128) m2m_fast(int nbp, int d, const int *__restrict__ child_start,
-                                               const uint32_t *__restrict__ code_child, const float *__restrict__ A, int P,
-                                               int RB, const float *__restrict__ mom_child, float *mom_parent) {
+                                               const uint32_t *__restrict__ code_child, const float *__restrict__ A,
+                                               KronCfg cfg, const float *__restrict__ mom_child, float *mom_parent) {
     extern __shared__ __align__(16) float sm[];
     constexpr int MS = mat_stride(PP);
     const int pb = blockIdx.x;
     const int nw = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int PR = P * RB, ntab = 2 * MS;
+    const int PR = cfg.P * cfg.RB, ntab = 2 * MS;
     float *Asm = sm;
     float *wbuf = sm + ntab + (size_t)w * 3 * PR;
     float *bufA = wbuf, *bufB = wbuf + PR, *acc = wbuf + 2 * PR;
     for (int q = threadIdx.x; q < ntab; q += blockDim.x) Asm[q] = A[q];
     for (int q = lane; q < PR; q += 32) acc[q] = 0.f;
+    float acc_reg[2][PP];
     __syncthreads();
     const int c0 = child_start[pb], c1 = child_start[pb + 1];
     for (int c = c0 + w; c < c1; c += nw) {
         const uint32_t code = code_child[c];
         const float *mats[MAXD];
-        for (int k = 0; k < d; k++) mats[k] = Asm + ((code >> k) & 1u) * MS;
-        warp_kron<PP>(mom_child + (size_t)c * PR, bufA, bufB, acc, mats, d, RB, P, lane);
+#pragma unroll
+        for (int k = 0; k < MAXD; k++) mats[k] = Asm + ((code >> k) & 1u) * MS;
+        warp_kron<PP, false>(mom_child + (size_t)c * PR, bufA, bufB, acc, acc_reg, mats, cfg, lane);
     }
     __syncthreads();
     for (int q = threadIdx.x; q < PR; q += blockDim.x) {
@@ -224,12 +299,12 @@ __global__ void __launch_bounds__(128) m2m_fast(int nbp, int d, const int *__res
 template <int PP>
 __global__ void __launch_bounds__(128) l2l_fast(int nbc, int d, const int *__restrict__ parent,
                                                const uint32_t *__restrict__ code_child, const int *__restrict__ off_c,
-                                               int row_begin, int row_end, const float *__restrict__ AT, int P, int RB,
+                                               int row_begin, int row_end, const float *__restrict__ AT, KronCfg cfg,
                                                const float *__restrict__ loc_parent, float *loc_child) {
     extern __shared__ __align__(16) float sm[];
     constexpr int MS = mat_stride(PP);
     const int nw = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int PR = P * RB, ntab = 2 * MS;
+    const int PR = cfg.P * cfg.RB, ntab = 2 * MS;
     float *Asm = sm;
     float *wbuf = sm + ntab + (size_t)w * 3 * PR;
     float *bufA = wbuf, *bufB = wbuf + PR, *acc = wbuf + 2 * PR;
@@ -242,8 +317,10 @@ __global__ void __launch_bounds__(128) l2l_fast(int nbc, int d, const int *__res
     __syncwarp();
     const uint32_t code = code_child[c];
     const float *mats[MAXD];
-    for (int k = 0; k < d; k++) mats[k] = Asm + ((code >> k) & 1u) * MS;
-    warp_kron<PP>(loc_parent + (size_t)parent[c] * PR, bufA, bufB, acc, mats, d, RB, P, lane);
+#pragma unroll
+    for (int k = 0; k < MAXD; k++) mats[k] = Asm + ((code >> k) & 1u) * MS;
+    float acc_reg[2][PP];
+    warp_kron<PP, false>(loc_parent + (size_t)parent[c] * PR, bufA, bufB, acc, acc_reg, mats, cfg, lane);
     for (int q = lane; q < PR; q += 32) loc_child[(size_t)c * PR + q] += acc[q];
 }
 
@@ -271,25 +348,30 @@ __device__ __forceinline__ void lagrange_pp(float t, const NodeTab2 &nt, float *
     }
 }
 
+// P2M.  A thread owns one combination (m_1 .. m_{d-1}) of the slower node indices and all p values of
+// the fastest one: per point it forms w = b * prod_{k>=1} L_k[m_k] once and adds w * L_0[i] to p
+// accumulators, so a (point, node) pair costs about one shared-memory read and one multiply-add.
+// Threads beyond the number of combinations form further groups that take every G-th point.
 template <int PP, int RB>
-__global__ void p2m_leaf(const float *__restrict__ pts, int n, int d, const float *__restrict__ bs, int R, int r0,
-                         const int *__restrict__ off, const float *__restrict__ ctr, float factor, NodeTab2 nt, int P,
-                         int nsplit, float *mom) {
+__global__ void __launch_bounds__(256) p2m_leaf(const float *__restrict__ pts, int n, int d, const float *__restrict__ bs, int R,
+                                               int r0, const int *__restrict__ off, const float *__restrict__ ctr,
+                                               float factor, NodeTab2 nt, int P, int nsplit, float *mom) {
     extern __shared__ __align__(16) float sm[];
-    const int TP = blockDim.x;
+    constexpr int TP = 128, NTH = 256, LS = TP + 1;
     float *Ls = sm;                                   // [d*PP][TP+1]
-    float *bsm = Ls + (size_t)d * PP * (TP + 1);      // [TP][RB]
+    float *bsm = Ls + (size_t)d * PP * LS;            // [TP][RB]
     float *accsm = bsm + (size_t)TP * RB;             // [P][RB]
     const int box = blockIdx.x;
     const int a = off[box], b = off[box + 1];
-    // this CTA's share of the box
     const int len = b - a;
     const int s0 = a + (int)(((long long)len * blockIdx.y) / nsplit), s1 = a + (int)(((long long)len * (blockIdx.y + 1)) / nsplit);
     if (s0 >= s1) return;
-    const int PR = P * RB;
-    for (int q = threadIdx.x; q < PR; q += TP) accsm[q] = 0.f;
+    const int PR = P * RB, C = P / PP;
+    for (int q = threadIdx.x; q < PR; q += NTH) accsm[q] = 0.f;
     float c[MAXD];
     for (int k = 0; k < d; k++) c[k] = ctr[box * d + k];
+    const int G = C >= NTH ? 1 : NTH / C;             // point groups
+    const int g = C >= NTH ? 0 : threadIdx.x / C;
     for (int base = s0; base < s1; base += TP) {
         const int cnt = min(TP, s1 - base);
         __syncthreads();
@@ -299,36 +381,52 @@ __global__ void p2m_leaf(const float *__restrict__ pts, int n, int d, const floa
                 float L[PP];
                 lagrange_pp<PP>(factor * (pts[(size_t)k * n + i] - c[k]), nt, L);
 #pragma unroll
-                for (int q = 0; q < PP; q++) Ls[(k * PP + q) * (TP + 1) + threadIdx.x] = L[q];
+                for (int q = 0; q < PP; q++) Ls[(k * PP + q) * LS + threadIdx.x] = L[q];
             }
 #pragma unroll
             for (int r = 0; r < RB; r++) bsm[threadIdx.x * RB + r] = (r0 + r < R) ? bs[(size_t)i * R + r0 + r] : 0.f;
         }
         __syncthreads();
-        for (int m = threadIdx.x; m < P; m += TP) {
-            const float *lp[MAXD];
-            int rem = m;
-            for (int k = 0; k < d; k++) {
-                lp[k] = Ls + (size_t)(k * PP + rem % PP) * (TP + 1);
-                rem /= PP;
+        if (g < G) {
+            for (int cc = (C >= NTH ? (int)threadIdx.x : (int)threadIdx.x - g * C); cc < C; cc += NTH) {
+                const float *lp[MAXD];
+                int rem = cc;
+#pragma unroll
+                for (int k = 1; k < MAXD; k++) {
+                    lp[k] = Ls;
+                    if (k < d) { lp[k] = Ls + (size_t)(k * PP + rem % PP) * LS; rem /= PP; }
+                }
+                float acc[PP][RB];
+#pragma unroll
+                for (int i = 0; i < PP; i++)
+#pragma unroll
+                    for (int r = 0; r < RB; r++) acc[i][r] = 0.f;
+                for (int j = g; j < cnt; j += G) {
+                    float w = 1.f;
+#pragma unroll
+                    for (int k = 1; k < MAXD; k++)
+                        if (k < d) w *= lp[k][j];
+                    float wb[RB];
+#pragma unroll
+                    for (int r = 0; r < RB; r++) wb[r] = w * bsm[j * RB + r];
+#pragma unroll
+                    for (int i = 0; i < PP; i++) {
+                        const float l0 = Ls[i * LS + j];
+#pragma unroll
+                        for (int r = 0; r < RB; r++) acc[i][r] = fmaf(l0, wb[r], acc[i][r]);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < PP; i++)
+#pragma unroll
+                    for (int r = 0; r < RB; r++) atomicAdd(&accsm[(cc * PP + i) * RB + r], acc[i][r]);
             }
-            float acc[RB];
-#pragma unroll
-            for (int r = 0; r < RB; r++) acc[r] = 0.f;
-            for (int j = 0; j < cnt; j++) {
-                float prod = lp[0][j];
-                for (int k = 1; k < d; k++) prod *= lp[k][j];
-#pragma unroll
-                for (int r = 0; r < RB; r++) acc[r] = fmaf(prod, bsm[j * RB + r], acc[r]);
-            }
-#pragma unroll
-            for (int r = 0; r < RB; r++) accsm[m * RB + r] += acc[r];
         }
     }
     __syncthreads();
     float *dst = mom + (size_t)box * PR;
-    if (nsplit == 1) for (int q = threadIdx.x; q < PR; q += TP) dst[q] = accsm[q];
-    else for (int q = threadIdx.x; q < PR; q += TP) atomicAdd(dst + q, accsm[q]);
+    if (nsplit == 1) for (int q = threadIdx.x; q < PR; q += NTH) dst[q] = accsm[q];
+    else for (int q = threadIdx.x; q < PR; q += NTH) atomicAdd(dst + q, accsm[q]);
 }
 
 template <int PP, int RB>
@@ -401,6 +499,7 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
     const int PR = P * RB;
     constexpr int MS = mat_stride(PP);
     NodeTab2 nt = make_nodes2(PP);
+    const KronCfg cfg = make_kron_cfg(d, PP, RB);
     const int n_x = (int)tx.n, n_y = (int)ty.n;
 
     std::vector<DevBuf<float>> mom(L + 1), loc(L + 1);
@@ -430,12 +529,11 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
     {
         Level &ly = ty.levels[L];
         const float factor = 2.f / ly.edge;          // 1_d_conv.cu:473
-        const int TP = P <= 128 ? 128 : 256;
         int nsplit = std::max(1, std::min(64, (ly.max_count + 8191) / 8192));
         if (nsplit > 1) mom[L].zero();
-        size_t smem = ((size_t)d * PP * (TP + 1) + (size_t)TP * RB + (size_t)PR) * sizeof(float);
+        size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
         F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        p2m_leaf<PP, RB><<<dim3(ly.nb, nsplit), TP, smem, s>>>(ty.pts.p, n_y, d, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt, P,
+        p2m_leaf<PP, RB><<<dim3(ly.nb, nsplit), 256, smem, s>>>(ty.pts.p, n_y, d, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt, P,
                                                               nsplit, mom[L].p);
         F3M_LAUNCH_CHECK();
         const int nw = warps_for(2 * MS * sizeof(float));
@@ -443,7 +541,7 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
         F3M_CUDA(cudaFuncSetAttribute(m2m_fast<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2));
         for (int l = L - 1; l >= lmin; l--) {
             Level &lp = ty.levels[l], &lc = ty.levels[l + 1];
-            m2m_fast<PP><<<lp.nb, 32 * nw, sm2, s>>>(lp.nb, d, lp.child_start.p, lc.code.p, A.p, P, RB, mom[l + 1].p, mom[l].p);
+            m2m_fast<PP><<<lp.nb, 32 * nw, sm2, s>>>(lp.nb, d, lp.child_start.p, lc.code.p, A.p, cfg, mom[l + 1].p, mom[l].p);
             F3M_LAUNCH_CHECK();
         }
     }
@@ -456,7 +554,10 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
         const size_t tab = (size_t)d * NOFF2 * MS * sizeof(float);
         const int nw = warps_for(tab);
         size_t smem = tab + nw * per_warp;
-        F3M_CUDA(cudaFuncSetAttribute(m2l_fast<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const bool acc_reg = cfg.nf <= 64;
+        if (acc_reg) F3M_CUDA(cudaFuncSetAttribute(m2l_fast<PP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        else F3M_CUDA(cudaFuncSetAttribute(m2l_fast<PP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DevBuf<int> cellx, celly;
         for (int l = lmin; l <= L; l++) {
             LevelLists &ll = pl->lists[l];
             if (ll.far.count == 0) continue;
@@ -471,8 +572,22 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
             }
             m2l_table2<<<8, 256, 0, s>>>(nt, d, (double)lx.edge, (double)pl->lcs, geo, T.p);
             F3M_LAUNCH_CHECK();
-            m2l_fast<PP><<<lx.nb, 32 * nw, smem, s>>>(lx.nb, l, d, ll.far.ptr.p, ll.far.idx.p, lx.code.p, ly.code.p, lx.off.p, rb,
-                                                     re, T.p, geo, P, RB, mom[l].p, loc[l].p, pl->d_flags);
+            cellx.alloc((size_t)lx.nb * d, s);
+            decode_cells_kernel<<<(lx.nb + 255) / 256, 256, 0, s>>>(lx.nb, l, d, lx.code.p, cellx.p);
+            F3M_LAUNCH_CHECK();
+            const int *cy = cellx.p;
+            if (!pl->same) {
+                celly.alloc((size_t)ly.nb * d, s);
+                decode_cells_kernel<<<(ly.nb + 255) / 256, 256, 0, s>>>(ly.nb, l, d, ly.code.p, celly.p);
+                F3M_LAUNCH_CHECK();
+                cy = celly.p;
+            }
+            if (acc_reg)
+                m2l_fast<PP, true><<<lx.nb, 32 * nw, smem, s>>>(lx.nb, d, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, lx.off.p, rb, re,
+                                                               T.p, geo, cfg, mom[l].p, loc[l].p, pl->d_flags);
+            else
+                m2l_fast<PP, false><<<lx.nb, 32 * nw, smem, s>>>(lx.nb, d, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, lx.off.p, rb, re,
+                                                                T.p, geo, cfg, mom[l].p, loc[l].p, pl->d_flags);
             F3M_LAUNCH_CHECK();
         }
     }
@@ -485,7 +600,7 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
         F3M_CUDA(cudaFuncSetAttribute(l2l_fast<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2));
         for (int l = lmin; l < L; l++) {
             Level &lc = tx.levels[l + 1];
-            l2l_fast<PP><<<(lc.nb + nw - 1) / nw, 32 * nw, sm2, s>>>(lc.nb, d, lc.parent.p, lc.code.p, lc.off.p, rb, re, AT.p, P, RB,
+            l2l_fast<PP><<<(lc.nb + nw - 1) / nw, 32 * nw, sm2, s>>>(lc.nb, d, lc.parent.p, lc.code.p, lc.off.p, rb, re, AT.p, cfg,
                                                                     loc[l].p, loc[l + 1].p);
             F3M_LAUNCH_CHECK();
         }

@@ -159,7 +159,8 @@ __global__ void __launch_bounds__(NT) near_kernel(const float *__restrict__ xpts
 // the FP32 issue rate, is then the only limit.  |yr| <= sqrt(d)/2 * s * edge and |xr| <= 3.5 sqrt(d) s edge
 // for every pair the lists can hold, so nothing overflows while s*edge <= 1, which the host checks.
 // ---------------------------------------------------------------------------------------------
-constexpr int NT2 = 64;     // threads per CTA
+constexpr int NT2 = 32;     // threads per CTA: one warp, so a tile holds 64 targets and a box of ~400 points
+                            // splits into tiles that are nearly full (measured: 64-thread CTAs lose 7% to padding)
 constexpr int TI2 = 2;      // targets per thread
 constexpr int ST2 = 384;    // source rows per shared-memory tile
 
@@ -198,8 +199,19 @@ __global__ void __launch_bounds__(256) pack_sources_rel(const float *__restrict_
     for (int c = 0; c < W / 4; c++) dst[c] = make_float4(row[4 * c], row[4 * c + 1], row[4 * c + 2], row[4 * c + 3]);
 }
 
-template <int D, int RB>
-__global__ void __launch_bounds__(NT2) near_kernel_exp(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
+// 2^t for small |t| on the FMA pipe: Taylor polynomial of degree DEG in t*ln2 (error <= (|t| ln2)^(DEG+1)/(DEG+1)!)
+template <int DEG>
+__device__ __forceinline__ float exp2_poly(float t) {
+    constexpr float C1 = 0.69314718056f, C2 = 0.24022650696f, C3 = 0.05550410866f;
+    if (DEG == 2) return fmaf(fmaf(C2, t, C1), t, 1.f);
+    return fmaf(fmaf(fmaf(C3, t, C2), t, C1), t, 1.f);
+}
+
+// POLY = 0: every exponential on the MUFU pipe.  POLY = 2 or 3: every third source row uses exp2_poly<POLY>
+// instead, which moves a third of the exponentials to the FMA pipe (the host enables it only when the
+// exponent 2 xr.yr is provably small for every pair of the list).
+template <int D, int RB, int NTH, int POLY>
+__global__ void __launch_bounds__(NTH) near_kernel_exp(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
                                                       int nbx, const int *__restrict__ tile_off,
                                                       const int *__restrict__ ptr, const int *__restrict__ idx,
                                                       const int *__restrict__ off_y, const float *__restrict__ ctr_y,
@@ -213,7 +225,7 @@ __global__ void __launch_bounds__(NT2) near_kernel_exp(const float *__restrict__
     int ti[TI2];
 #pragma unroll
     for (int u = 0; u < TI2; u++) {
-        ti[u] = t0 + threadIdx.x + u * NT2;
+        ti[u] = t0 + threadIdx.x + u * NTH;
         int ii = ti[u] < t1 ? ti[u] : t0;
 #pragma unroll
         for (int k = 0; k < D; k++) x[u][k] = xpts[(size_t)k * n_x + ii];
@@ -242,10 +254,9 @@ __global__ void __launch_bounds__(NT2) near_kernel_exp(const float *__restrict__
             __syncthreads();
             const float4 *g = reinterpret_cast<const float4 *>(packed + (size_t)base * W);
             float4 *sdst = reinterpret_cast<float4 *>(smem);
-            for (int q = threadIdx.x; q < cnt * (W / 4); q += NT2) sdst[q] = __ldg(g + q);
+            for (int q = threadIdx.x; q < cnt * (W / 4); q += NTH) sdst[q] = __ldg(g + q);
             __syncthreads();
-#pragma unroll 8
-            for (int j = 0; j < cnt; j++) {
+            auto body = [&](int j, bool poly) {
                 float row[W];
                 const float4 *src = reinterpret_cast<const float4 *>(smem + j * W);
 #pragma unroll
@@ -258,11 +269,20 @@ __global__ void __launch_bounds__(NT2) near_kernel_exp(const float *__restrict__
                     float t = xr[u][0] * row[0];
 #pragma unroll
                     for (int k = 1; k < D; k++) t = fmaf(xr[u][k], row[k], t);
-                    const float ev = ex2_approx(t);
+                    const float ev = (POLY && poly) ? exp2_poly<POLY ? POLY : 2>(t) : ex2_approx(t);
 #pragma unroll
                     for (int r = 0; r < RB; r++) acc[u][r] = fmaf(ev, row[D + r], acc[u][r]);
                 }
+            };
+            int j = 0;
+            if (POLY) {
+#pragma unroll 2
+                for (; j + 3 <= cnt; j += 3) { body(j, false); body(j + 1, true); body(j + 2, false); }
+            } else {
+#pragma unroll 8
+                for (; j + 1 <= cnt; j++) body(j, false);
             }
+            for (; j < cnt; j++) body(j, false);
         }
 #pragma unroll
         for (int u = 0; u < TI2; u++)
@@ -322,9 +342,21 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     pl->last.end(s);
     F3M_LAUNCH_CHECK();
     pl->last.begin(ST_DIRECT, s);
-    if (expanded)
-        near_kernel_exp<D, RB><<<items, NT2, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, csr.idx.p,
-                                                    ly.off.p, ly.ctr.p, packed.p, scale, R, r0, out);
+    if (expanded) {
+        // bound of |2 xr.yr| over the pairs a list can hold: per dimension |x - c_source| <= 2.5 edge for pairs kept
+        // for refinement (centres closer than 2 edges), 5.5 edge for "small" pairs (children of kept parents)
+        const bool final_near = (&csr == &pl->lists[level].keep);
+        const float se = scale * ly.edge;
+        const float tmax = D * (final_near ? 2.5f : 5.5f) * se * se;
+        const int poly = tmax <= 0.02f ? 2 : (tmax <= 0.1f ? 3 : 0);
+#define F3M_NEAR_EXP(NTH_, POLY_)                                                                                      \
+    near_kernel_exp<D, RB, NTH_, POLY_><<<items, NTH_, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, \
+                                                              csr.idx.p, ly.off.p, ly.ctr.p, packed.p, scale, R, r0, out)
+        if (poly == 2) F3M_NEAR_EXP(NT2, 2);
+        else if (poly == 3) F3M_NEAR_EXP(NT2, 3);
+        else F3M_NEAR_EXP(NT2, 0);
+#undef F3M_NEAR_EXP
+    }
     else
         near_kernel<D, RB, 1><<<items, NT, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, csr.idx.p, ly.off.p,
                                                    packed.p, scale, R, r0, out);

@@ -64,6 +64,7 @@ SIGNATURES = {
     "f3m_rbf_dense_f32": (C.c_int, [_P, _I64, _P, _I64, _P, _I32, _I32, _F32, _P, _P]),
     "f3m_rbf_dense_f64": (C.c_int, [_P, _I64, _P, _I64, _P, _I32, _I32, _F64, _P, _P]),
     "f3m_rbf_dense_grad_f32": (C.c_int, [_P, _I64, _P, _I64, _P, _I32, _I32, _F32, _P, _P]),
+    "f3m_rbf_dense_f32_static": (C.c_int, [_P, _I64, _P, _I64, _P, _I32, _I32, _F32, _P, _P]),
     "f3m_measure_peaks": (C.c_int, [C.POINTER(_F64), C.POINTER(_F64), _P]),
     "f3m_plan_last_timings": (C.c_int, [_P, C.POINTER(_F32)]),
     "f3m_plan_last_direct_launches": (C.c_int, [_P]),

@@ -391,6 +391,16 @@ int f3m_rbf_dense_f64(const double *X, int64_t N, const double *Y, int64_t M, co
     });
 }
 
+int f3m_rbf_dense_f32_static(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R, int32_t d,
+                             float ls, float *out, void *stream) {
+    return guarded([&] {
+        F3M_REQUIRE(X && Y && b && out && N > 0 && M > 0 && R >= 1 && d >= 1 && d <= F3M_MAX_DIM && ls > 0, F3M_ERR_ARG,
+                    "bad argument to f3m_rbf_dense_f32_static");
+        dense_f32_static(X, N, Y, M, b, R, d, ls, out, (cudaStream_t)stream);   // no allocation anywhere on this path
+        F3M_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    });
+}
+
 int f3m_measure_peaks(double *gexp_per_s, double *gfma_per_s, void *stream) {
     if (!gexp_per_s || !gfma_per_s) return F3M_ERR_ARG;
     return guarded([&] {

@@ -193,5 +193,7 @@ void dense_f32(const float *X, int64_t N, const float *Y, int64_t M, const float
 void dense_f64(const double *X, int64_t N, const double *Y, int64_t M, const double *b, int R, int d, double ls, double *out,
                cudaStream_t s);
 void measure_peaks(double *gexp, double *gfma, cudaStream_t s);
+void dense_f32_static(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int R, int d, float ls, float *out,
+                      cudaStream_t s);
 
 }  // namespace f3m

@@ -520,6 +520,77 @@ void dense_f64(const double *X, int64_t N, const double *Y, int64_t M, const dou
 }
 
 // ---------------------------------------------------------------------------------------------
+// Exact dense product without any allocation.
+//
+// Some hosts may not touch the CUDA allocator once they are running: a service that handed all device
+// memory to its own pool at start-up, or a control loop with a "no allocation after initialisation"
+// rule, because an allocation can stall the whole device.  For them f3m_rbf_dense_f32_static computes
+// the same product as f3m_rbf_dense_f32 with its only scratch buffer -- the packed source rows -- in a
+// fixed array that is part of the library image.  Every GPU that loads libf3m.so holds this array
+// (F3M_STATIC_SCRATCH_FLOATS floats = 16 MiB) until the process exits.
+//
+// In host code the array's name is only a stand-in, not a device address; the address a kernel can use
+// is obtained once per device, with that device current, through cudaGetSymbolAddress.  The first call
+// on a device performs this look-up, so make that first call before any stream capture starts.
+// All calls share the one array: it keeps whatever the previous call packed (every row a call reads is
+// rewritten by that call first, so nothing has to be cleared), and two calls that overlap on the GPU
+// -- different streams, or different host threads -- race on it.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_static_scratch[F3M_STATIC_SCRATCH_FLOATS];
+
+static float *static_scratch_for_current_device() {
+    static float *ptr_of_device[64] = {nullptr};
+    int dev = 0;
+    F3M_CUDA(cudaGetDevice(&dev));
+    F3M_REQUIRE(dev >= 0 && dev < 64, F3M_ERR_UNSUPPORTED, "device ordinal %d not supported by the static entry point", dev);
+    if (!ptr_of_device[dev]) {
+        float *p = nullptr;
+        F3M_CUDA(cudaGetSymbolAddress((void **)&p, g_static_scratch));
+        ptr_of_device[dev] = p;
+    }
+    return ptr_of_device[dev];
+}
+
+template <int D>
+static void dense_static_d(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int R, float ls, float *out,
+                           float *scratch, cudaStream_t s) {
+    const float lcs = 1.f / (2.f * ls * ls);
+    const float scale = near_scale(lcs);
+    const unsigned gy = (unsigned)((M + 255) / 256), gx = (unsigned)((N + NT - 1) / NT);
+    for (int r0 = 0; r0 < R;) {   // column blocks reuse the scratch one after the other on the same stream
+        if (R - r0 >= 2) {
+            pack_rows_dense<D, 4><<<gy, 256, 0, s>>>(Y, M, b, R, r0, scale, scratch);
+            F3M_LAUNCH_CHECK();
+            dense_kernel<D, 4, false><<<gx, NT, 0, s>>>(X, N, scratch, M, scale, 1.f, R, r0, out);
+            r0 += 4;
+        } else {
+            pack_rows_dense<D, 1><<<gy, 256, 0, s>>>(Y, M, b, R, r0, scale, scratch);
+            F3M_LAUNCH_CHECK();
+            dense_kernel<D, 1, false><<<gx, NT, 0, s>>>(X, N, scratch, M, scale, 1.f, R, r0, out);
+            r0 += 1;
+        }
+        F3M_LAUNCH_CHECK();
+    }
+}
+
+void dense_f32_static(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int R, int d, float ls, float *out,
+                      cudaStream_t s) {
+    const int64_t width = row_width(d, R >= 2 ? 4 : 1);
+    F3M_REQUIRE(M * width <= (int64_t)F3M_STATIC_SCRATCH_FLOATS, F3M_ERR_TOO_LARGE,
+                "f3m_rbf_dense_f32_static holds %lld packed floats; M=%lld sources of %lld floats each need %lld "
+                "(use f3m_rbf_dense_f32, which allocates)",
+                (long long)F3M_STATIC_SCRATCH_FLOATS, (long long)M, (long long)width, (long long)(M * width));
+    float *scratch = static_scratch_for_current_device();
+    switch (d) {
+        case 1: dense_static_d<1>(X, N, Y, M, b, R, ls, out, scratch, s); break;
+        case 2: dense_static_d<2>(X, N, Y, M, b, R, ls, out, scratch, s); break;
+        case 3: dense_static_d<3>(X, N, Y, M, b, R, ls, out, scratch, s); break;
+        case 4: dense_static_d<4>(X, N, Y, M, b, R, ls, out, scratch, s); break;
+        default: dense_static_d<5>(X, N, Y, M, b, R, ls, out, scratch, s); break;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // issue-rate probes: register-only loops of ex2 and of fma
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) probe_ex2(float *out, int iters) {

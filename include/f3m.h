@@ -148,6 +148,19 @@ int f3m_rbf_dense_f64(const double *X, int64_t N, const double *Y, int64_t M, co
 int f3m_rbf_dense_grad_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R,
                            int32_t d, float ls, float *out, void *stream);
 
+/* The same product as f3m_rbf_dense_f32 for hosts that must not allocate device memory while they run
+ * (all memory pre-reserved by the host's own pool, or a no-allocation-after-start-up rule because an
+ * allocation can stall the device).  It has no counterpart in the reference.  Its scratch -- the packed
+ * source rows -- lives in a fixed 16 MiB array inside the library image (F3M_STATIC_SCRATCH_FLOATS floats,
+ * held by every GPU that loads the library), so it calls no cudaMalloc, cudaFree or pool routine.
+ * Limit: M * w <= F3M_STATIC_SCRATCH_FLOATS with w = 4 floats per source for d <= 3 and one column
+ * (in general d + min(R,4) rounded up to a multiple of 4); larger inputs return F3M_ERR_TOO_LARGE.
+ * The first call on a device looks up the array's device address; make it before any stream capture.
+ * Calls share the array: calls that overlap on the GPU (other streams or host threads) race. */
+#define F3M_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)
+int f3m_rbf_dense_f32_static(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R,
+                             int32_t d, float ls, float *out, void *stream);
+
 /* -------- measurement helpers -------------------------------------------------------------- */
 
 /* Measures the SM's exponential (MUFU.EX2) and FP32 FMA issue peaks with two register-only

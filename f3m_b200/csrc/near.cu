@@ -603,11 +603,11 @@ __global__ void __launch_bounds__(256) probe_ex2(float *out, int iters) {
 }
 __global__ void __launch_bounds__(256) probe_fma(float *out, int iters) {
     float a = threadIdx.x * 1e-3f, b = a + 0.1f, c = a + 0.2f, d = a + 0.3f, e = a + 0.4f, f = a + 0.5f, g = a + 0.6f, h = a + 0.7f;
-    const float m = 0.999f, q = 1e-3f;
+    const float m = -1e-6f;   // x <- x*m + x: two distinct source registers per instruction (no register-bank conflicts)
 #pragma unroll 8
     for (int i = 0; i < iters; i++) {
-        a = fmaf(a, m, q); b = fmaf(b, m, q); c = fmaf(c, m, q); d = fmaf(d, m, q);
-        e = fmaf(e, m, q); f = fmaf(f, m, q); g = fmaf(g, m, q); h = fmaf(h, m, q);
+        a = fmaf(a, m, a); b = fmaf(b, m, b); c = fmaf(c, m, c); d = fmaf(d, m, d);
+        e = fmaf(e, m, e); f = fmaf(f, m, f); g = fmaf(g, m, g); h = fmaf(h, m, h);
     }
     if (a + b + c + d + e + f + g + h == 12345.f) out[0] = a;
 }

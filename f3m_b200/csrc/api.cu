@@ -7,6 +7,7 @@
 #include <math.h>
 #include <algorithm>
 #include <mutex>
+#include <vector>
 #include "common.cuh"
 
 namespace f3m {
@@ -39,10 +40,38 @@ void ensure_pool_configured() {
 
 using namespace f3m;
 
+// Small per-plan scratch (64 pinned host words for read-backs, 64 device words for flags and counters).
+// cudaHostAlloc / cudaMalloc / cudaFree serialise the device, so slots are created once and recycled:
+// a plan takes a slot of its device from a free list and gives it back when it is destroyed.
+namespace {
+struct ScratchSlot { int device; int *h_pinned; int *d_flags; };
+std::mutex g_slot_mu;
+std::vector<ScratchSlot> g_free_slots;
+
+ScratchSlot take_slot(int device) {
+    {
+        std::lock_guard<std::mutex> lk(g_slot_mu);
+        for (size_t i = 0; i < g_free_slots.size(); i++)
+            if (g_free_slots[i].device == device) {
+                ScratchSlot sl = g_free_slots[i];
+                g_free_slots.erase(g_free_slots.begin() + i);
+                return sl;
+            }
+    }
+    ScratchSlot sl{device, nullptr, nullptr};
+    F3M_CUDA(cudaHostAlloc((void **)&sl.h_pinned, 64 * sizeof(int), cudaHostAllocDefault));
+    F3M_CUDA(cudaMalloc((void **)&sl.d_flags, 64 * sizeof(int)));
+    return sl;
+}
+void give_slot(const ScratchSlot &sl) {
+    std::lock_guard<std::mutex> lk(g_slot_mu);
+    g_free_slots.push_back(sl);
+}
+}  // namespace
+
 f3m_plan::~f3m_plan() {
     last.resolve();
-    if (h_pinned) cudaFreeHost(h_pinned);
-    if (d_flags) cudaFree(d_flags);
+    if (h_pinned && d_flags) give_slot(ScratchSlot{device, h_pinned, d_flags});
 }
 
 template <typename F>
@@ -76,8 +105,11 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
     pl->prm = *prm;
     pl->same = (X == Y);                                  // n_tree.cu:1072
     pl->lcs = 1 / (2 * prm->ls * prm->ls);                // n_tree.cu:1060
-    F3M_CUDA(cudaHostAlloc((void **)&pl->h_pinned, 64 * sizeof(int), cudaHostAllocDefault));
-    F3M_CUDA(cudaMalloc((void **)&pl->d_flags, 64 * sizeof(int)));
+    {
+        ScratchSlot sl = take_slot(pl->device);
+        pl->h_pinned = sl.h_pinned;
+        pl->d_flags = sl.d_flags;
+    }
     F3M_CUDA(cudaMemsetAsync(pl->d_flags, 0, 64 * sizeof(int), s));
     pl->last.begin(ST_BUILD, s);
 
@@ -266,7 +298,8 @@ int f3m_plan_apply(f3m_plan *plan, const float *b, int32_t R, float *out, void *
 
 int f3m_plan_destroy(f3m_plan *plan) {
     if (!plan) return F3M_OK;
-    cudaDeviceSynchronize();
+    // every entry point that enqueues work on the plan's buffers synchronises its stream before it
+    // returns, so the buffers can go back to the stream-ordered pool without a device-wide wait
     delete plan;
     return F3M_OK;
 }

@@ -50,6 +50,7 @@ _I64, _I32, _F32, _F64 = C.c_int64, C.c_int32, C.c_float, C.c_double
 # name -> (restype, argtypes); every symbol declared in include/f3m.h
 SIGNATURES = {
     "f3m_version": (C.c_int, []),
+    "f3m_release_cached_memory": (C.c_int, []),
     "f3m_status_string": (C.c_char_p, [C.c_int]),
     "f3m_last_error": (C.c_char_p, []),
     "f3m_kmvm_f32": (C.c_int, [_P, _I64, _P, _I64, _P, _I32, _I32, C.POINTER(Params), _P, _P]),

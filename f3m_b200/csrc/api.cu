@@ -22,18 +22,66 @@ void set_error(const char *fmt, ...) {
     va_end(ap);
 }
 
-void ensure_pool_configured() {
-    static std::mutex mu;
-    static bool done[64] = {false};
+// ---- caching device allocator ------------------------------------------------------------------
+namespace {
+struct FreeBlock { void *p; size_t bytes; int device; };
+std::mutex g_mem_mu;
+std::vector<FreeBlock> g_free_blocks;
+
+size_t round_request(size_t bytes) {
+    if (bytes < 512) bytes = 512;
+    const size_t q = bytes >= (1u << 20) ? (1u << 20) : 512;   // 1 MiB granularity for large blocks
+    return (bytes + q - 1) / q * q;
+}
+}  // namespace
+
+void *dev_alloc(size_t bytes, size_t *granted) {
+    const size_t need = round_request(bytes);
     int dev = 0;
     F3M_CUDA(cudaGetDevice(&dev));
-    std::lock_guard<std::mutex> lk(mu);
-    if (dev < 64 && done[dev]) return;
-    cudaMemPool_t pool;
-    F3M_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
-    uint64_t thr = UINT64_MAX;   // keep freed blocks in the pool
-    F3M_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thr));
-    if (dev < 64) done[dev] = true;
+    {
+        std::lock_guard<std::mutex> lk(g_mem_mu);
+        int best = -1;
+        for (size_t i = 0; i < g_free_blocks.size(); i++) {
+            const FreeBlock &b = g_free_blocks[i];
+            if (b.device != dev || b.bytes < need || b.bytes > need + need / 4 + (1u << 20)) continue;
+            if (best < 0 || b.bytes < g_free_blocks[best].bytes) best = (int)i;
+        }
+        if (best >= 0) {
+            FreeBlock b = g_free_blocks[best];
+            g_free_blocks.erase(g_free_blocks.begin() + best);
+            *granted = b.bytes;
+            return b.p;
+        }
+    }
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, need);
+    if (e == cudaErrorMemoryAllocation) {   // give the cached blocks back and try once more
+        cudaGetLastError();
+        {
+            std::lock_guard<std::mutex> lk(g_mem_mu);
+            for (size_t i = 0; i < g_free_blocks.size();) {
+                if (g_free_blocks[i].device == dev) { cudaFree(g_free_blocks[i].p); g_free_blocks.erase(g_free_blocks.begin() + i); }
+                else i++;
+            }
+        }
+        e = cudaMalloc(&p, need);
+    }
+    if (e != cudaSuccess) {
+        set_error("cudaMalloc of %zu bytes failed: %s", need, cudaGetErrorString(e));
+        throw Fail{F3M_ERR_CUDA};
+    }
+    *granted = need;
+    return p;
+}
+
+void dev_free(void *p, size_t granted) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) == cudaSuccess) dev = attr.device;
+    std::lock_guard<std::mutex> lk(g_mem_mu);
+    g_free_blocks.push_back(FreeBlock{p, granted, dev});
 }
 
 }  // namespace f3m
@@ -99,7 +147,6 @@ static void check_common(const void *X, int64_t N, const void *Y, int64_t M, int
 
 static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, int64_t M, int d, const f3m_params *prm,
                        cudaStream_t s) {
-    ensure_pool_configured();
     F3M_CUDA(cudaGetDevice(&pl->device));
     pl->d = d;
     pl->prm = *prm;
@@ -319,8 +366,7 @@ int f3m_kmvm_host_f32(const float *X, int64_t N, const float *Y, int64_t M, cons
     int st = guarded([&] {
         check_common(X, N, Y, M, d, prm);
         F3M_REQUIRE(b && out && R >= 1, F3M_ERR_ARG, "bad right-hand side");
-        ensure_pool_configured();
-        cudaStream_t s = nullptr;
+            cudaStream_t s = nullptr;
         const bool same = (X == Y);
         DevBuf<float> dX, dY, db, dout;
         dX.alloc((size_t)N * d, s);
@@ -397,8 +443,7 @@ int f3m_rbf_dense_f32(const float *X, int64_t N, const float *Y, int64_t M, cons
     return guarded([&] {
         F3M_REQUIRE(X && Y && b && out && N > 0 && M > 0 && R >= 1 && d >= 1 && d <= F3M_MAX_DIM && ls > 0, F3M_ERR_ARG,
                     "bad argument to f3m_rbf_dense_f32");
-        ensure_pool_configured();
-        dense_f32<false>(X, N, Y, M, b, R, d, ls, out, (cudaStream_t)stream);
+            dense_f32<false>(X, N, Y, M, b, R, d, ls, out, (cudaStream_t)stream);
         F3M_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     });
 }
@@ -408,8 +453,7 @@ int f3m_rbf_dense_grad_f32(const float *X, int64_t N, const float *Y, int64_t M,
     return guarded([&] {
         F3M_REQUIRE(X && Y && b && out && N > 0 && M > 0 && R >= 1 && d >= 1 && d <= F3M_MAX_DIM && ls > 0, F3M_ERR_ARG,
                     "bad argument to f3m_rbf_dense_grad_f32");
-        ensure_pool_configured();
-        dense_f32<true>(X, N, Y, M, b, R, d, ls, out, (cudaStream_t)stream);
+            dense_f32<true>(X, N, Y, M, b, R, d, ls, out, (cudaStream_t)stream);
         F3M_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     });
 }
@@ -437,9 +481,15 @@ int f3m_rbf_dense_f32_static(const float *X, int64_t N, const float *Y, int64_t 
 int f3m_measure_peaks(double *gexp_per_s, double *gfma_per_s, void *stream) {
     if (!gexp_per_s || !gfma_per_s) return F3M_ERR_ARG;
     return guarded([&] {
-        ensure_pool_configured();
-        measure_peaks(gexp_per_s, gfma_per_s, (cudaStream_t)stream);
+            measure_peaks(gexp_per_s, gfma_per_s, (cudaStream_t)stream);
     });
+}
+
+int f3m_release_cached_memory(void) {
+    std::lock_guard<std::mutex> lk(g_mem_mu);
+    for (auto &b : g_free_blocks) cudaFree(b.p);
+    g_free_blocks.clear();
+    return F3M_OK;
 }
 
 int f3m_plan_last_timings(const f3m_plan *plan, float ms[8]) {

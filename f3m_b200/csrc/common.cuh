@@ -41,24 +41,31 @@ extern long long g_launches;   // kernels launched by this library (all threads;
         }                                                                                        \
     } while (0)
 
-// ---- stream-ordered device buffer ------------------------------------------------------------
-// Memory comes from the device's default stream-ordered pool (cudaMallocAsync); the pool keeps
-// freed blocks, so repeated products do not go back to the driver.
-void ensure_pool_configured();
+// ---- device buffers --------------------------------------------------------------------------
+// Device memory comes from a small caching allocator inside the library (api.cu): blocks are obtained
+// with cudaMalloc once, kept on a free list when released and handed out again to requests of a similar
+// size, so that a repeated product makes no driver call at all.  (The driver's stream-ordered pool
+// was tried first; with multi-GB buffers freed and re-requested every call it re-mapped memory at
+// unpredictable times, 200 ms at a time.)  A released block may be reused immediately by work that is
+// enqueued later on the same stream; every entry point synchronises its stream before it returns, so
+// blocks never cross streams while in use.  f3m_release_cached_memory() returns the free list to the driver.
+void *dev_alloc(size_t bytes, size_t *granted);
+void dev_free(void *p, size_t granted);
 
 template <typename T>
 struct DevBuf {
     T *p = nullptr;
     size_t n = 0;
+    size_t granted = 0;
     cudaStream_t s = nullptr;
     DevBuf() = default;
     DevBuf(const DevBuf &) = delete;
     DevBuf &operator=(const DevBuf &) = delete;
-    DevBuf(DevBuf &&o) noexcept : p(o.p), n(o.n), s(o.s) { o.p = nullptr; o.n = 0; }
+    DevBuf(DevBuf &&o) noexcept : p(o.p), n(o.n), granted(o.granted), s(o.s) { o.p = nullptr; o.n = 0; }
     DevBuf &operator=(DevBuf &&o) noexcept {
         if (this != &o) {
             release();
-            p = o.p; n = o.n; s = o.s;
+            p = o.p; n = o.n; granted = o.granted; s = o.s;
             o.p = nullptr; o.n = 0;
         }
         return *this;
@@ -68,11 +75,11 @@ struct DevBuf {
         s = stream;
         n = count;
         if (count == 0) count = 1;
-        F3M_CUDA(cudaMallocAsync((void **)&p, count * sizeof(T), stream));
+        p = static_cast<T *>(dev_alloc(count * sizeof(T), &granted));
     }
     void zero() { F3M_CUDA(cudaMemsetAsync(p, 0, (n ? n : 1) * sizeof(T), s)); }
     void release() {
-        if (p) cudaFreeAsync(p, s);
+        if (p) dev_free(p, granted);
         p = nullptr;
         n = 0;
     }

@@ -227,18 +227,26 @@ __global__ void __launch_bounds__(RS_THREADS) rs_hist(const uint32_t *__restrict
     counts[threadIdx.x * G + blockIdx.x] = h[threadIdx.x];
 }
 
+// Stable scatter of one pass.  Keys of a tile are first ranked (warp-level multi-split), then staged in
+// shared memory in digit order, so that the global writes of a tile are runs of consecutive addresses
+// per digit instead of 4-byte scatters.
 __global__ void __launch_bounds__(RS_THREADS) rs_scatter(const uint32_t *__restrict__ keys, const int *__restrict__ vals,
                                                         int64_t n, int shift, int64_t chunk,
                                                         const int *__restrict__ scanned, int G, uint32_t *okeys,
                                                         int *ovals) {
-    __shared__ int base[256];
-    __shared__ int wcnt[RS_WARPS][256];
+    __shared__ int base[256];              // next global position per digit for this block
+    __shared__ int dstart[256];            // start of the digit inside the staged tile
+    __shared__ int wcnt[RS_WARPS][256];    // per-warp digit counts, then per-warp bases
+    __shared__ uint32_t skeys[RS_TILE];
+    __shared__ int svals[RS_TILE];
+    __shared__ int scan_sm[33];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     base[threadIdx.x] = scanned[threadIdx.x * G + blockIdx.x];
     for (int q = 0; q < RS_WARPS; q++) wcnt[q][threadIdx.x] = 0;
     __syncthreads();
     int64_t beg = (int64_t)blockIdx.x * chunk, end = min(n, beg + chunk);
     for (int64_t tile = beg; tile < end; tile += RS_TILE) {
+        const int tile_cnt = (int)min((int64_t)RS_TILE, end - tile);
         uint32_t k[RS_ITEMS];
         int v[RS_ITEMS], off[RS_ITEMS];
 #pragma unroll
@@ -272,15 +280,24 @@ __global__ void __launch_bounds__(RS_THREADS) rs_scatter(const uint32_t *__restr
             }
             tile_total = run;
         }
+        dstart[threadIdx.x] = block_exclusive_scan(tile_total, nullptr, scan_sm);   // ends with a barrier
         __syncthreads();
 #pragma unroll
         for (int r = 0; r < RS_ITEMS; r++) {
             if (off[r] >= 0) {
                 int dg = (k[r] >> shift) & 255;
-                int64_t pos = (int64_t)base[dg] + wcnt[w][dg] + off[r];
-                okeys[pos] = k[r];
-                ovals[pos] = v[r];
+                int sp = dstart[dg] + wcnt[w][dg] + off[r];
+                skeys[sp] = k[r];
+                svals[sp] = v[r];
             }
+        }
+        __syncthreads();
+        for (int q = threadIdx.x; q < tile_cnt; q += RS_THREADS) {
+            uint32_t kk = skeys[q];
+            int dg = (kk >> shift) & 255;
+            int64_t pos = (int64_t)base[dg] + (q - dstart[dg]);
+            okeys[pos] = kk;
+            ovals[pos] = svals[q];
         }
         __syncthreads();
         base[threadIdx.x] += tile_total;

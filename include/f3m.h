@@ -60,6 +60,10 @@ typedef struct f3m_plan f3m_plan;   /* tree + interaction lists of one (X, Y) pa
 
 /* -------- library ------------------------------------------------------------------------- */
 int f3m_version(void);
+/* The library keeps the device blocks it has used on a free list and reuses them; this returns the
+ * unused ones to the driver (call it between phases of very different sizes, or before another
+ * framework needs the memory).  Must not run concurrently with other calls into the library. */
+int f3m_release_cached_memory(void);
 const char *f3m_status_string(int status);
 /* Message of the last failing call made by this thread ("" if none). */
 const char *f3m_last_error(void);

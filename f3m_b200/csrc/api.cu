@@ -282,7 +282,8 @@ static void plan_apply(f3m_plan *pl, const float *b, int R, float *out, int64_t 
     if (L > 0) direct_sums(pl, L, pl->lists[L].keep, bs.p, R, outs.p, row_begin, row_end, s);   // n_tree.cu:1092-1094
 
     pl->last.begin(ST_UNPERMUTE, s);
-    scatter_rows(outs.p, tx.perm.p, out, N, R, s);
+    if (row_begin <= 0 && row_end >= N) scatter_rows(outs.p, tx.perm.p, out, N, R, s);
+    else scatter_rows_nonzero(outs.p, tx.perm.p, out, N, R, s);   // a slice: most rows are zero
     pl->last.end(s);
     F3M_CUDA(cudaEventRecord(pl->last.spans[0].b, s));   // closes the ST_TOTAL span opened first
     F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, pl->d_flags, sizeof(int), cudaMemcpyDeviceToHost, s));
@@ -366,19 +367,44 @@ int f3m_kmvm_host_f32(const float *X, int64_t N, const float *Y, int64_t M, cons
     int st = guarded([&] {
         check_common(X, N, Y, M, d, prm);
         F3M_REQUIRE(b && out && R >= 1, F3M_ERR_ARG, "bad right-hand side");
-            cudaStream_t s = nullptr;
-        const bool same = (X == Y);
-        DevBuf<float> dX, dY, db, dout;
+            const bool same = (X == Y);
+        // two streams: the coordinates go first and the tree is built from them while b is still on the link
+        cudaStream_t s = nullptr, sb = nullptr;
+        cudaEvent_t ev_x = nullptr, ev_b = nullptr;
+        f3m_plan *pl = nullptr;
+        DevBuf<float> dX, dY, db, dout;   // declared before the guard below: released after the streams are drained
+        struct Cleanup {
+            cudaStream_t &s, &sb; cudaEvent_t &ex, &eb; f3m_plan *&pl;
+            ~Cleanup() {
+                if (s) cudaStreamSynchronize(s);
+                if (sb) cudaStreamSynchronize(sb);
+                if (pl) f3m_plan_destroy(pl);
+                if (ex) cudaEventDestroy(ex);
+                if (eb) cudaEventDestroy(eb);
+                if (s) cudaStreamDestroy(s);
+                if (sb) cudaStreamDestroy(sb);
+            }
+        } cleanup{s, sb, ev_x, ev_b, pl};
+        F3M_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+        F3M_CUDA(cudaStreamCreateWithFlags(&sb, cudaStreamNonBlocking));
+        F3M_CUDA(cudaEventCreateWithFlags(&ev_x, cudaEventDisableTiming));
+        F3M_CUDA(cudaEventCreateWithFlags(&ev_b, cudaEventDisableTiming));
         dX.alloc((size_t)N * d, s);
         F3M_CUDA(cudaMemcpyAsync(dX.p, X, (size_t)N * d * sizeof(float), cudaMemcpyHostToDevice, s));
         if (!same) {
             dY.alloc((size_t)M * d, s);
             F3M_CUDA(cudaMemcpyAsync(dY.p, Y, (size_t)M * d * sizeof(float), cudaMemcpyHostToDevice, s));
         }
+        F3M_CUDA(cudaEventRecord(ev_x, s));
         db.alloc((size_t)M * R, s);
-        F3M_CUDA(cudaMemcpyAsync(db.p, b, (size_t)M * R * sizeof(float), cudaMemcpyHostToDevice, s));
+        F3M_CUDA(cudaStreamWaitEvent(sb, ev_x, 0));
+        F3M_CUDA(cudaMemcpyAsync(db.p, b, (size_t)M * R * sizeof(float), cudaMemcpyHostToDevice, sb));
+        F3M_CUDA(cudaEventRecord(ev_b, sb));
         dout.alloc((size_t)N * R, s);
-        int st2 = f3m_kmvm_f32(dX.p, N, same ? dX.p : dY.p, M, db.p, R, d, prm, dout.p, s);
+        int st2 = f3m_plan_create(&pl, dX.p, N, same ? dX.p : dY.p, M, d, prm, s);
+        if (st2 != F3M_OK) throw Fail{st2};
+        F3M_CUDA(cudaStreamWaitEvent(s, ev_b, 0));
+        st2 = f3m_plan_apply(pl, db.p, R, dout.p, s);
         if (st2 != F3M_OK) throw Fail{st2};
         F3M_CUDA(cudaMemcpyAsync(out, dout.p, (size_t)N * R * sizeof(float), cudaMemcpyDeviceToHost, s));
         F3M_CUDA(cudaStreamSynchronize(s));

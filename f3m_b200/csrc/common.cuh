@@ -177,6 +177,7 @@ void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *o
 void exclusive_scan_i32(const int *in, int *out, int64_t n, cudaStream_t s);  // out may alias in; writes n+1? no: n values
 void gather_rows(const float *src, const int *perm, float *dst, int64_t n, int cols, cudaStream_t s);
 void scatter_rows(const float *src, const int *perm, float *dst, int64_t n, int cols, cudaStream_t s);
+void scatter_rows_nonzero(const float *src, const int *perm, float *dst, int64_t n, int cols, cudaStream_t s);
 
 // ---- tree.cu ---------------------------------------------------------------------------------
 void build_root(Tree &t, cudaStream_t s);

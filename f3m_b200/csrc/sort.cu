@@ -332,6 +332,24 @@ __global__ void __launch_bounds__(256) scatter_rows_kernel(const float *__restri
     int c = (int)(e - i * cols);
     dst[(int64_t)perm[i] * cols + c] = src[e];
 }
+// rows that are entirely zero are skipped (dst must be zero-filled): used when only a slice of the sorted
+// rows was computed, so that the random writes are paid for that slice only
+__global__ void __launch_bounds__(256) scatter_rows_nonzero_kernel(const float *__restrict__ src, const int *__restrict__ perm,
+                                                                  float *dst, int64_t n, int cols) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    bool any = false;
+    for (int c = 0; c < cols; c++) any |= (src[i * cols + c] != 0.f);
+    if (!any) return;
+    const int64_t r = perm[i];
+    for (int c = 0; c < cols; c++) dst[r * cols + c] = src[i * cols + c];
+}
+void scatter_rows_nonzero(const float *src, const int *perm, float *dst, int64_t n, int cols, cudaStream_t s) {
+    if (n == 0) return;
+    F3M_CUDA(cudaMemsetAsync(dst, 0, (size_t)n * cols * sizeof(float), s));
+    scatter_rows_nonzero_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, perm, dst, n, cols);
+    F3M_LAUNCH_CHECK();
+}
 void gather_rows(const float *src, const int *perm, float *dst, int64_t n, int cols, cudaStream_t s) {
     int64_t tot = n * cols;
     if (tot == 0) return;

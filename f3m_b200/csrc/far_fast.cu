@@ -128,8 +128,8 @@ static KronCfg make_kron_cfg(int d, int p, int RB) {
 // i.e. two rounds per lane); otherwise in the warp's shared-memory accumulator.
 template <int PP, bool ACC_REG>
 __device__ __forceinline__ void warp_kron(const float *src0, float *bufA, float *bufB, float *acc_sm,
-                                          float (&acc_reg)[2][PP], const float *const (&mats)[MAXD], const KronCfg &cfg,
-                                          int lane) {
+                                          float (&acc_reg)[2][PP], float &acc_left, const float *const (&mats)[MAXD],
+                                          const KronCfg &cfg, int lane) {
     constexpr int MS = mat_stride(PP);
     const float *src = src0;
     float *dst = bufA;
@@ -165,7 +165,21 @@ __device__ __forceinline__ void warp_kron(const float *src0, float *bufA, float 
             };
             if (ACC_REG) {   // at most two rounds, register accumulators indexed statically
                 if (lane < nf) fibre(lane, acc_reg[0]);
-                if (lane + 32 < nf) fibre(lane + 32, acc_reg[1]);
+                const int left = nf - 32;
+                if (left > 0 && left * PP <= 32) {
+                    // a short second round (e.g. 36 fibres): one OUTPUT per lane instead of one fibre per lane
+                    if (lane < left * PP) {
+                        const int lf = lane / PP, i = lane - lf * PP, f = 32 + lf;
+                        const int hi = last ? 0 : __float2int_rz(((float)f + 0.5f) * inv);
+                        const int base = hi * st * PP + (f - hi * st);
+                        const float *mrow = mats[k] + i * PP;
+                        float o = 0.f;
+#pragma unroll
+                        for (int j = 0; j < PP; j++) o = fmaf(mrow[j], src[base + j * st], o);
+                        if (!last) dst[base + i * st] = o;
+                        else acc_left += o;
+                    }
+                } else if (lane + 32 < nf) fibre(lane + 32, acc_reg[1]);
             } else {
                 for (int f = lane; f < nf; f += 32) fibre(f, acc_reg[0]);
             }
@@ -178,14 +192,21 @@ __device__ __forceinline__ void warp_kron(const float *src0, float *bufA, float 
 
 // after the last pair: registers -> the warp's shared-memory accumulator (layout of the last stage: base = fibre)
 template <int PP>
-__device__ __forceinline__ void flush_acc(float (&acc_reg)[2][PP], float *acc_sm, const KronCfg &cfg, int lane) {
+__device__ __forceinline__ void flush_acc(float (&acc_reg)[2][PP], float acc_left, float *acc_sm, const KronCfg &cfg,
+                                          int lane) {
     const int st = cfg.st[cfg.d - 1];
+    const int left = cfg.nf - 32;
+    const bool short_round = left > 0 && left * PP <= 32;
 #pragma unroll
     for (int rnd = 0; rnd < 2; rnd++) {
         const int f = lane + rnd * 32;
-        if (f < cfg.nf)
+        if (f < cfg.nf && !(rnd == 1 && short_round))
 #pragma unroll
             for (int i = 0; i < PP; i++) acc_sm[f + i * st] = acc_reg[rnd][i];
+    }
+    if (short_round && lane < left * PP) {
+        const int lf = lane / PP, i = lane - lf * PP;
+        acc_sm[32 + lf + i * st] = acc_left;
     }
 }
 
@@ -210,7 +231,7 @@ __device__ __forceinline__ void decode_cell2(uint32_t code, int level, int d, in
 // M2L: one CTA per target box, its warps share the far row
 // ---------------------------------------------------------------------------------------------
 template <int PP, bool ACC_REG>
-__global__ void __launch_bounds__(128) m2l_fast(int nbx, int d, const int *__restrict__ fptr, const int *__restrict__ fidx,
+__global__ void __launch_bounds__(128, 5) m2l_fast(int nbx, int d, const int *__restrict__ fptr, const int *__restrict__ fidx,
                                                const int *__restrict__ cell_x, const int *__restrict__ cell_y,
                                                const int *__restrict__ off_x, int row_begin, int row_end,
                                                const float *__restrict__ T, Geom2 geo, KronCfg cfg,
@@ -228,7 +249,7 @@ __global__ void __launch_bounds__(128) m2l_fast(int nbx, int d, const int *__res
     float *bufA = wbuf, *bufB = wbuf + PR, *acc = wbuf + 2 * PR;
     for (int q = threadIdx.x; q < ntab; q += blockDim.x) Tsm[q] = T[q];
     for (int q = lane; q < PR; q += 32) acc[q] = 0.f;
-    float acc_reg[2][PP];
+    float acc_reg[2][PP], acc_left = 0.f;
 #pragma unroll
     for (int a = 0; a < 2; a++)
 #pragma unroll
@@ -251,9 +272,9 @@ __global__ void __launch_bounds__(128) m2l_fast(int nbx, int d, const int *__res
             mats[k] = Tsm + (k * NOFF2 + o) * MS;
         }
         if (!ok) { if (lane == 0) atomicExch(err, 2); continue; }
-        warp_kron<PP, ACC_REG>(mom + (size_t)by * PR, bufA, bufB, acc, acc_reg, mats, cfg, lane);
+        warp_kron<PP, ACC_REG>(mom + (size_t)by * PR, bufA, bufB, acc, acc_reg, acc_left, mats, cfg, lane);
     }
-    if (ACC_REG) flush_acc<PP>(acc_reg, acc, cfg, lane);
+    if (ACC_REG) flush_acc<PP>(acc_reg, acc_left, acc, cfg, lane);
     __syncthreads();
     for (int q = threadIdx.x; q < PR; q += blockDim.x) {
         float s = 0.f;
@@ -277,7 +298,7 @@ __global__ void __launch_bounds__(128) m2m_fast(int nbp, int d, const int *__res
     float *bufA = wbuf, *bufB = wbuf + PR, *acc = wbuf + 2 * PR;
     for (int q = threadIdx.x; q < ntab; q += blockDim.x) Asm[q] = A[q];
     for (int q = lane; q < PR; q += 32) acc[q] = 0.f;
-    float acc_reg[2][PP];
+    float acc_reg[2][PP], acc_left = 0.f;
     __syncthreads();
     const int c0 = child_start[pb], c1 = child_start[pb + 1];
     for (int c = c0 + w; c < c1; c += nw) {
@@ -285,7 +306,7 @@ __global__ void __launch_bounds__(128) m2m_fast(int nbp, int d, const int *__res
         const float *mats[MAXD];
 #pragma unroll
         for (int k = 0; k < MAXD; k++) mats[k] = Asm + ((code >> k) & 1u) * MS;
-        warp_kron<PP, false>(mom_child + (size_t)c * PR, bufA, bufB, acc, acc_reg, mats, cfg, lane);
+        warp_kron<PP, false>(mom_child + (size_t)c * PR, bufA, bufB, acc, acc_reg, acc_left, mats, cfg, lane);
     }
     __syncthreads();
     for (int q = threadIdx.x; q < PR; q += blockDim.x) {
@@ -319,8 +340,8 @@ __global__ void __launch_bounds__(128) l2l_fast(int nbc, int d, const int *__res
     const float *mats[MAXD];
 #pragma unroll
     for (int k = 0; k < MAXD; k++) mats[k] = Asm + ((code >> k) & 1u) * MS;
-    float acc_reg[2][PP];
-    warp_kron<PP, false>(loc_parent + (size_t)parent[c] * PR, bufA, bufB, acc, acc_reg, mats, cfg, lane);
+    float acc_reg[2][PP], acc_left = 0.f;
+    warp_kron<PP, false>(loc_parent + (size_t)parent[c] * PR, bufA, bufB, acc, acc_reg, acc_left, mats, cfg, lane);
     for (int q = lane; q < PR; q += 32) loc_child[(size_t)c * PR + q] += acc[q];
 }
 

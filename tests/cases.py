@@ -15,6 +15,13 @@ CASES = {
     "n4_r8": dict(d=4, N=20000, M=None, dist="normal", ls=1.0, min_points=500., P=81, small=81, var_comp=False, eff=0.15, R=8, seed=8),
     "n5_r8": dict(d=5, N=12000, M=None, dist="normal", ls=1.5, min_points=1000., P=32, small=32, var_comp=False, eff=0.15, R=8, seed=9),
     "clustered3": dict(d=3, N=30000, M=None, dist="clustered", ls=0.5, min_points=300., P=64, small=64, var_comp=False, eff=0.15, R=1, seed=10),
+    # per-level far path (more than 8 nodes per dimension, or node counts that change between levels)
+    "u2_p10": dict(d=2, N=20000, M=None, dist="uniform", ls=0.5, min_points=300., P=100, small=100, var_comp=False, eff=0.15, R=1, seed=13),
+    "u1_p32": dict(d=1, N=20000, M=None, dist="uniform", ls=0.1, min_points=300., P=32, small=32, var_comp=False, eff=0.15, R=2, seed=14),
+    "u3_vc_mixed_p": dict(d=3, N=60000, M=None, dist="uniform", ls=1.03, min_points=150., P=64, small=64, var_comp=True, eff=0.001, R=1, seed=15),
+    # two point sets whose cubes do not overlap: every level-1 pair is far
+    "xy_far_apart": dict(d=3, N=15000, M=12000, dist="uniform", ls=2.0, min_points=500., P=64, small=64, var_comp=False, eff=0.15, R=1, seed=16, y_shift=4.0),
+    "u3_r10": dict(d=3, N=15000, M=None, dist="uniform", ls=1.0, min_points=400., P=27, small=27, var_comp=False, eff=0.15, R=10, seed=17),
     "tiny": dict(d=3, N=50, M=None, dist="uniform", ls=1.0, min_points=1000., P=64, small=1000, var_comp=False, eff=0.15, R=1, seed=11),
     "dup_points": dict(d=3, N=5000, M=None, dist="duplicates", ls=1.0, min_points=100., P=27, small=27, var_comp=False, eff=0.15, R=1, seed=12),
 }
@@ -42,7 +49,7 @@ def make_case(name):
     c = dict(CASES[name])
     g = torch.Generator().manual_seed(c["seed"])
     X = _draw(c["dist"], c["N"], c["d"], g).float().contiguous()
-    Y = None if c["M"] is None else (_draw(c["dist"], c["M"], c["d"], g) * 0.9 + 0.05).float().contiguous()
+    Y = None if c["M"] is None else (_draw(c["dist"], c["M"], c["d"], g) * 0.9 + 0.05 + c.get("y_shift", 0.0)).float().contiguous()
     b = torch.randn(c["N"] if Y is None else c["M"], c["R"], generator=g).float().contiguous()
     c.update(X=X, Y=Y, b=b)
     return c

@@ -339,6 +339,44 @@ int f3m_plan_apply_range(f3m_plan *plan, const float *b, int32_t R, float *out, 
     return st;
 }
 
+int f3m_plan_moments_size(const f3m_plan *plan, int32_t R, int64_t *nfloats) {
+    if (!plan || !nfloats || R < 1) return F3M_ERR_ARG;
+    *nfloats = far_moments_size(plan, R);
+    return F3M_OK;
+}
+
+int f3m_plan_moments_range(f3m_plan *plan, const float *b, int32_t R, int64_t src_begin, int64_t src_end, float *mom_out,
+                           void *stream) {
+    if (!plan || !b || !mom_out) return F3M_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    int st = guarded([&] {
+        F3M_REQUIRE(far_moments_size(plan, R) > 0, F3M_ERR_UNSUPPORTED, "this plan does not exchange moments (see f3m_plan_moments_size)");
+        Tree &ty = *plan->ty;
+        DevBuf<float> bs;
+        bs.alloc((size_t)ty.n * R, s);
+        gather_rows(b, ty.perm.p, bs.p, ty.n, R, s);
+        plan->moments_out = mom_out;
+        plan->mom_begin = src_begin;
+        plan->mom_end = src_end;
+        far_field(plan, bs.p, R, nullptr, 0, 0, s);
+        F3M_CUDA(cudaStreamSynchronize(s));
+    });
+    plan->moments_out = nullptr;
+    if (st != F3M_OK) cudaStreamSynchronize(s);
+    plan->last.resolve();
+    return st;
+}
+
+int f3m_plan_apply_range_moments(f3m_plan *plan, const float *b, int32_t R, float *out, int64_t row_begin, int64_t row_end,
+                                 const float *mom, void *stream) {
+    if (!plan || !mom) return F3M_ERR_ARG;
+    if (far_moments_size(plan, R) <= 0) return F3M_ERR_UNSUPPORTED;
+    plan->ext_mom = mom;
+    int st = f3m_plan_apply_range(plan, b, R, out, row_begin, row_end, stream);
+    plan->ext_mom = nullptr;
+    return st;
+}
+
 int f3m_plan_apply(f3m_plan *plan, const float *b, int32_t R, float *out, void *stream) {
     if (!plan) return F3M_ERR_ARG;
     return f3m_plan_apply_range(plan, b, R, out, 0, plan->tx.n, stream);

@@ -163,6 +163,11 @@ struct f3m_plan {
     int levels = 0;
     f3m_plan_stats stats{};
     f3m::Timings last;
+    // sharded moments (multi-GPU): either write the finest-level moments of a slice of the source boxes
+    // into moments_out and stop, or take the complete finest-level moments from ext_mom instead of computing them
+    float *moments_out = nullptr;
+    int64_t mom_begin = 0, mom_end = 0;
+    const float *ext_mom = nullptr;
     int *h_pinned = nullptr;              // pinned host words for count read-back
     int *d_flags = nullptr;               // device status / counters (64 ints)
     ~f3m_plan();
@@ -191,6 +196,7 @@ void far_field_level(f3m_plan *pl, int level, const float *b_sorted, int R, floa
                      int64_t row_begin, int64_t row_end, cudaStream_t s);   // per-level path (far.cu)
 void far_field(f3m_plan *pl, const float *b_sorted, int R, float *out_sorted, int64_t row_begin, int64_t row_end,
                cudaStream_t s);                                               // whole product (far_fast.cu)
+int64_t far_moments_size(const f3m_plan *pl, int R);
 
 // ---- near.cu ---------------------------------------------------------------------------------
 void direct_sums(f3m_plan *pl, int level, const PairCSR &csr, const float *b_sorted, int R, float *out_sorted,

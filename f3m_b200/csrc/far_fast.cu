@@ -376,7 +376,8 @@ __device__ __forceinline__ void lagrange_pp(float t, const NodeTab2 &nt, float *
 template <int PP, int RB>
 __global__ void __launch_bounds__(256) p2m_leaf(const float *__restrict__ pts, int n, int d, const float *__restrict__ bs, int R,
                                                int r0, const int *__restrict__ off, const float *__restrict__ ctr,
-                                               float factor, NodeTab2 nt, int P, int nsplit, float *mom) {
+                                               float factor, NodeTab2 nt, int P, int nsplit, int src_begin, int src_end,
+                                               float *mom) {
     extern __shared__ __align__(16) float sm[];
     constexpr int TP = 128, NTH = 256, LS = TP + 1;
     float *Ls = sm;                                   // [d*PP][TP+1]
@@ -384,6 +385,7 @@ __global__ void __launch_bounds__(256) p2m_leaf(const float *__restrict__ pts, i
     float *accsm = bsm + (size_t)TP * RB;             // [P][RB]
     const int box = blockIdx.x;
     const int a = off[box], b = off[box + 1];
+    if (a < src_begin || a >= src_end) return;      // only the boxes of this slice of the sorted sources
     const int len = b - a;
     const int s0 = a + (int)(((long long)len * blockIdx.y) / nsplit), s1 = a + (int)(((long long)len * (blockIdx.y + 1)) / nsplit);
     if (s0 >= s1) return;
@@ -523,9 +525,26 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
     const KronCfg cfg = make_kron_cfg(d, PP, RB);
     const int n_x = (int)tx.n, n_y = (int)ty.n;
 
+    if (pl->moments_out) {
+        // sharded P2M: finest-level moments of the source boxes that start in [mom_begin, mom_end), zero elsewhere
+        Level &ly = ty.levels[L];
+        F3M_CUDA(cudaMemsetAsync(pl->moments_out, 0, (size_t)ly.nb * PR * sizeof(float), s));
+        int nsplit = std::max(1, std::min(64, (ly.max_count + 8191) / 8192));
+        size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
+        F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        pl->last.begin(ST_P2M, s);
+        p2m_leaf<PP, RB><<<dim3(ly.nb, nsplit), 256, smem, s>>>(ty.pts.p, n_y, d, bs, R, r0, ly.off.p, ly.ctr.p, 2.f / ly.edge, nt, P,
+                                                              nsplit > 1 ? nsplit : 1, (int)pl->mom_begin, (int)pl->mom_end,
+                                                              pl->moments_out);
+        pl->last.end(s);
+        F3M_LAUNCH_CHECK();
+        return;
+    }
     std::vector<DevBuf<float>> mom(L + 1), loc(L + 1);
+    std::vector<const float *> momp(L + 1, nullptr);
     for (int l = lmin; l <= L; l++) {
-        mom[l].alloc((size_t)ty.levels[l].nb * PR, s);
+        if (!(l == L && pl->ext_mom)) mom[l].alloc((size_t)ty.levels[l].nb * PR, s);
+        momp[l] = (l == L && pl->ext_mom) ? pl->ext_mom : mom[l].p;
         loc[l].alloc((size_t)tx.levels[l].nb * PR, s);
         loc[l].zero();
     }
@@ -550,19 +569,21 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
     {
         Level &ly = ty.levels[L];
         const float factor = 2.f / ly.edge;          // 1_d_conv.cu:473
-        int nsplit = std::max(1, std::min(64, (ly.max_count + 8191) / 8192));
-        if (nsplit > 1) mom[L].zero();
-        size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
-        F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        p2m_leaf<PP, RB><<<dim3(ly.nb, nsplit), 256, smem, s>>>(ty.pts.p, n_y, d, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt, P,
-                                                              nsplit, mom[L].p);
-        F3M_LAUNCH_CHECK();
+        if (!pl->ext_mom) {
+            int nsplit = std::max(1, std::min(64, (ly.max_count + 8191) / 8192));
+            if (nsplit > 1) mom[L].zero();
+            size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
+            F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            p2m_leaf<PP, RB><<<dim3(ly.nb, nsplit), 256, smem, s>>>(ty.pts.p, n_y, d, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt, P,
+                                                                  nsplit, 0, n_y, mom[L].p);
+            F3M_LAUNCH_CHECK();
+        }
         const int nw = warps_for(2 * MS * sizeof(float));
         size_t sm2 = (size_t)2 * MS * sizeof(float) + nw * per_warp;
         F3M_CUDA(cudaFuncSetAttribute(m2m_fast<PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm2));
         for (int l = L - 1; l >= lmin; l--) {
             Level &lp = ty.levels[l], &lc = ty.levels[l + 1];
-            m2m_fast<PP><<<lp.nb, 32 * nw, sm2, s>>>(lp.nb, d, lp.child_start.p, lc.code.p, A.p, cfg, mom[l + 1].p, mom[l].p);
+            m2m_fast<PP><<<lp.nb, 32 * nw, sm2, s>>>(lp.nb, d, lp.child_start.p, lc.code.p, A.p, cfg, momp[l + 1], mom[l].p);
             F3M_LAUNCH_CHECK();
         }
     }
@@ -605,10 +626,10 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
             }
             if (acc_reg)
                 m2l_fast<PP, true><<<lx.nb, 32 * nw, smem, s>>>(lx.nb, d, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, lx.off.p, rb, re,
-                                                               T.p, geo, cfg, mom[l].p, loc[l].p, pl->d_flags);
+                                                               T.p, geo, cfg, momp[l], loc[l].p, pl->d_flags);
             else
                 m2l_fast<PP, false><<<lx.nb, 32 * nw, smem, s>>>(lx.nb, d, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, lx.off.p, rb, re,
-                                                                T.p, geo, cfg, mom[l].p, loc[l].p, pl->d_flags);
+                                                                T.p, geo, cfg, momp[l], loc[l].p, pl->d_flags);
             F3M_LAUNCH_CHECK();
         }
     }
@@ -647,6 +668,30 @@ static void far_fast_p(f3m_plan *pl, const float *bs, int R, float *out, int rb,
         if (wide) { far_fast_block<PP, 8>(pl, bs, R, r0, out, rb, re, lmin, s); r0 += 8; }
         else { far_fast_block<PP, 1>(pl, bs, R, r0, out, rb, re, lmin, s); r0 += 1; }
     }
+}
+
+// Number of floats of the finest-level moment array when the far field of (plan, R) runs as one column block on
+// the single-pass path, else 0 (then moments cannot be exchanged between ranks and every rank computes its own).
+int64_t far_moments_size(const f3m_plan *pl, int R) {
+    const int L = pl->levels;
+    int lmin = 0, p = 0;
+    bool uniform = true;
+    for (int l = 1; l <= L; l++) {
+        if (pl->lists[l].far.count == 0) continue;
+        if (!lmin) { lmin = l; p = pl->lists[l].p; }
+        else if (pl->lists[l].p != p) uniform = false;
+    }
+    if (!lmin || !uniform || p > PMAX_FAST || p < 2) return 0;
+    int P = 1;
+    for (int k = 0; k < pl->d; k++) P *= p;
+    const size_t tab = (size_t)pl->d * NOFF2 * mat_stride(p) * sizeof(float);
+    if ((size_t)3 * P * sizeof(float) + tab > 200 * 1024) return 0;
+    int RB = 1;
+    if (R > 1) {
+        if (R > 8 || (size_t)3 * P * 8 * sizeof(float) + tab > 200 * 1024) return 0;
+        RB = 8;
+    }
+    return (int64_t)pl->ty->levels[L].nb * P * RB;
 }
 
 // Far field of the whole product.  Fast path when every level with far pairs uses the same p <= 8;

@@ -49,7 +49,25 @@ class Plan:
                                             self.d, C.byref(self.params), _stream_ptr(self.device))
         check(st, "f3m_plan_create")
 
-    def apply(self, b: torch.Tensor, row_range=None) -> torch.Tensor:
+    def moments_size(self, R: int) -> int:
+        """Floats of the finest-level moment array if this plan can exchange moments between ranks, else 0."""
+        n = C.c_int64()
+        check(_lib.lib().f3m_plan_moments_size(self._h, int(R), C.byref(n)), "f3m_plan_moments_size")
+        return int(n.value)
+
+    def moments(self, b: torch.Tensor, src_range) -> torch.Tensor:
+        """Finest-level moments of the source boxes starting inside src_range of the sorted order (zero elsewhere)."""
+        b = _as_f32(b.to(self.device))
+        if b.dim() == 1:
+            b = b[:, None]
+        mom = torch.empty(self.moments_size(b.shape[1]), device=self.device, dtype=torch.float32)
+        with torch.cuda.device(self.device):
+            st = _lib.lib().f3m_plan_moments_range(self._h, b.data_ptr(), b.shape[1], int(src_range[0]), int(src_range[1]),
+                                                   mom.data_ptr(), _stream_ptr(self.device))
+        check(st, "f3m_plan_moments_range")
+        return mom
+
+    def apply(self, b: torch.Tensor, row_range=None, moments: Optional[torch.Tensor] = None) -> torch.Tensor:
         b = _as_f32(b.to(self.device))
         if b.dim() == 1:
             b = b[:, None]
@@ -57,7 +75,11 @@ class Plan:
             raise AssertionError(f"b has {b.shape[0]} rows, Y has {self.M}")
         out = torch.empty(self.N, b.shape[1], device=self.device, dtype=torch.float32)
         with torch.cuda.device(self.device):
-            if row_range is None:
+            if moments is not None:
+                rr = (0, self.N) if row_range is None else row_range
+                st = _lib.lib().f3m_plan_apply_range_moments(self._h, b.data_ptr(), b.shape[1], out.data_ptr(), int(rr[0]),
+                                                             int(rr[1]), moments.data_ptr(), _stream_ptr(self.device))
+            elif row_range is None:
                 st = _lib.lib().f3m_plan_apply(self._h, b.data_ptr(), b.shape[1], out.data_ptr(), _stream_ptr(self.device))
             else:
                 st = _lib.lib().f3m_plan_apply_range(self._h, b.data_ptr(), b.shape[1], out.data_ptr(), int(row_range[0]),

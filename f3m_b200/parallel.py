@@ -6,8 +6,10 @@ every rank holds a shard of the points and of b:
 
   1. all-gather the shards of X and b (NCCL over NVLink): every rank holds all sources;
   2. every rank builds the same tree and interaction lists (cheap next to the sums);
-  3. the target boxes are split into contiguous slices of the sorted order, one per rank, and each
-     rank computes the far and near field of its slice only (f3m_plan_apply_range);
+  3. the boxes are split into contiguous slices of the sorted order, one per rank; each rank computes
+     the finest-level moments of its slice of the SOURCE boxes (f3m_plan_moments_range), the moment
+     arrays are summed with an all-reduce, and each rank computes the far and near field of its slice
+     of the TARGET boxes (f3m_plan_apply_range_moments);
   4. the slices are combined with an all-reduce, so every rank ends with the whole product
      (rows outside a rank's slice are zero before the sum).
 """
@@ -59,7 +61,14 @@ def distributed_kmvm(x_shard: torch.Tensor, b_shard: torch.Tensor, params, group
     if compute is None:
         from . import engine
         plan = engine.Plan(X, None, params)
-        out = plan.apply(b, row_range=(lo, hi))
+        if plan.moments_size(b.shape[1]) > 0:
+            # each rank interpolates the sources of its own slice onto the finest-level nodes; the moment
+            # arrays (zero outside the slice) are summed over NVLink, so nobody passes over all sources
+            mom = plan.moments(b, (lo, hi))
+            dist.all_reduce(mom, group=group)
+            out = plan.apply(b, row_range=(lo, hi), moments=mom)
+        else:
+            out = plan.apply(b, row_range=(lo, hi))
         plan.close()
     else:
         out = compute(X, b, lo, hi)

@@ -95,6 +95,18 @@ int f3m_plan_create(f3m_plan **plan, const float *X, int64_t N, const float *Y, 
 int f3m_plan_apply(f3m_plan *plan, const float *b, int32_t R, float *out, void *stream);
 int f3m_plan_apply_range(f3m_plan *plan, const float *b, int32_t R, float *out, int64_t row_begin,
                          int64_t row_end, void *stream);
+/* Sharing box moments between GPUs (no counterpart in the reference, whose multi-GPU mode is independent
+ * processes: experiments/FFM_classes.py:128-211).  Every rank holds the same plan.  f3m_plan_moments_range
+ * computes the finest-level moments of the source boxes that start inside [src_begin, src_end) of the sorted
+ * order into mom_out (nfloats floats from f3m_plan_moments_size, zero for all other boxes); the caller sums the
+ * arrays of all ranks (an all-reduce over NVLink) and passes the result to f3m_plan_apply_range_moments, which
+ * then skips its own pass over the sources.  nfloats == 0 means this plan cannot exchange moments (node counts
+ * change between levels, more than 8 nodes per dimension, or more than 8 columns): use f3m_plan_apply_range. */
+int f3m_plan_moments_size(const f3m_plan *plan, int32_t R, int64_t *nfloats);
+int f3m_plan_moments_range(f3m_plan *plan, const float *b, int32_t R, int64_t src_begin, int64_t src_end,
+                           float *mom_out, void *stream);
+int f3m_plan_apply_range_moments(f3m_plan *plan, const float *b, int32_t R, float *out, int64_t row_begin,
+                                 int64_t row_end, const float *mom, void *stream);
 int f3m_plan_destroy(f3m_plan *plan);
 
 /* -------- introspection (parity checks and work accounting) ------------------------------ */

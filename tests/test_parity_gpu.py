@@ -146,6 +146,26 @@ def test_row_range_shards_sum_to_full(cuda):
     assert rel_l2(parts.cpu(), full.cpu()) <= 1e-6
 
 
+@pytest.mark.parametrize("name", ["u3_shared", "n4_r8", "u3_xy"])
+def test_sharded_moments_and_rows_sum_to_full(name, cuda):
+    """The multi-GPU decomposition on one GPU: two "ranks" each interpolate their slice of the sources onto
+    the finest-level nodes, the moment arrays are added (the all-reduce), and each computes its slice of the
+    target boxes from the summed moments; the two outputs add up to the full product."""
+    from f3m_b200 import engine
+    c = make_case(name)
+    prm = engine.make_params(c["ls"], c["min_points"], c["P"], c["var_comp"], c["eff"], c["small"])
+    X = c["X"].to(cuda)
+    Y = None if c["Y"] is None else c["Y"].to(cuda)
+    plan = engine.Plan(X, Y, prm)
+    b = c["b"].to(cuda)
+    full = plan.apply(b)
+    assert plan.moments_size(c["R"]) > 0
+    N, M = plan.N, plan.M
+    mom = plan.moments(b, (0, M // 3)) + plan.moments(b, (M // 3, M))
+    parts = plan.apply(b, row_range=(0, N // 2), moments=mom) + plan.apply(b, row_range=(N // 2, N), moments=mom)
+    assert rel_l2(parts.cpu(), full.cpu()) <= 2e-6
+
+
 def test_dense_ops(cuda):
     from f3m_b200 import engine
     from oracle.f3m_oracle import dense_kmvm_f64

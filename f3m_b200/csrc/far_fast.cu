@@ -126,20 +126,25 @@ static KronCfg make_kron_cfg(int d, int p, int RB) {
 // matrix of the stage into registers once, then p inputs -> p outputs per fibre.  With ACC_REG the
 // outputs of the last stage are accumulated in registers (possible when a stage has at most 64 fibres,
 // i.e. two rounds per lane); otherwise in the warp's shared-memory accumulator.
-template <int PP, bool ACC_REG>
+__host__ __device__ constexpr int cpow(int b, int e) { return e <= 0 ? 1 : b * cpow(b, e - 1); }
+
+// DD > 0: dimension known at compile time and one column (RB = 1): every stride is a constant, so the
+// index arithmetic folds into immediate offsets.  DD = 0: dimension and column block taken from cfg.
+template <int PP, bool ACC_REG, int DD>
 __device__ __forceinline__ void warp_kron(const float *src0, float *bufA, float *bufB, float *acc_sm,
                                           float (&acc_reg)[2][PP], float &acc_left, const float *const (&mats)[MAXD],
                                           const KronCfg &cfg, int lane) {
     constexpr int MS = mat_stride(PP);
     const float *src = src0;
     float *dst = bufA;
-    const int nf = cfg.nf;
+    const int nf = DD ? cpow(PP, DD - 1) : cfg.nf;
+    const int dd = DD ? DD : cfg.d;
 #pragma unroll
     for (int k = 0; k < MAXD; k++) {
-        if (k < cfg.d) {
-            const bool last = (k == cfg.d - 1);
-            const int st = cfg.st[k];
-            const float inv = cfg.inv_st[k];
+        if (k < dd) {
+            const bool last = (k == dd - 1);
+            const int st = DD ? cpow(PP, k) : cfg.st[k];
+            const float inv = DD ? 1.0f / (float)cpow(PP, k) : cfg.inv_st[k];
             float M[MS];
             const float4 *M4 = reinterpret_cast<const float4 *>(mats[k]);
 #pragma unroll
@@ -148,7 +153,7 @@ __device__ __forceinline__ void warp_kron(const float *src0, float *bufA, float 
                 M[4 * q] = v.x; M[4 * q + 1] = v.y; M[4 * q + 2] = v.z; M[4 * q + 3] = v.w;
             }
             auto fibre = [&](int f, float *areg) {
-                const int hi = last ? 0 : __float2int_rz(((float)f + 0.5f) * inv);
+                const int hi = last ? 0 : (DD ? f / st : __float2int_rz(((float)f + 0.5f) * inv));
                 const int base = hi * st * PP + (f - hi * st);
                 float v[PP];
 #pragma unroll
@@ -170,7 +175,7 @@ __device__ __forceinline__ void warp_kron(const float *src0, float *bufA, float 
                     // a short second round (e.g. 36 fibres): one OUTPUT per lane instead of one fibre per lane
                     if (lane < left * PP) {
                         const int lf = lane / PP, i = lane - lf * PP, f = 32 + lf;
-                        const int hi = last ? 0 : __float2int_rz(((float)f + 0.5f) * inv);
+                        const int hi = last ? 0 : (DD ? f / st : __float2int_rz(((float)f + 0.5f) * inv));
                         const int base = hi * st * PP + (f - hi * st);
                         const float *mrow = mats[k] + i * PP;
                         float o = 0.f;
@@ -194,7 +199,7 @@ __device__ __forceinline__ void warp_kron(const float *src0, float *bufA, float 
 template <int PP>
 __device__ __forceinline__ void flush_acc(float (&acc_reg)[2][PP], float acc_left, float *acc_sm, const KronCfg &cfg,
                                           int lane) {
-    const int st = cfg.st[cfg.d - 1];
+    const int st = cfg.st[cfg.d - 1];   // for one column this equals the number of fibres
     const int left = cfg.nf - 32;
     const bool short_round = left > 0 && left * PP <= 32;
 #pragma unroll
@@ -230,7 +235,7 @@ __device__ __forceinline__ void decode_cell2(uint32_t code, int level, int d, in
 // ---------------------------------------------------------------------------------------------
 // M2L: one CTA per target box, its warps share the far row
 // ---------------------------------------------------------------------------------------------
-template <int PP, bool ACC_REG>
+template <int PP, bool ACC_REG, int DD>
 __global__ void __launch_bounds__(128, 5) m2l_fast(int nbx, int d, const int *__restrict__ fptr, const int *__restrict__ fidx,
                                                const int *__restrict__ cell_x, const int *__restrict__ cell_y,
                                                const int *__restrict__ off_x, int row_begin, int row_end,
@@ -272,7 +277,7 @@ __global__ void __launch_bounds__(128, 5) m2l_fast(int nbx, int d, const int *__
             mats[k] = Tsm + (k * NOFF2 + o) * MS;
         }
         if (!ok) { if (lane == 0) atomicExch(err, 2); continue; }
-        warp_kron<PP, ACC_REG>(mom + (size_t)by * PR, bufA, bufB, acc, acc_reg, acc_left, mats, cfg, lane);
+        warp_kron<PP, ACC_REG, DD>(mom + (size_t)by * PR, bufA, bufB, acc, acc_reg, acc_left, mats, cfg, lane);
     }
     if (ACC_REG) flush_acc<PP>(acc_reg, acc_left, acc, cfg, lane);
     __syncthreads();
@@ -306,7 +311,7 @@ __global__ void __launch_bounds__(128) m2m_fast(int nbp, int d, const int *__res
         const float *mats[MAXD];
 #pragma unroll
         for (int k = 0; k < MAXD; k++) mats[k] = Asm + ((code >> k) & 1u) * MS;
-        warp_kron<PP, false>(mom_child + (size_t)c * PR, bufA, bufB, acc, acc_reg, acc_left, mats, cfg, lane);
+        warp_kron<PP, false, 0>(mom_child + (size_t)c * PR, bufA, bufB, acc, acc_reg, acc_left, mats, cfg, lane);
     }
     __syncthreads();
     for (int q = threadIdx.x; q < PR; q += blockDim.x) {
@@ -341,7 +346,7 @@ __global__ void __launch_bounds__(128) l2l_fast(int nbc, int d, const int *__res
 #pragma unroll
     for (int k = 0; k < MAXD; k++) mats[k] = Asm + ((code >> k) & 1u) * MS;
     float acc_reg[2][PP], acc_left = 0.f;
-    warp_kron<PP, false>(loc_parent + (size_t)parent[c] * PR, bufA, bufB, acc, acc_reg, acc_left, mats, cfg, lane);
+    warp_kron<PP, false, 0>(loc_parent + (size_t)parent[c] * PR, bufA, bufB, acc, acc_reg, acc_left, mats, cfg, lane);
     for (int q = lane; q < PR; q += 32) loc_child[(size_t)c * PR + q] += acc[q];
 }
 
@@ -351,21 +356,25 @@ __global__ void __launch_bounds__(128) l2l_fast(int nbc, int d, const int *__res
 // Barycentric Lagrange basis (lagrange_data_load + calculate_barycentric_lagrange, 1_d_conv.cu:217-238, 418-448)
 template <int PP>
 __device__ __forceinline__ void lagrange_pp(float t, const NodeTab2 &nt, float *L) {
+    // q_i = w_i / (t - t_i) with the fast reciprocal (2 ulp): L_i = q_i / sum_l q_l.  The reference's kernels are
+    // built with --use_fast_math, so their divisions are the approximate ones too.
     int hit = -1;
     float sum = 0.f;
+    float q[PP];
 #pragma unroll
     for (int i = 0; i < PP; i++) {
-        float diff = t - nt.node[i];
+        const float diff = t - nt.node[i];
         if (diff == 0.f) hit = i;
-        else sum += nt.w[i] / diff;
+        q[i] = __fdividef(nt.w[i], diff);
+        sum += q[i];
     }
     if (hit >= 0) {
 #pragma unroll
         for (int i = 0; i < PP; i++) L[i] = (i == hit) ? 1.f : 0.f;
     } else {
-        const float lx = 1.f / sum;
+        const float lx = __fdividef(1.f, sum);
 #pragma unroll
-        for (int i = 0; i < PP; i++) L[i] = (lx * nt.w[i]) / (t - nt.node[i]);
+        for (int i = 0; i < PP; i++) L[i] = lx * q[i];
     }
 }
 
@@ -597,8 +606,20 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
         const int nw = warps_for(tab);
         size_t smem = tab + nw * per_warp;
         const bool acc_reg = cfg.nf <= 64;
-        if (acc_reg) F3M_CUDA(cudaFuncSetAttribute(m2l_fast<PP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        else F3M_CUDA(cudaFuncSetAttribute(m2l_fast<PP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // launcher: static strides for d = 2, 3 with one column, runtime strides otherwise
+        auto launch_m2l = [&](int nbx, const int *fptr, const int *fidx, const int *cx, const int *cy, const int *offx,
+                              const Geom2 &geo, const float *momL, float *locL) {
+#define F3M_M2L_CALL(ACC_, DD_)                                                                                          \
+    {                                                                                                                    \
+        F3M_CUDA(cudaFuncSetAttribute(m2l_fast<PP, ACC_, DD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        m2l_fast<PP, ACC_, DD_><<<nbx, 32 * nw, smem, s>>>(nbx, d, fptr, fidx, cx, cy, offx, rb, re, T.p, geo, cfg, momL,  \
+                                                          locL, pl->d_flags);                                            \
+    }
+            if (RB == 1 && d == 3) { if (acc_reg) F3M_M2L_CALL(true, 3) else F3M_M2L_CALL(false, 3) }
+            else if (RB == 1 && d == 2) { if (acc_reg) F3M_M2L_CALL(true, 2) else F3M_M2L_CALL(false, 2) }
+            else { if (acc_reg) F3M_M2L_CALL(true, 0) else F3M_M2L_CALL(false, 0) }
+#undef F3M_M2L_CALL
+        };
         DevBuf<int> cellx, celly;
         for (int l = lmin; l <= L; l++) {
             LevelLists &ll = pl->lists[l];
@@ -624,12 +645,7 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
                 F3M_LAUNCH_CHECK();
                 cy = celly.p;
             }
-            if (acc_reg)
-                m2l_fast<PP, true><<<lx.nb, 32 * nw, smem, s>>>(lx.nb, d, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, lx.off.p, rb, re,
-                                                               T.p, geo, cfg, momp[l], loc[l].p, pl->d_flags);
-            else
-                m2l_fast<PP, false><<<lx.nb, 32 * nw, smem, s>>>(lx.nb, d, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, lx.off.p, rb, re,
-                                                                T.p, geo, cfg, momp[l], loc[l].p, pl->d_flags);
+            launch_m2l(lx.nb, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, lx.off.p, geo, momp[l], loc[l].p);
             F3M_LAUNCH_CHECK();
         }
     }

@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(256) morton_kernel(const float *__restrict__ X
 // (digit, block) matrix, stable scatter with warp-level multi-split ranking.
 // ---------------------------------------------------------------------------------------------
 constexpr int RS_THREADS = 256;
-constexpr int RS_ITEMS = 16;
+constexpr int RS_ITEMS = 8;
 constexpr int RS_WARPS = RS_THREADS / 32;
 constexpr int RS_TILE = RS_THREADS * RS_ITEMS;
 
@@ -392,7 +392,7 @@ void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *o
     }
     F3M_LAUNCH_CHECK();
 
-    int G = (int)std::min<int64_t>((n + RS_TILE - 1) / RS_TILE, NUM_SMS_HINT * 4);
+    int G = (int)std::min<int64_t>((n + RS_TILE - 1) / RS_TILE, NUM_SMS_HINT * 10);
     if (G < 1) G = 1;
     int64_t chunk = (n + G - 1) / G;
     chunk = (chunk + RS_TILE - 1) / RS_TILE * RS_TILE;

@@ -1,3 +1,3 @@
 """`import FFM_classes` as experiments/run_obj.py:1 of the reference writes it."""
 from f3m_b200.FFM_classes import *  # noqa: F401,F403
-from f3m_b200.FFM_classes import FFM, benchmark_matmul, benchmark_matmul_double, block_FFM_matmul  # noqa: F401
+from f3m_b200.FFM_classes import FFM, benchmark_matmul, benchmark_matmul_double, block_FFM_matmul, par_FFM_block  # noqa: F401

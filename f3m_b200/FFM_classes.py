@@ -8,6 +8,7 @@ with the same constructor arguments, methods and error behaviour, running on lib
   benchmark_matmul(X, Y, ls, device) @ b      experiments/FFM_classes.py:264-323 (exact dense op, float32)
   benchmark_matmul_double(...)                experiments/FFM_classes.py:325-383 (float64)
   block_FFM_matmul(...)                       experiments/FFM_classes.py:385-435
+  par_FFM_block(...)                          experiments/FFM_classes.py:128-211
 
 Differences, all on purpose: pykeops is not needed at import; a product whose X and Y are the tensors
 given at construction reuses the tree and the interaction lists between calls (the reference rebuilds
@@ -141,30 +142,93 @@ class benchmark_matmul_double(benchmark_matmul):
     _dtype = torch.float64
 
 
-class block_FFM_matmul:
-    """2-D blocked product accumulated on the host (experiments/FFM_classes.py:385-435): K is split into
-    blocks x blocks tiles and each tile is one product of its own."""
+class block_FFM_matmul(FFM):
+    """Blocked product accumulated on the host (experiments/FFM_classes.py:385-435): K is split into
+    blocks_X x blocks_Y tiles and each tile is one product of its own.  (The reference passes None as Y on
+    diagonal blocks, which its own forward cannot handle; here diagonal blocks use the shared-tree product.)"""
 
     def __init__(self, X, Y=None, ls=1.0, min_points=1000, nr_of_interpolation=64, eff_var_limit=0.15,
-                 var_compression=False, small_field_points=1000, device="cuda:0", blocks=2):
-        self.X = X.float()
-        self.Y = Y.float() if torch.is_tensor(Y) else self.X
-        self.kw = dict(ls=ls, min_points=min_points, nr_of_interpolation=nr_of_interpolation, eff_var_limit=eff_var_limit,
-                       var_compression=var_compression, small_field_points=small_field_points, device=device)
-        self.blocks = blocks
-        self.device = device
+                 var_compression=False, small_field_points=1000, device="cuda:0", blocks_X=1, blocks_Y=1):
+        super().__init__(X=X, Y=Y, ls=ls, min_points=min_points, nr_of_interpolation=nr_of_interpolation,
+                         eff_var_limit=eff_var_limit, var_compression=var_compression,
+                         small_field_points=small_field_points, device=device)
+        self.blocks_X = blocks_X
+        self.blocks_Y = blocks_Y
+        self._xy_mode = torch.is_tensor(Y)
 
     def __matmul__(self, b):
-        b = b.float()
-        xs = torch.chunk(self.X, self.blocks, 0)
-        ys = torch.chunk(self.Y, self.blocks, 0)
-        bs = torch.chunk(b, self.blocks, 0)
-        rows = []
-        for xc in xs:
-            acc = torch.zeros(xc.shape[0], b.shape[1])
-            for yc, bc in zip(ys, bs):
-                same = yc.data_ptr() == xc.data_ptr() and yc.shape == xc.shape
-                op = FFM(xc, None if same else yc, **self.kw)
-                acc += (op @ bc).cpu()
-            rows.append(acc)
-        return torch.cat(rows, 0)
+        b = b.float().to(self.device)
+        out = []
+        if self._xy_mode:
+            ys = torch.chunk(self.Y, self.blocks_Y, dim=0)
+            bs = torch.chunk(b, self.blocks_Y, dim=0)
+            for x in torch.chunk(self.X, self.blocks_X, dim=0):
+                acc = torch.zeros(x.shape[0], b.shape[1])
+                for y, bc in zip(ys, bs):
+                    acc += self.forward(x.contiguous(), y.contiguous(), bc.contiguous()).cpu()
+                out.append(acc)
+        else:
+            xs = [x.contiguous() for x in torch.chunk(self.X, self.blocks_X, dim=0)]
+            bs = torch.chunk(b, self.blocks_X, dim=0)
+            for i, x in enumerate(xs):
+                acc = torch.zeros(x.shape[0], b.shape[1])
+                for j, y in enumerate(xs):
+                    acc += self.forward(x, x if i == j else y, bs[j].contiguous()).cpu()
+                out.append(acc)
+        return torch.cat(out, dim=0)
+
+
+class par_FFM_block:
+    """Independent block products spread over several GPUs (experiments/FFM_classes.py:128-211): K is cut
+    into len(devices) x len(devices) blocks, block (x_i, y_j) runs on devices[i], and calling the object
+    returns the list of block results in the reference's job order (outer loop over y blocks, inner over x
+    blocks) without summing them, as the reference does.  One host thread per device instead of one
+    process per device; for a product that is summed and sharded by target boxes see f3m_b200.parallel."""
+
+    def __init__(self, X, b, Y=None, ls=1.0, min_points=1000, nr_of_interpolation=64, eff_var_limit=0.15,
+                 var_compression=False, small_field_points=1000, devices=(0,)):
+        self.X = X.float()
+        self.b = b.float()
+        self.Y = Y.float() if torch.is_tensor(Y) else self.X
+        self.d = self.X.shape[1]
+        if not 1 <= self.d <= MAX_DIM:
+            raise ValueError(f"dimension {self.d} not supported (1..{MAX_DIM})")
+        self.ls, self.min_points = float(ls), float(min_points)
+        self.nr_of_interpolation, self.eff_var_limit = int(nr_of_interpolation), float(eff_var_limit)
+        self.var_compression, self.small_field_points = var_compression, small_field_points
+        self.devices = list(devices)
+        self.par_fac = len(self.devices)
+        ys = torch.chunk(self.Y, self.par_fac, dim=0)
+        xs = torch.chunk(self.X, self.par_fac, dim=0)
+        bs = torch.chunk(self.b, self.par_fac, dim=0)
+        self.jobs_list = [(x.clone(), y.clone(), bb.clone(), dev) for y, bb in zip(ys, bs) for x, dev in zip(xs, self.devices)]
+
+    def update_ls(self, ls):
+        if not ls > 0:
+            raise AssertionError("ls must be positive")
+        self.ls = float(ls)
+
+    def forward(self, X, Y, b, device):
+        dev = torch.device("cuda", int(device))
+        X, Y, b = X.to(dev), Y.to(dev), b.to(dev)
+        if not (Y.shape[1] == X.shape[1] and Y.shape[0] == b.shape[0]):
+            raise AssertionError("shapes of X, Y and b do not match")
+        prm = engine.make_params(self.ls, self.min_points, self.nr_of_interpolation, self.var_compression,
+                                 self.eff_var_limit, self.small_field_points)
+        with torch.cuda.device(dev):
+            return engine.kmvm(X, Y, b, prm)
+
+    def __call__(self):
+        from concurrent.futures import ThreadPoolExecutor
+        results = [None] * len(self.jobs_list)
+        by_device = {}
+        for k, job in enumerate(self.jobs_list):
+            by_device.setdefault(job[3], []).append(k)
+
+        def run(keys):
+            for k in keys:
+                results[k] = self.forward(*self.jobs_list[k])
+
+        with ThreadPoolExecutor(max_workers=len(by_device)) as ex:
+            list(ex.map(run, by_device.values()))
+        return results

@@ -4,7 +4,7 @@ from . import _lib
 
 _lib.lib()   # no fallback: a missing library is an import error
 
-from .FFM_classes import FFM, benchmark_matmul, benchmark_matmul_double, block_FFM_matmul  # noqa: E402
+from .FFM_classes import FFM, benchmark_matmul, benchmark_matmul_double, block_FFM_matmul, par_FFM_block  # noqa: E402
 from . import engine  # noqa: E402
 
-__all__ = ["FFM", "benchmark_matmul", "benchmark_matmul_double", "block_FFM_matmul", "engine"]
+__all__ = ["FFM", "benchmark_matmul", "benchmark_matmul_double", "block_FFM_matmul", "par_FFM_block", "engine"]

@@ -207,6 +207,18 @@ def test_operator_surface(cuda):
     full = opxy @ by
     chunked = opxy.chunk_forward_example(by, chunks=3)
     assert rel_l2(chunked.cpu(), full.cpu()) <= 1e-4
+    # blocked products (block_FFM_matmul, par_FFM_block) against the single product
+    from F3M_src.FFM_classes import block_FFM_matmul, par_FFM_block
+    blk = block_FFM_matmul(X, ls=1.0, min_points=500, nr_of_interpolation=64, small_field_points=64, device="cuda:0", blocks_X=2)
+    assert rel_l2(blk @ b, res.cpu()) <= 1e-4
+    blkxy = block_FFM_matmul(X, Y, ls=1.0, min_points=500, nr_of_interpolation=64, small_field_points=64, device="cuda:0",
+                             blocks_X=2, blocks_Y=3)
+    assert rel_l2(blkxy @ by, full.cpu()) <= 1e-4
+    par = par_FFM_block(X, b, ls=1.0, min_points=500, nr_of_interpolation=64, small_field_points=64, devices=[0, 0])
+    parts = par()
+    assert len(parts) == 4
+    top = parts[0].cpu() + parts[2].cpu()          # row block 0: source blocks 0 and 1
+    assert rel_l2(top, res[:top.shape[0]].cpu()) <= 1e-4
     with pytest.raises(AssertionError):
         opxy.forward(opxy.X, opxy.Y, torch.randn(5, 1, device="cuda:0"))
     with pytest.raises(AssertionError):

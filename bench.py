@@ -242,11 +242,11 @@ def main():
         slots_per_pair = 2 * 3 + 1 + 1                      # 2d + 1 + R FP32 issue slots, plus one exponential
         peak_pairs = min(peaks["gfma_per_s"] / slots_per_pair, peaks["gexp_per_s"]) * 1e9
         achieved_pairs = st["direct_pairs"] / (direct_ms * 1e-3)
-        line["roofline"] = {"bound": "fp32-issue+sfu (not hbm, not tensor: distance + exponential, no contraction)",
+        line["roofline"] = {"bound": "sfu+fp32-issue", "bound_note": "not hbm, not tensor: distance + exponential, no contraction; a source row is reused by every target of a tile",
                             "achieved": achieved_pairs * flop_per_pair / 1e12, "peak": peak_pairs * flop_per_pair / 1e12,
                             "unit": "TFLOP/s", "frac": achieved_pairs / peak_pairs,
-                            # DRAM bytes per launch from the ncu capture of this kernel at N=1e7 (profiles/near_kernel_exp_c2_1e7.md:
-                            # 377 MB = 37.7 B per point), scaled by N: the traffic is per point (sources, targets, output)
+                            # DRAM bytes per launch from an ncu capture of this kernel at N=1e7 (377 MB = 37.7 B per point),
+                            # scaled by N: the traffic is per point (sources, targets, output)
                             "traffic": 37.7 * N, "traffic_note": "37.7 B/point from the ncu capture at N=1e7, scaled to N; algorithmic minimum 36 B/point",
                             "kernel": "near_kernel_exp<3,1,32,POLY> (all direct-sum launches of one product; a third of the exponentials run as a polynomial on the FMA pipe when the exponent is provably small)",
                             "pairs": st["direct_pairs"], "ms": direct_ms, "launches": tm["direct_launches"],

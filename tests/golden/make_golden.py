@@ -4,7 +4,7 @@ The reference has no CPU path, so it cannot run where it is built: oracle/Makefi
 sm_100a from the reference's own sources into oracle/_ref/f3m_ref_d3.so, and this script is run on a
 machine with a B200:
 
-    python tests/golden/make_golden.py [out_dir]      # default out_dir: gpurun_out/golden
+    python tests/golden/make_golden.py [out_dir]      # default out_dir: ./golden_out ; copy the files here afterwards
 
 For every seeded case of tests/cases.py listed in GOLDEN_CASES it stores, per level, the reference's
 box offsets (unique_counts_cum_reindexed), box centres, the box of every point at the finest level,
@@ -48,7 +48,7 @@ def canon(pairs):
 
 
 def main():
-    out_dir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden")
+    out_dir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "golden_out")
     os.makedirs(out_dir, exist_ok=True)
     ref = load_ref(3)
     dev = "cuda:0"

@@ -3,7 +3,7 @@
 Bit-exact: per-level box offsets / counts, box centres, far / small / keep pair lists (engine in
 IEEE mode vs the oracle's IEEE float32 arithmetic).  Floating point: KMVM output within rel-L2
 1e-5 of the oracle's output and no worse than the oracle against the exact float64 product
-(tolerances are the ones BASELINE.json's north_star states)."""
+(rel-L2 1e-5 against the reference algorithm at equal nodes and leaf size is the tolerance this engine is specified to)."""
 import numpy as np
 import pytest
 import torch

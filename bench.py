@@ -258,8 +258,25 @@ def main():
         rows = torch.randperm(N, device=dev, generator=g)[:a.check_rows]
         exact = engine.rbf_dense(Xs[rows].double(), Xs.double(), bs.double(), a.ls)
         line["rel_l2_vs_f64"] = float((out[rows].double() - exact).norm() / exact.norm())
-        del exact
         plan.close()
+        # ---- the same product with the optional moment form of the near field (not the headline: `value` above is
+        # the default path, whose near field is the direct sum) ---------------------------------------------------
+        from f3m_b200 import _lib as f3m_lib
+        prm_m = engine.make_params(a.ls, a.min_points, a.nodes, False, 0.15, a.nodes, flags=f3m_lib.FLAG_NEAR_MOMENTS)
+        for _ in range(2):
+            out_m = engine.kmvm(Xs, None, bs, prm_m)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.steps):
+            out_m = engine.kmvm(Xs, None, bs, prm_m)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_m = e0.elapsed_time(e1) / a.steps
+        line["near_moments_mode"] = {"ms_per_step": ms_m, "value": float(N) * float(N) / (ms_m * 1e-3), "unit": UNIT,
+                                     "rel_l2_vs_f64": float((out_m[rows].double() - exact).norm() / exact.norm()),
+                                     "note": "F3M_FLAG_NEAR_MOMENTS: near sums from 2nd/3rd-order box moments where the exponent "
+                                             "is provably tiny; same pair lists; optional, off by default"}
+        del exact, out_m
         # ---- end to end through the host-buffer entry point ------------------------------------------------------
         Xh = torch.empty(N, 3, pin_memory=True).copy_(Xs)
         bh = torch.empty(N, 1, pin_memory=True).copy_(bs)

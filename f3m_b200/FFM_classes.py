@@ -19,14 +19,17 @@ from __future__ import annotations
 import torch
 
 from . import engine
-from ._lib import MATH_FASTMATH
+from ._lib import MATH_FASTMATH, FLAG_NEAR_MOMENTS
 
 MAX_DIM = 5
 
 
 class FFM:
     def __init__(self, X, Y=None, ls=1.0, min_points=1000, nr_of_interpolation=64, eff_var_limit=0.15,
-                 var_compression=False, small_field_points=1000, device="cuda:0", math_mode=MATH_FASTMATH):
+                 var_compression=False, small_field_points=1000, device="cuda:0", math_mode=MATH_FASTMATH,
+                 near_moments=False):
+        # math_mode and near_moments are additions to the reference's arguments: the numeric flavour of the box
+        # index / far test, and the optional evaluation of near sums by box moments (see include/f3m.h)
         self.X = X.float().to(device)
         if torch.is_tensor(Y):
             self.Y = Y.float().to(device)
@@ -43,13 +46,15 @@ class FFM:
         self.device = device
         self.small_field_points = small_field_points
         self.math_mode = math_mode
+        self.near_moments = bool(near_moments)
         self._plan = None
         self._plan_key = None
 
     # ---- parameters ----------------------------------------------------------------------------
     def _params(self):
         return engine.make_params(self.ls, self.min_points, self.nr_of_interpolation, self.var_compression,
-                                  self.eff_var_limit, self.small_field_points, self.math_mode)
+                                  self.eff_var_limit, self.small_field_points, self.math_mode,
+                                  flags=FLAG_NEAR_MOMENTS if self.near_moments else 0)
 
     def update_ls(self, ls):
         if not ls > 0:
@@ -77,7 +82,7 @@ class FFM:
         Y = self.Y if Y is None else Y
         key = (X.data_ptr(), X._version, tuple(X.shape), Y.data_ptr(), Y._version, tuple(Y.shape), self.ls,
                self.min_points, self.nr_of_interpolation, self.eff_var_limit, bool(self.var_compression),
-               self.small_field_points, self.math_mode)
+               self.small_field_points, self.math_mode, self.near_moments)
         if self._plan is None or self._plan_key != key:
             if self._plan is not None:
                 self._plan.close()

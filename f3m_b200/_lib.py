@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libf3m.so")
 
 MATH_FASTMATH = 0
 MATH_IEEE = 1
+FLAG_NEAR_MOMENTS = 1
 
 # array ids of f3m_plan_copy_array
 ARR_SORTED_INDEX, ARR_BOX_OFFSETS, ARR_BOX_CENTERS = 0, 1, 2
@@ -29,7 +30,7 @@ class F3MError(RuntimeError):
 class Params(C.Structure):
     _fields_ = [("ls", C.c_float), ("min_points", C.c_float), ("nr_interpolation", C.c_int32),
                 ("var_compression", C.c_int32), ("eff_var_limit", C.c_float), ("small_field_points", C.c_int32),
-                ("math_mode", C.c_int32), ("reserved", C.c_int32)]
+                ("math_mode", C.c_int32), ("flags", C.c_int32)]
 
 
 class LevelInfo(C.Structure):

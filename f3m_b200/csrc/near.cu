@@ -310,6 +310,146 @@ __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__
     tiles[b] = t;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Moment form of the near field (optional, F3M_FLAG_NEAR_MOMENTS).  In the expanded form the pair term
+// is fx_i * 2^(t_ij) * w_j with t_ij = xr_i . Y_j.  When |t| is provably small for every pair of a list
+// (boxes much smaller than the lengthscale), 2^t = 1 + c1 t + c2 t^2 (+ c3 t^3) to within 5e-7 / 1e-6
+// relative, and the sum over the sources of a box collapses into moments of that box that do not depend on
+// the target:   sum_j w_j 2^(t_ij) = M0 + c1 xr.M1 + c2 xr^T M2 xr (+ c3 M3[xr,xr,xr]).
+// The near sum of a target then costs ~20 multiply-adds per source BOX instead of ~6 issue slots per source
+// POINT.  The pair lists are untouched; only the way their sums are evaluated changes, with a truncation error
+// of the size of the ex2.approx error.  Lists whose exponent bound is larger keep the direct kernels.
+// ---------------------------------------------------------------------------------------------
+template <int D, int ORD>
+struct MomLayout {
+    static constexpr int N2 = D * (D + 1) / 2;
+    static constexpr int N3 = ORD >= 3 ? D * (D + 1) * (D + 2) / 6 : 0;
+    static constexpr int NM = 1 + D + N2 + N3;
+};
+
+// one warp per (source box, column)
+template <int D, int ORD>
+__global__ void __launch_bounds__(256) near_moments_kernel(const float *__restrict__ pts, int n, const float *__restrict__ bs,
+                                                          int R, float scale, const int *__restrict__ off_y, int nby,
+                                                          const float *__restrict__ ctr_y, float *mom) {
+    using ML = MomLayout<D, ORD>;
+    constexpr float C1 = 0.69314718056f, C2 = 0.24022650696f, C3 = 0.05550410866f;
+    const int lane = threadIdx.x & 31;
+    const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wid >= nby * R) return;
+    const int by = wid / R, r = wid - by * R;
+    float c[D];
+#pragma unroll
+    for (int k = 0; k < D; k++) c[k] = ctr_y[by * D + k];
+    float acc[ML::NM];
+#pragma unroll
+    for (int q = 0; q < ML::NM; q++) acc[q] = 0.f;
+    for (int j = off_y[by] + lane; j < off_y[by + 1]; j += 32) {
+        float Y[D], ny = 0.f;
+#pragma unroll
+        for (int k = 0; k < D; k++) {
+            const float yr = scale * (pts[(size_t)k * n + j] - c[k]);
+            ny = fmaf(-yr, yr, ny);
+            Y[k] = 2.f * yr;
+        }
+        const float w = bs[(size_t)j * R + r] * ex2_approx(ny);
+        acc[0] += w;
+        int q2 = 1 + D, q3 = 1 + D + ML::N2;
+#pragma unroll
+        for (int a = 0; a < D; a++) {
+            const float wa = w * Y[a];
+            acc[1 + a] += wa;
+#pragma unroll
+            for (int b = a; b < D; b++) {
+                const float wab = wa * Y[b];
+                acc[q2++] += wab;
+                if (ORD >= 3) {
+#pragma unroll
+                    for (int cc = b; cc < D; cc++) { acc[q3] = fmaf(wab, Y[cc], acc[q3]); q3++; }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < ML::NM; q++) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[q] += __shfl_xor_sync(0xffffffffu, acc[q], o);
+    }
+    if (lane == 0) {
+        // fold the Taylor coefficients and the multiplicities of the symmetric tensors into the stored moments
+        float *m = mom + (size_t)wid * ML::NM;
+        m[0] = acc[0];
+        int q2 = 1 + D, q3 = 1 + D + ML::N2;
+#pragma unroll
+        for (int a = 0; a < D; a++) {
+            m[1 + a] = C1 * acc[1 + a];
+#pragma unroll
+            for (int b = a; b < D; b++) {
+                m[q2] = C2 * (a == b ? 1.f : 2.f) * acc[q2];
+                q2++;
+                if (ORD >= 3) {
+#pragma unroll
+                    for (int cc = b; cc < D; cc++) {
+                        const float mult = (a == b && b == cc) ? 1.f : ((a == b || b == cc) ? 3.f : 6.f);
+                        m[q3] = C3 * mult * acc[q3];
+                        q3++;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// one thread per target; items = (target box, tile of 128 targets)
+template <int D, int ORD>
+__global__ void __launch_bounds__(128) near_taylor_kernel(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
+                                                         int nbx, const int *__restrict__ tile_off,
+                                                         const int *__restrict__ ptr, const int *__restrict__ idx,
+                                                         const float *__restrict__ ctr_y, const float *__restrict__ mom,
+                                                         float scale, int R, float *out) {
+    using ML = MomLayout<D, ORD>;
+    int box, t0, t1;
+    item_to_tile(blockIdx.x, tile_off, nbx, off_x, box, t0, t1);
+    const int i = t0 + threadIdx.x;
+    if (i >= t1) return;
+    float x[D];
+#pragma unroll
+    for (int k = 0; k < D; k++) x[k] = xpts[(size_t)k * n_x + i];
+    const int e0 = ptr[box], e1 = ptr[box + 1];
+    for (int r = 0; r < R; r++) {
+        float tot = 0.f;
+        for (int e = e0; e < e1; e++) {
+            const int by = idx[e];
+            float xr[D], nx = 0.f;
+#pragma unroll
+            for (int k = 0; k < D; k++) {
+                xr[k] = scale * (x[k] - __ldg(ctr_y + by * D + k));
+                nx = fmaf(-xr[k], xr[k], nx);
+            }
+            const float *m = mom + ((size_t)by * R + r) * ML::NM;
+            float poly = __ldg(m);
+            int q2 = 1 + D, q3 = 1 + D + ML::N2;
+#pragma unroll
+            for (int a = 0; a < D; a++) {
+                float s1 = __ldg(m + 1 + a);
+#pragma unroll
+                for (int b = a; b < D; b++) {
+                    float s2 = __ldg(m + q2);
+                    q2++;
+                    if (ORD >= 3) {
+#pragma unroll
+                        for (int cc = b; cc < D; cc++) { s2 = fmaf(xr[cc], __ldg(m + q3), s2); q3++; }
+                    }
+                    s1 = fmaf(xr[b], s2, s1);
+                }
+                poly = fmaf(xr[a], s1, poly);
+            }
+            tot = fmaf(ex2_approx(nx), poly, tot);
+        }
+        out[(size_t)i * R + r] += tot;
+    }
+}
+
 static inline float near_scale(float lcs) { return sqrtf(lcs * 1.4426950408889634f); }
 
 // one list, one block of RB columns starting at r0
@@ -365,9 +505,47 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     F3M_LAUNCH_CHECK();
 }
 
+template <int D, int ORD>
+static void taylor_impl(f3m_plan *pl, int level, const PairCSR &csr, const float *bs, int R, float *out, int row_begin,
+                        int row_end, cudaStream_t s) {
+    using ML = MomLayout<D, ORD>;
+    Tree &tx = pl->tx, &ty = *pl->ty;
+    Level &lx = tx.levels[level], &ly = ty.levels[level];
+    const float scale = near_scale(pl->lcs);
+    DevBuf<int> tiles;
+    tiles.alloc((size_t)lx.nb + 1, s);
+    near_tiles_per_box<<<(unsigned)((lx.nb + 1 + 255) / 256), 256, 0, s>>>(lx.nb, lx.off.p, csr.ptr.p, row_begin, row_end, 128,
+                                                                           tiles.p);
+    F3M_LAUNCH_CHECK();
+    exclusive_scan_i32(tiles.p, tiles.p, (int64_t)lx.nb + 1, s);
+    F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, tiles.p + lx.nb, sizeof(int), cudaMemcpyDeviceToHost, s));
+    F3M_CUDA(cudaStreamSynchronize(s));
+    const int items = pl->h_pinned[0];
+    if (items <= 0) return;
+    DevBuf<float> mom;
+    mom.alloc((size_t)ly.nb * R * ML::NM, s);
+    pl->last.begin(ST_DIRECT, s);
+    near_moments_kernel<D, ORD><<<(unsigned)(((size_t)ly.nb * R * 32 + 255) / 256), 256, 0, s>>>(ty.pts.p, (int)ty.n, bs, R, scale,
+                                                                                             ly.off.p, ly.nb, ly.ctr.p, mom.p);
+    F3M_LAUNCH_CHECK();
+    near_taylor_kernel<D, ORD><<<items, 128, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, csr.idx.p, ly.ctr.p,
+                                                    mom.p, scale, R, out);
+    pl->last.end(s);
+    pl->last.direct_launches++;
+    F3M_LAUNCH_CHECK();
+}
+
 template <int D>
 static void direct_d(f3m_plan *pl, int level, const PairCSR &csr, const float *bs, int R, float *out, int rb, int re,
                      cudaStream_t s) {
+    if ((pl->prm.flags & F3M_FLAG_NEAR_MOMENTS) && level > 0) {
+        // same exponent bound as the polynomial offload of near_kernel_exp (see direct_impl)
+        const float se = near_scale(pl->lcs) * pl->ty->levels[level].edge;
+        const bool final_near = (&csr == &pl->lists[level].keep);
+        const float tmax = D * (final_near ? 2.5f : 5.5f) * se * se;
+        if (se <= 1.0f && tmax <= 0.02f) { taylor_impl<D, 2>(pl, level, csr, bs, R, out, rb, re, s); return; }
+        if (se <= 1.0f && tmax <= 0.1f) { taylor_impl<D, 3>(pl, level, csr, bs, R, out, rb, re, s); return; }
+    }
     for (int r0 = 0; r0 < R;) {
         const int left = R - r0;
         if (left >= 5) { direct_impl<D, 8>(pl, level, csr, bs, R, r0, out, rb, re, s); r0 += 8; }

@@ -23,9 +23,9 @@ def _as_f32(t: torch.Tensor) -> torch.Tensor:
 
 
 def make_params(ls, min_points, nr_of_interpolation, var_compression, eff_var_limit, small_field_points,
-                math_mode=_lib.MATH_FASTMATH) -> Params:
+                math_mode=_lib.MATH_FASTMATH, flags=0) -> Params:
     return Params(float(ls), float(min_points), int(nr_of_interpolation), int(bool(var_compression)),
-                  float(eff_var_limit), int(small_field_points), int(math_mode), 0)
+                  float(eff_var_limit), int(small_field_points), int(math_mode), int(flags))
 
 
 class Plan:

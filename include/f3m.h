@@ -44,6 +44,13 @@ enum f3m_status {
                                --use_fast_math build executes (F3M_src/setup.py:16) -- default */
 #define F3M_MATH_IEEE 1     /* IEEE divide, sqrt, no contraction: what a CPU restatement computes */
 
+/* Optional evaluation of the near field by box moments: when every pair of a near / small list has a provably
+ * tiny exponent (boxes much smaller than the lengthscale), the sum over a source box is replaced by its 2nd/3rd
+ * order Taylor moments (truncation error <= 1e-6 relative, the size of the ex2.approx error).  The pair lists do
+ * not change.  Off by default: the default near field is the direct sum of the reference
+ * (near_field_run, F3M_src/n_tree.cu:831-902). */
+#define F3M_FLAG_NEAR_MOMENTS 1
+
 /* Parameters of FFM_XY<float,d> (F3M_src/n_tree.cu:1056-1059) / FFM.__init__ (experiments/FFM_classes.py:9-19). */
 typedef struct f3m_params {
     float ls;                 /* lengthscale l;  K = exp(-r^2/(2 l^2)) */
@@ -53,7 +60,7 @@ typedef struct f3m_params {
     float eff_var_limit;
     int32_t small_field_points;
     int32_t math_mode;        /* F3M_MATH_FASTMATH or F3M_MATH_IEEE */
-    int32_t reserved;
+    int32_t flags;            /* F3M_FLAG_* bits, 0 by default */
 } f3m_params;
 
 typedef struct f3m_plan f3m_plan;   /* tree + interaction lists of one (X, Y) pair; reusable for many b */

@@ -166,6 +166,36 @@ def test_sharded_moments_and_rows_sum_to_full(name, cuda):
     assert rel_l2(parts.cpu(), full.cpu()) <= 2e-6
 
 
+@pytest.mark.parametrize("d,ls,R", [(3, 3.0, 1), (3, 1.2, 2), (2, 2.0, 1), (4, 4.0, 3)])
+def test_near_moments_flag(d, ls, R, cuda):
+    """Optional moment form of the near field: with boxes much smaller than the lengthscale the near sums are
+    evaluated from 2nd/3rd-order box moments; the result must agree with the direct sums to the size of the
+    ex2.approx error, and the accuracy against float64 must not get worse."""
+    from f3m_b200 import engine, _lib
+    from oracle.f3m_oracle import dense_kmvm_f64
+    g = torch.Generator().manual_seed(100 + d)
+    X = torch.rand(40000, d, generator=g)
+    b = torch.randn(40000, R, generator=g)
+    P = {2: 36, 3: 64, 4: 81}[d]
+    outs = {}
+    for flags in (0, _lib.FLAG_NEAR_MOMENTS):
+        prm = engine.make_params(ls, 300.0, P, False, 0.15, P, flags=flags)
+        plan = engine.Plan(X.to(cuda), None, prm)
+        outs[flags] = plan.apply(b.to(cuda)).cpu()
+        assert plan.stats()["direct_pairs"] > 0
+    assert rel_l2(outs[_lib.FLAG_NEAR_MOMENTS], outs[0]) <= 3e-6
+    rows = torch.arange(2000)
+    exact = dense_kmvm_f64(X, X, b, ls, rows=rows)
+    e0, e1 = rel_l2(outs[0][rows], exact), rel_l2(outs[_lib.FLAG_NEAR_MOMENTS][rows], exact)
+    assert e1 <= max(1.2 * e0, e0 + 2e-6)
+    # a lengthscale for which the exponent bound is too large: the flag must change nothing
+    prm0 = engine.make_params(0.05, 300.0, P, False, 0.15, P)
+    prm1 = engine.make_params(0.05, 300.0, P, False, 0.15, P, flags=_lib.FLAG_NEAR_MOMENTS)
+    a0 = engine.kmvm(X.to(cuda), None, b.to(cuda), prm0).cpu()
+    a1 = engine.kmvm(X.to(cuda), None, b.to(cuda), prm1).cpu()
+    assert rel_l2(a1, a0) <= 1e-7
+
+
 def test_dense_ops(cuda):
     from f3m_b200 import engine
     from oracle.f3m_oracle import dense_kmvm_f64

@@ -120,6 +120,10 @@ struct PairCSR {
 struct LevelLists {
     PairCSR far, small, keep;
     int p = 0;        // nodes per dimension used for the far field of this level
+    // far rows re-ordered by box offset (last axis most significant) with the packed offsets, built on first use
+    DevBuf<uint32_t> far_okey;
+    DevBuf<int> far_oidx;
+    bool far_ordered = false;
 };
 
 // Device time per stage, from CUDA events recorded on the product's stream and read after its

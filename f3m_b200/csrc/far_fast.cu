@@ -291,15 +291,15 @@ __global__ void __launch_bounds__(128, 5) m2l_fast(int nbx, int d, const int *__
 // ---------------------------------------------------------------------------------------------
 // M2L, nested form (d = 2, 3, one column).  T(pair) = T_{d-1}(o_{d-1}) x .. x T_0(o_0) and the sum over the
 // far pairs of a target box can be taken axis by axis:
-//     loc = sum_{o2} T2(o2) [ sum_{o1} T1(o1) [ sum_{o0} T0(o0) mom(o0,o1,o2) ] ]
-// With the row ordered by (o2, o1, o0) only the axis-0 transform is applied per pair; the axis-1 transform
-// once per (o1,o2) group and the axis-2 transform once per o2 group: ~240 instead of 567 stage applications
+//     loc = sum_{o0} T0(o0) [ sum_{o1} T1(o1) [ sum_{o2} T2(o2) mom(o0,o1,o2) ] ]
+// With the row ordered by (o0, o1, o2) only the last-axis transform is applied per pair; the axis-1 transform
+// once per (o0,o1) group and the axis-0 transform once per o0 group: ~240 instead of 567 stage applications
 // for the 189 far pairs of an interior box.  Any order is correct (a group is flushed whenever the higher
 // offsets change), ordering only increases the sharing.
 // ---------------------------------------------------------------------------------------------
 constexpr int ORD_MAXROW = 1024;
 
-// one warp per target box: packed offsets of its far pairs, stably sorted by them
+// one warp per target box: packed offsets of its far pairs (axis 0 most significant), stably sorted by them
 __global__ void __launch_bounds__(128) far_order_kernel(int nbx, int d, const int *__restrict__ fptr, const int *__restrict__ fidx,
                                                        const int *__restrict__ cell_x, const int *__restrict__ cell_y,
                                                        Geom2 geo, uint32_t *okey, int *oidx, int *err) {
@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(128) far_order_kernel(int nbx, int d, const in
         for (int k = 0; k < d; k++) {
             int o = cell_y[by * d + k] - cell_x[bx * d + k] - geo.dqmin[k];
             if (o < 0 || o >= NOFF2) { atomicExch(err, 2); o = 0; }
-            key |= (uint32_t)o << (4 * k);
+            key |= (uint32_t)o << (4 * (d - 1 - k));   // last axis lowest, axis 0 on top
         }
         return key;
     };
@@ -333,78 +333,141 @@ __global__ void __launch_bounds__(128) far_order_kernel(int nbx, int d, const in
     }
 }
 
-// One axis of the nested transform.  MODE 0: source = global moments, destination += in shared memory.
-// MODE 1: source = shared buffer (read and cleared), destination += in shared memory.
-// MODE 2: source = shared buffer (read and cleared), destination += in the lane's registers (last axis).
-template <int PP, int K, int DD, int MODE>
-__device__ __forceinline__ void nested_stage(const float *gsrc, float *ssrc, float *sdst, float (&acc_reg)[2][PP],
-                                             float &acc_left, const float *Mk, int lane) {
-    constexpr int MS = mat_stride(PP);
-    constexpr int nf = cpow(PP, DD - 1), st = cpow(PP, K);
-    constexpr int left = nf - 32;
-    constexpr bool short_round = left > 0 && left * PP <= 32;
-    float M[MS];
+// Accumulators of one lane for one buffer of the nested transform: the fibres lane and lane+32 of the
+// axis that produced it, or (when only a few fibres are left after the first 32) one output of a fibre
+// beyond 32 per lane.
+template <int PP>
+struct FibreAcc {
+    float r0[PP], r1[PP], left;
+    __device__ __forceinline__ void clear() {
+#pragma unroll
+        for (int i = 0; i < PP; i++) r0[i] = r1[i] = 0.f;
+        left = 0.f;
+    }
+};
+
+template <int PP, int DD>
+struct NestGeom {
+    static constexpr int MS = mat_stride(PP);
+    static constexpr int P = cpow(PP, DD);
+    static constexpr int nf = cpow(PP, DD - 1);
+    static constexpr int left = nf - 32;
+    static constexpr bool short_round = left > 0 && left * PP <= 32;
+    static constexpr bool second_round = left > 0 && !short_round;
+    template <int K>
+    static __device__ __forceinline__ int base(int f) {
+        constexpr int st = cpow(PP, K);
+        const int hi = f / st;
+        return hi * st * PP + (f - hi * st);
+    }
+};
+
+// inputs of one lane for one application along axis K
+template <int PP>
+struct FibreIn {
+    float v0[PP], v1[PP];
+};
+
+template <int PP, int K, int DD, bool GLOBAL>
+__device__ __forceinline__ void nest_load(const float *src, FibreIn<PP> &in, int lane) {
+    using G = NestGeom<PP, DD>;
+    constexpr int st = cpow(PP, K);
+    if (lane < G::nf) {
+        const int base = G::template base<K>(lane);
+#pragma unroll
+        for (int j = 0; j < PP; j++) in.v0[j] = GLOBAL ? __ldg(src + base + j * st) : src[base + j * st];
+    }
+    if (G::short_round) {
+        if (lane < G::left * PP) {
+            const int base = G::template base<K>(32 + lane / PP);
+#pragma unroll
+            for (int j = 0; j < PP; j++) in.v1[j] = GLOBAL ? __ldg(src + base + j * st) : src[base + j * st];
+        }
+    } else if (G::second_round) {
+        if (lane + 32 < G::nf) {
+            const int base = G::template base<K>(lane + 32);
+#pragma unroll
+            for (int j = 0; j < PP; j++) in.v1[j] = GLOBAL ? __ldg(src + base + j * st) : src[base + j * st];
+        }
+    }
+}
+
+// out += M_k applied along the axis to the loaded fibres
+template <int PP, int DD>
+__device__ __forceinline__ void nest_apply(const FibreIn<PP> &in, const float *Mk, FibreAcc<PP> &out, int lane) {
+    using G = NestGeom<PP, DD>;
+    float M[G::MS];
     const float4 *M4 = reinterpret_cast<const float4 *>(Mk);
 #pragma unroll
-    for (int q = 0; q < MS / 4; q++) {
+    for (int q = 0; q < G::MS / 4; q++) {
         float4 v = M4[q];
         M[4 * q] = v.x; M[4 * q + 1] = v.y; M[4 * q + 2] = v.z; M[4 * q + 3] = v.w;
     }
-    auto fibre = [&](int f, float *areg) {
-        const int hi = f / st;
-        const int base = hi * st * PP + (f - hi * st);
-        float v[PP];
-#pragma unroll
-        for (int j = 0; j < PP; j++) {
-            if (MODE == 0) v[j] = __ldg(gsrc + base + j * st);
-            else { v[j] = ssrc[base + j * st]; ssrc[base + j * st] = 0.f; }
-        }
+    if (lane < G::nf) {
 #pragma unroll
         for (int i = 0; i < PP; i++) {
             float o = 0.f;
 #pragma unroll
-            for (int j = 0; j < PP; j++) o = fmaf(M[i * PP + j], v[j], o);
-            if (MODE == 2) areg[i] += o;
-            else sdst[base + i * st] += o;
-        }
-    };
-    if (lane < nf) fibre(lane, acc_reg[0]);
-    if (short_round) {
-        if (lane < left * PP) {   // one output per lane for the few fibres beyond the first 32
-            const int lf = lane / PP, i = lane - lf * PP, f = 32 + lf;
-            const int hi = f / st;
-            const int base = hi * st * PP + (f - hi * st);
-            float o = 0.f;
-#pragma unroll
-            for (int j = 0; j < PP; j++) o = fmaf(Mk[i * PP + j], MODE == 0 ? __ldg(gsrc + base + j * st) : ssrc[base + j * st], o);
-            if (MODE == 2) acc_left += o;
-            else sdst[base + i * st] += o;
-        }
-        if (MODE != 0) {          // the lanes above read the whole fibre: clear it afterwards
-            __syncwarp();
-            if (lane < left * PP) {
-                const int lf = lane / PP, i = lane - lf * PP, f = 32 + lf;
-                const int hi = f / st;
-                ssrc[hi * st * PP + (f - hi * st) + i * st] = 0.f;
-            }
-        }
-    } else {
-        for (int f = lane + 32; f < nf; f += 32) {
-            static_assert(MODE != 2 || nf <= 64, "register accumulators hold two rounds");
-            fibre(f, acc_reg[1]);
+            for (int j = 0; j < PP; j++) o = fmaf(M[i * PP + j], in.v0[j], o);
+            out.r0[i] += o;
         }
     }
-    __syncwarp();
+    if (G::short_round) {
+        if (lane < G::left * PP) {
+            const float *mrow = Mk + (lane % PP) * PP;
+            float o = 0.f;
+#pragma unroll
+            for (int j = 0; j < PP; j++) o = fmaf(mrow[j], in.v1[j], o);
+            out.left += o;
+        }
+    } else if (G::second_round) {
+        if (lane + 32 < G::nf) {
+#pragma unroll
+            for (int i = 0; i < PP; i++) {
+                float o = 0.f;
+#pragma unroll
+                for (int j = 0; j < PP; j++) o = fmaf(M[i * PP + j], in.v1[j], o);
+                out.r1[i] += o;
+            }
+        }
+    }
 }
 
+// registers -> shared memory in the layout of axis K (the axis that produced them), then clear
+template <int PP, int K, int DD>
+__device__ __forceinline__ void nest_spill(FibreAcc<PP> &a, float *dst, int lane) {
+    using G = NestGeom<PP, DD>;
+    constexpr int st = cpow(PP, K);
+    if (lane < G::nf) {
+        const int base = G::template base<K>(lane);
+#pragma unroll
+        for (int i = 0; i < PP; i++) dst[base + i * st] = a.r0[i];
+    }
+    if (G::short_round) {
+        if (lane < G::left * PP) dst[G::template base<K>(32 + lane / PP) + (lane % PP) * st] = a.left;
+    } else if (G::second_round) {
+        if (lane + 32 < G::nf) {
+            const int base = G::template base<K>(lane + 32);
+#pragma unroll
+            for (int i = 0; i < PP; i++) dst[base + i * st] = a.r1[i];
+        }
+    }
+    a.clear();
+}
+
+// The per-pair transform runs along the LAST axis (its fibres are strided by the number of fibres, so a
+// warp reads 32 consecutive floats per load); the packed key of a pair holds the offset of that axis in
+// its lowest 4 bits, the next axis above it, axis 0 on top.
 template <int PP, int DD>
-__global__ void __launch_bounds__(128, 5) m2l_nested(int nbx, const int *__restrict__ fptr, const uint32_t *__restrict__ okey,
-                                                    const int *__restrict__ oidx, const int *__restrict__ off_x, int row_begin,
-                                                    int row_end, const float *__restrict__ T, KronCfg cfg,
-                                                    const float *__restrict__ mom, float *loc) {
+__global__ void __launch_bounds__(128, PP <= 6 ? 4 : 2) m2l_nested(int nbx, const int *__restrict__ fptr,
+                                                                   const uint32_t *__restrict__ okey, const int *__restrict__ oidx,
+                                                                   const int *__restrict__ off_x, int row_begin, int row_end,
+                                                                   const float *__restrict__ T, const float *__restrict__ mom,
+                                                                   float *loc) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int MS = mat_stride(PP);
-    constexpr int P = cpow(PP, DD);
+    using G = NestGeom<PP, DD>;
+    constexpr int MS = G::MS, P = G::P;
+    constexpr int KA = DD - 1;               // axis applied per pair
     const int bx = blockIdx.x;
     const int e0 = fptr[bx], e1 = fptr[bx + 1];
     if (e0 == e1) return;
@@ -412,41 +475,63 @@ __global__ void __launch_bounds__(128, 5) m2l_nested(int nbx, const int *__restr
     const int nw = blockDim.x >> 5, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int ntab = DD * NOFF2 * MS;
     float *Tsm = sm;
-    float *wbuf = sm + ntab + (size_t)w * 3 * P;
-    float *V = wbuf, *U = wbuf + P, *acc = wbuf + 2 * P;
+    float *buf = sm + ntab + (size_t)w * P;  // one transpose buffer per warp
     for (int q = threadIdx.x; q < ntab; q += blockDim.x) Tsm[q] = T[q];
-    for (int q = lane; q < 3 * P; q += 32) wbuf[q] = 0.f;
-    float acc_reg[2][PP], acc_left = 0.f;
-#pragma unroll
-    for (int a = 0; a < 2; a++)
-#pragma unroll
-        for (int i = 0; i < PP; i++) acc_reg[a][i] = 0.f;
+    FibreAcc<PP> V, U, A;
+    V.clear(); U.clear(); A.clear();
     __syncthreads();
     const int len = e1 - e0;
     const int cb = e0 + (int)(((long long)len * w) / nw), ce = e0 + (int)(((long long)len * (w + 1)) / nw);
-    uint32_t prev = 0xffffffffu;
-    auto mat = [&](int k, uint32_t key) { return Tsm + (k * NOFF2 + ((key >> (4 * k)) & 15u)) * MS; };
-    auto flush = [&](uint32_t key, bool all) {
-        // close the axis-1 group (and the axis-2 group when `all`) that ended with `key`
+    // matrix of axis k for the offset stored in nibble (DD-1-k) of the key
+    auto mat = [&](int k, uint32_t key) { return Tsm + (k * NOFF2 + ((key >> (4 * (DD - 1 - k))) & 15u)) * MS; };
+    auto close_groups = [&](uint32_t key, bool all) {
+        FibreIn<PP> in;
+        nest_spill<PP, KA, DD>(V, buf, lane);
+        __syncwarp();
         if (DD == 3) {
-            nested_stage<PP, 1, DD, 1>(nullptr, V, U, acc_reg, acc_left, mat(1, key), lane);
-            if (all) nested_stage<PP, 2, DD, 2>(nullptr, U, nullptr, acc_reg, acc_left, mat(2, key), lane);
+            nest_load<PP, 1, DD, false>(buf, in, lane);
+            nest_apply<PP, DD>(in, mat(1, key), U, lane);
+            __syncwarp();
+            if (all) {
+                nest_spill<PP, 1, DD>(U, buf, lane);
+                __syncwarp();
+                nest_load<PP, 0, DD, false>(buf, in, lane);
+                nest_apply<PP, DD>(in, mat(0, key), A, lane);
+                __syncwarp();
+            }
         } else {
-            nested_stage<PP, 1, DD, 2>(nullptr, V, nullptr, acc_reg, acc_left, mat(1, key), lane);
+            nest_load<PP, 0, DD, false>(buf, in, lane);
+            nest_apply<PP, DD>(in, mat(0, key), A, lane);
+            __syncwarp();
         }
     };
-    for (int e = cb; e < ce; e++) {
-        const uint32_t key = okey[e];
-        if (prev != 0xffffffffu && (key >> 4) != (prev >> 4)) flush(prev, DD == 3 ? (key >> 8) != (prev >> 8) : true);
-        nested_stage<PP, 0, DD, 0>(mom + (size_t)oidx[e] * P, nullptr, V, acc_reg, acc_left, mat(0, key), lane);
-        prev = key;
+    uint32_t prev = 0xffffffffu;
+    for (int c = cb; c < ce; c += 32) {
+        const int cn = min(32, ce - c);
+        uint32_t mykey = 0;
+        int myidx = 0;
+        if (lane < cn) { mykey = okey[c + lane]; myidx = oidx[c + lane]; }
+        FibreIn<PP> cur;
+        nest_load<PP, KA, DD, true>(mom + (size_t)__shfl_sync(0xffffffffu, myidx, 0) * P, cur, lane);
+        for (int t = 0; t < cn; t++) {
+            const uint32_t key = __shfl_sync(0xffffffffu, mykey, t);
+            FibreIn<PP> nxt;
+            const int tn = min(t + 1, cn - 1);   // the last one re-reads itself: no branch around the loads
+            nest_load<PP, KA, DD, true>(mom + (size_t)__shfl_sync(0xffffffffu, myidx, tn) * P, nxt, lane);
+            if (prev != 0xffffffffu && (key >> 4) != (prev >> 4)) close_groups(prev, DD == 3 ? (key >> 8) != (prev >> 8) : true);
+            nest_apply<PP, DD>(cur, mat(KA, key), V, lane);
+            prev = key;
+            cur = nxt;
+        }
     }
-    if (prev != 0xffffffffu) flush(prev, true);
-    flush_acc<PP>(acc_reg, acc_left, acc, cfg, lane);
+    if (prev != 0xffffffffu) close_groups(prev, true);
+    // layout of axis 0: the lane's fibre is PP consecutive entries
+    float *accw = sm + ntab + (size_t)w * P;
+    nest_spill<PP, 0, DD>(A, accw, lane);
     __syncthreads();
     for (int q = threadIdx.x; q < P; q += blockDim.x) {
         float s = 0.f;
-        for (int ww = 0; ww < nw; ww++) s += sm[ntab + (size_t)ww * 3 * P + 2 * P + q];
+        for (int ww = 0; ww < nw; ww++) s += sm[ntab + (size_t)ww * P + q];
         loc[(size_t)bx * P + q] = s;
     }
 }
@@ -818,14 +903,15 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
                     F3M_LAUNCH_CHECK();
                     ll.far_ordered = true;
                 }
+                const size_t smem_n = tab + (size_t)4 * P * sizeof(float);   // tables + one buffer per warp
                 if (d == 3) {
-                    F3M_CUDA(cudaFuncSetAttribute(m2l_nested<PP, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                    m2l_nested<PP, 3><<<lx.nb, 32 * nw, smem, s>>>(lx.nb, ll.far.ptr.p, ll.far_okey.p, ll.far_oidx.p, lx.off.p, rb, re,
-                                                                  T.p, cfg, momp[l], loc[l].p);
+                    F3M_CUDA(cudaFuncSetAttribute(m2l_nested<PP, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_n));
+                    m2l_nested<PP, 3><<<lx.nb, 128, smem_n, s>>>(lx.nb, ll.far.ptr.p, ll.far_okey.p, ll.far_oidx.p, lx.off.p, rb, re,
+                                                                  T.p, momp[l], loc[l].p);
                 } else {
-                    F3M_CUDA(cudaFuncSetAttribute(m2l_nested<PP, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                    m2l_nested<PP, 2><<<lx.nb, 32 * nw, smem, s>>>(lx.nb, ll.far.ptr.p, ll.far_okey.p, ll.far_oidx.p, lx.off.p, rb, re,
-                                                                  T.p, cfg, momp[l], loc[l].p);
+                    F3M_CUDA(cudaFuncSetAttribute(m2l_nested<PP, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_n));
+                    m2l_nested<PP, 2><<<lx.nb, 128, smem_n, s>>>(lx.nb, ll.far.ptr.p, ll.far_okey.p, ll.far_oidx.p, lx.off.p, rb, re,
+                                                                  T.p, momp[l], loc[l].p);
                 }
             } else
                 launch_m2l(lx.nb, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, lx.off.p, geo, momp[l], loc[l].p);

@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libf3m.so")
 MATH_FASTMATH = 0
 MATH_IEEE = 1
 FLAG_NEAR_MOMENTS = 1
+FLAG_NEAR_TENSOR_CORES = 2
 
 # array ids of f3m_plan_copy_array
 ARR_SORTED_INDEX, ARR_BOX_OFFSETS, ARR_BOX_CENTERS = 0, 1, 2

@@ -297,18 +297,20 @@ __global__ void __launch_bounds__(128, 5) m2l_fast(int nbx, int d, const int *__
 // for the 189 far pairs of an interior box.  Any order is correct (a group is flushed whenever the higher
 // offsets change), ordering only increases the sharing.
 // ---------------------------------------------------------------------------------------------
-constexpr int ORD_MAXROW = 1024;
-
-// one warp per target box: packed offsets of its far pairs (axis 0 most significant), stably sorted by them
+// One warp per target box: packed offsets of its far pairs (axis 0 most significant) and the row in
+// ascending order of them.  The source boxes of one row have distinct cells, hence distinct keys below
+// 16^3: the rank of a key is the number of set bits below it in a bitmap of the row.
+constexpr int ORD_WORDS = 128;   // 4096 keys
 __global__ void __launch_bounds__(128) far_order_kernel(int nbx, int d, const int *__restrict__ fptr, const int *__restrict__ fidx,
                                                        const int *__restrict__ cell_x, const int *__restrict__ cell_y,
                                                        Geom2 geo, uint32_t *okey, int *oidx, int *err) {
-    __shared__ uint32_t skey[4][ORD_MAXROW];
-    __shared__ int sby[4][ORD_MAXROW];
+    __shared__ uint32_t bits[4][ORD_WORDS];
+    __shared__ int below[4][ORD_WORDS];
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bx = blockIdx.x * 4 + w;
     if (bx >= nbx) return;
     const int e0 = fptr[bx], n = fptr[bx + 1] - e0;
+    if (n == 0) return;
     auto key_of = [&](int by) {
         uint32_t key = 0;
         for (int k = 0; k < d; k++) {
@@ -318,18 +320,36 @@ __global__ void __launch_bounds__(128) far_order_kernel(int nbx, int d, const in
         }
         return key;
     };
-    if (n > ORD_MAXROW) {   // very long row: keep the list order
+    for (int q = lane; q < ORD_WORDS; q += 32) bits[w][q] = 0u;
+    __syncwarp();
+    for (int i = lane; i < n; i += 32) {
+        const uint32_t key = key_of(fidx[e0 + i]);
+        atomicOr(&bits[w][key >> 5], 1u << (key & 31u));
+    }
+    __syncwarp();
+    // exclusive prefix of the word populations: 4 words per lane, then a warp scan
+    int c[4], tot = 0;
+#pragma unroll
+    for (int q = 0; q < 4; q++) { c[q] = __popc(bits[w][lane * 4 + q]); tot += c[q]; }
+    int incl = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+    int run = incl - tot;
+#pragma unroll
+    for (int q = 0; q < 4; q++) { below[w][lane * 4 + q] = run; run += c[q]; }
+    const int distinct = __shfl_sync(0xffffffffu, incl, 31);
+    __syncwarp();
+    if (distinct != n) {   // cannot happen for boxes of one level; keep the list order rather than lose pairs
+        if (lane == 0) atomicExch(err, 2);
         for (int i = lane; i < n; i += 32) { int by = fidx[e0 + i]; okey[e0 + i] = key_of(by); oidx[e0 + i] = by; }
         return;
     }
-    for (int i = lane; i < n; i += 32) { int by = fidx[e0 + i]; sby[w][i] = by; skey[w][i] = key_of(by); }
-    __syncwarp();
     for (int i = lane; i < n; i += 32) {
-        const uint32_t ki = skey[w][i];
-        int rank = 0;
-        for (int j = 0; j < n; j++) { const uint32_t kj = skey[w][j]; rank += (kj < ki) || (kj == ki && j < i); }
-        okey[e0 + rank] = ki;
-        oidx[e0 + rank] = sby[w][i];
+        const int by = fidx[e0 + i];
+        const uint32_t key = key_of(by);
+        const int rank = below[w][key >> 5] + __popc(bits[w][key >> 5] & ((1u << (key & 31u)) - 1u));
+        okey[e0 + rank] = key;
+        oidx[e0 + rank] = by;
     }
 }
 

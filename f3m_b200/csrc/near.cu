@@ -298,6 +298,177 @@ __global__ void __launch_bounds__(NTH) near_kernel_exp(const float *__restrict__
         }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Expanded form with packed FP32 pairs (fma.rn.f32x2, sm_100): two SOURCES share every instruction of
+// the inner product, the polynomial and the accumulation, which halves the issue slots they take.
+// Sources are packed in pairs, column by column: pair block = [c0a c0b c1a c1b ... ] (2 W floats), so a
+// 16-byte shared-memory load yields two aligned register pairs.  Box b starts at the even row
+// (off[b] + b + 1) & ~1 of the packed array; an odd box gets a zero-weight partner for its last source.
+// ---------------------------------------------------------------------------------------------
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__host__ __device__ __forceinline__ int pair_row_start(int off, int box) { return (off + box + 1) & ~1; }
+
+template <int D, int RB>
+__global__ void __launch_bounds__(256) pack_pairs_rel(const float *__restrict__ pts, int n, const float *__restrict__ bs,
+                                                     int R, int r0, float scale, const int *__restrict__ off_y, int nby,
+                                                     const float *__restrict__ ctr_y, float *packed) {
+    constexpr int W = row_width(D, RB);
+    int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const int by = box_of_pt(off_y, nby, j);
+    const int s0 = off_y[by], s1 = off_y[by + 1];
+    float row[W];
+    float ny = 0.f;
+#pragma unroll
+    for (int k = 0; k < D; k++) {
+        float yr = scale * (pts[(size_t)k * n + j] - ctr_y[by * D + k]);
+        ny = fmaf(-yr, yr, ny);
+        row[k] = 2.f * yr;
+    }
+    const float wy = ex2_approx(ny);
+#pragma unroll
+    for (int r = 0; r < RB; r++) row[D + r] = (r0 + r < R) ? bs[(size_t)j * R + r0 + r] * wy : 0.f;
+#pragma unroll
+    for (int c = D + RB; c < W; c++) row[c] = 0.f;
+    const int pos = pair_row_start(s0, by) + (j - s0);
+    float *dst = packed + (size_t)(pos >> 1) * (2 * W) + (pos & 1);
+#pragma unroll
+    for (int c = 0; c < W; c++) dst[2 * c] = row[c];
+    if (j == s1 - 1 && !(pos & 1)) {   // last source of an odd box: its partner weighs nothing
+#pragma unroll
+        for (int c = 0; c < W; c++) dst[2 * c + 1] = 0.f;
+    }
+}
+
+constexpr int SP2 = 192;   // source pairs per shared-memory tile
+
+// POLY = 0: every exponential on the MUFU pipe.  POLY = 2 or 3: PNUM of every PDEN source pairs use the
+// polynomial of that degree instead (the host enables it only when the exponent is provably small).
+template <int D, int RB, int POLY, int PNUM, int PDEN>
+__global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
+                                                     int nbx, const int *__restrict__ tile_off,
+                                                     const int *__restrict__ ptr, const int *__restrict__ idx,
+                                                     const int *__restrict__ off_y, const float *__restrict__ ctr_y,
+                                                     const float *__restrict__ packed, float scale, int R, int r0,
+                                                     float *out) {
+    constexpr int W = row_width(D, RB);
+    __shared__ __align__(16) float smem[SP2 * 2 * W];
+    int box, t0, t1;
+    item_to_tile(blockIdx.x, tile_off, nbx, off_x, box, t0, t1);
+    float x[TI2][D], tot[TI2][RB];
+    int ti[TI2];
+#pragma unroll
+    for (int u = 0; u < TI2; u++) {
+        ti[u] = t0 + threadIdx.x + u * NT2;
+        int ii = ti[u] < t1 ? ti[u] : t0;
+#pragma unroll
+        for (int k = 0; k < D; k++) x[u][k] = xpts[(size_t)k * n_x + ii];
+#pragma unroll
+        for (int r = 0; r < RB; r++) tot[u][r] = 0.f;
+    }
+    constexpr float C1 = 0.69314718056f, C2 = 0.24022650696f, C3 = 0.05550410866f;
+    const f32x2 c1 = pack2(C1, C1), c2 = pack2(C2, C2), c3 = pack2(C3, C3), one = pack2(1.f, 1.f);
+    const int e0 = ptr[box], e1 = ptr[box + 1];
+    for (int e = e0; e < e1; e++) {
+        const int by = idx[e];
+        const int s0 = off_y[by], cnt = off_y[by + 1] - s0;
+        const int npairs = (cnt + 1) >> 1;
+        const float *rows = packed + (size_t)pair_row_start(s0, by) * W;
+        f32x2 xr[TI2][D], acc[TI2][RB];
+        float fx[TI2];
+#pragma unroll
+        for (int u = 0; u < TI2; u++) {
+            float nx = 0.f;
+#pragma unroll
+            for (int k = 0; k < D; k++) {
+                const float v = scale * (x[u][k] - __ldg(ctr_y + by * D + k));
+                nx = fmaf(-v, v, nx);
+                xr[u][k] = pack2(v, v);
+            }
+            fx[u] = ex2_approx(nx);
+#pragma unroll
+            for (int r = 0; r < RB; r++) acc[u][r] = pack2(0.f, 0.f);
+        }
+        for (int base = 0; base < npairs; base += SP2) {
+            const int np = min(SP2, npairs - base);
+            __syncthreads();
+            const float4 *g = reinterpret_cast<const float4 *>(rows + (size_t)base * 2 * W);
+            float4 *sdst = reinterpret_cast<float4 *>(smem);
+            for (int q = threadIdx.x; q < np * (2 * W / 4); q += NT2) sdst[q] = __ldg(g + q);
+            __syncthreads();
+            auto body = [&](int j, bool poly) {
+                f32x2 col[W];
+                const ulonglong2 *src = reinterpret_cast<const ulonglong2 *>(smem + j * 2 * W);
+#pragma unroll
+                for (int q = 0; q < W / 2; q++) {
+                    const ulonglong2 v = src[q];
+                    col[2 * q] = v.x;
+                    col[2 * q + 1] = v.y;
+                }
+#pragma unroll
+                for (int u = 0; u < TI2; u++) {
+                    f32x2 t = mul2(xr[u][0], col[0]);
+#pragma unroll
+                    for (int k = 1; k < D; k++) t = fma2(xr[u][k], col[k], t);
+                    f32x2 ev;
+                    if (POLY && poly) {
+                        ev = (POLY == 2) ? fma2(fma2(c2, t, c1), t, one) : fma2(fma2(fma2(c3, t, c2), t, c1), t, one);
+                    } else {
+                        float ta, tb;
+                        unpack2(t, ta, tb);
+                        ev = pack2(ex2_approx(ta), ex2_approx(tb));
+                    }
+#pragma unroll
+                    for (int r = 0; r < RB; r++) acc[u][r] = fma2(ev, col[D + r], acc[u][r]);
+                }
+            };
+            int j = 0;
+            if (POLY) {
+#pragma unroll 1
+                for (; j + PDEN <= np; j += PDEN) {
+#pragma unroll
+                    for (int q = 0; q < PDEN; q++) body(j + q, ((q + 1) * PNUM) / PDEN != (q * PNUM) / PDEN);
+                }
+            } else {
+#pragma unroll 4
+                for (; j + 1 <= np; j++) body(j, false);
+            }
+            for (; j < np; j++) body(j, false);
+        }
+#pragma unroll
+        for (int u = 0; u < TI2; u++)
+#pragma unroll
+            for (int r = 0; r < RB; r++) {
+                float lo, hi;
+                unpack2(acc[u][r], lo, hi);
+                tot[u][r] = fmaf(fx[u], lo + hi, tot[u][r]);
+            }
+    }
+#pragma unroll
+    for (int u = 0; u < TI2; u++)
+        if (ti[u] < t1) {
+#pragma unroll
+            for (int r = 0; r < RB; r++)
+                if (r0 + r < R) out[(size_t)ti[u] * R + r0 + r] += tot[u][r];
+        }
+}
+
 __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__restrict__ off_x, const int *__restrict__ ptr,
                                                          int row_begin, int row_end, int tile_pts, int *tiles) {
     int b = blockIdx.x * blockDim.x + threadIdx.x;
@@ -309,6 +480,8 @@ __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__
     }
     tiles[b] = t;
 }
+
+#include "near_mma.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // Moment form of the near field (optional, F3M_FLAG_NEAR_MOMENTS).  In the expanded form the pair term
@@ -460,7 +633,10 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     Level &lx = tx.levels[level], &ly = ty.levels[level];
     const float scale = near_scale(pl->lcs);
     const bool expanded = scale * ly.edge <= 1.0f && level > 0;
-    const int tile_pts = expanded ? NT2 * TI2 : NT;
+    // tensor-core form (on request): one column, boxes at most half a scaled unit wide, so that the split
+    // operands keep the exponent at FP32 accuracy
+    const bool use_mma = RB == 1 && level > 0 && scale * ly.edge <= 0.5f && (pl->prm.flags & F3M_FLAG_NEAR_TENSOR_CORES);
+    const int tile_pts = use_mma ? MM_M : (expanded ? NT2 * TI2 : NT);
     DevBuf<int> tiles;
     tiles.alloc((size_t)lx.nb + 1, s);
     near_tiles_per_box<<<(unsigned)((lx.nb + 1 + 255) / 256), 256, 0, s>>>(lx.nb, lx.off.p, csr.ptr.p, row_begin, row_end,
@@ -472,12 +648,47 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     const int items = pl->h_pinned[0];
     if (items <= 0) return;
     DevBuf<float> packed;
-    packed.alloc((size_t)ty.n * row_width(D, RB), s);
+    // the pair layout of the expanded form starts every box on an even row
+    packed.alloc((size_t)(ty.n + (expanded && !use_mma ? ly.nb + 2 : 0)) * row_width(D, RB), s);
     const unsigned g = (unsigned)((ty.n + 255) / 256);
+    if (use_mma) {
+        // raw coordinates and the column: the kernel forms both operands about the target box centre
+        pl->last.begin(ST_PERMUTE, s);
+        pack_sources<D, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, 1.0f, packed.p);
+        pl->last.end(s);
+        F3M_LAUNCH_CHECK();
+        int *counter = pl->d_flags + 32;
+        F3M_CUDA(cudaMemsetAsync(counter, 0, sizeof(int), s));
+        const bool final_near = (&csr == &pl->lists[level].keep);
+        const float se = scale * ly.edge;
+        const float reach = final_near ? 3.f : 6.f;   // |x - y| per dimension, in box edges, over the pairs of the list
+        const float tmax = D * reach * reach * se * se;
+        int dev = 0, nsm = 0;
+        F3M_CUDA(cudaGetDevice(&dev));
+        F3M_CUDA(cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev));
+        const int grid = std::min(items, nsm);
+        pl->last.begin(ST_DIRECT, s);
+#define F3M_NEAR_MMA(DEG_, NP_)                                                                                              \
+    {                                                                                                                        \
+        F3M_CUDA(cudaFuncSetAttribute(near_mma_kernel<D, DEG_, NP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                      MM_SMEM_BYTES));                                                                       \
+        near_mma_kernel<D, DEG_, NP_><<<grid, MM_THREADS, MM_SMEM_BYTES, s>>>(                                                \
+            tx.pts.p, (int)tx.n, lx.off.p, lx.ctr.p, lx.nb, tiles.p, items, csr.ptr.p, csr.idx.p, ly.off.p, packed.p, scale, \
+            R, r0, out, counter, pl->d_flags);                                                                               \
+    }
+        if (tmax <= 0.085f) F3M_NEAR_MMA(3, 5)
+        else if (tmax <= 0.2f) F3M_NEAR_MMA(4, 4)
+        else F3M_NEAR_MMA(0, 0)
+#undef F3M_NEAR_MMA
+        pl->last.end(s);
+        pl->last.direct_launches++;
+        F3M_LAUNCH_CHECK();
+        return;
+    }
     pl->last.begin(ST_PERMUTE, s);
-    if (expanded)
-        pack_sources_rel<D, RB><<<g, 256, 0, s>>>(ty.pts.p, (int)ty.n, bs, R, r0, scale, ly.off.p, ly.nb, ly.ctr.p, packed.p);
-    else
+    if (expanded) {
+        pack_pairs_rel<D, RB><<<g, 256, 0, s>>>(ty.pts.p, (int)ty.n, bs, R, r0, scale, ly.off.p, ly.nb, ly.ctr.p, packed.p);
+    } else
         pack_sources<D, RB><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
     pl->last.end(s);
     F3M_LAUNCH_CHECK();
@@ -489,12 +700,12 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
         const float se = scale * ly.edge;
         const float tmax = D * (final_near ? 2.5f : 5.5f) * se * se;
         const int poly = tmax <= 0.02f ? 2 : (tmax <= 0.1f ? 3 : 0);
-#define F3M_NEAR_EXP(NTH_, POLY_)                                                                                      \
-    near_kernel_exp<D, RB, NTH_, POLY_><<<items, NTH_, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, \
-                                                              csr.idx.p, ly.off.p, ly.ctr.p, packed.p, scale, R, r0, out)
-        if (poly == 2) F3M_NEAR_EXP(NT2, 2);
-        else if (poly == 3) F3M_NEAR_EXP(NT2, 3);
-        else F3M_NEAR_EXP(NT2, 0);
+#define F3M_NEAR_EXP(POLY_, PNUM_, PDEN_)                                                                                     \
+    near_kernel_x2<D, RB, POLY_, PNUM_, PDEN_><<<items, NT2, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, \
+                                                                    csr.idx.p, ly.off.p, ly.ctr.p, packed.p, scale, R, r0, out)
+        if (poly == 2) F3M_NEAR_EXP(2, 2, 5);
+        else if (poly == 3) F3M_NEAR_EXP(3, 1, 3);
+        else F3M_NEAR_EXP(0, 0, 1);
 #undef F3M_NEAR_EXP
     }
     else

@@ -51,6 +51,12 @@ enum f3m_status {
  * (near_field_run, F3M_src/n_tree.cu:831-902). */
 #define F3M_FLAG_NEAR_MOMENTS 1
 
+/* Optional evaluation of the direct near sums on the tensor cores (one column, boxes at most half a scaled
+ * lengthscale wide): the exponent matrix -|x_i - y_j|^2 / (2 l^2) of a 128-target x 256-source tile is a TF32
+ * tcgen05 product of split (head + tail) operands, exact to FP32 rounding; the exponentials and the sum stay on
+ * the CUDA cores.  Same sums as the default near field; no counterpart in the reference. */
+#define F3M_FLAG_NEAR_TENSOR_CORES 2
+
 /* Parameters of FFM_XY<float,d> (F3M_src/n_tree.cu:1056-1059) / FFM.__init__ (experiments/FFM_classes.py:9-19). */
 typedef struct f3m_params {
     float ls;                 /* lengthscale l;  K = exp(-r^2/(2 l^2)) */

@@ -79,7 +79,7 @@ __device__ __forceinline__ void tile_accumulate(const float *__restrict__ smem, 
 
 // ---------------------------------------------------------------------------------------------
 // Direct form: pair = d subtractions, d multiply-adds, ex2, RB multiply-adds.  Used when the boxes
-// are wide compared with the lengthscale (see near_kernel_exp below for the usual case).
+// are wide compared with the lengthscale (see near_kernel_x2 below for the usual case).
 // items: (target box, tile) ; tile_off[b] = first item of box b (exclusive scan of tiles per box)
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void item_to_tile(int item, const int *__restrict__ tile_off, int nbx,
@@ -162,7 +162,6 @@ __global__ void __launch_bounds__(NT) near_kernel(const float *__restrict__ xpts
 constexpr int NT2 = 32;     // threads per CTA: one warp, so a tile holds 64 targets and a box of ~400 points
                             // splits into tiles that are nearly full (measured: 64-thread CTAs lose 7% to padding)
 constexpr int TI2 = 2;      // targets per thread
-constexpr int ST2 = 384;    // source rows per shared-memory tile
 
 __device__ __forceinline__ int box_of_pt(const int *__restrict__ off, int nb, int i) {
     int lo = 0, hi = nb;
@@ -171,131 +170,6 @@ __device__ __forceinline__ int box_of_pt(const int *__restrict__ off, int nb, in
         if (off[mid] <= i) lo = mid; else hi = mid;
     }
     return lo;
-}
-
-template <int D, int RB>
-__global__ void __launch_bounds__(256) pack_sources_rel(const float *__restrict__ pts, int n, const float *__restrict__ bs,
-                                                       int R, int r0, float scale, const int *__restrict__ off_y, int nby,
-                                                       const float *__restrict__ ctr_y, float *packed) {
-    constexpr int W = row_width(D, RB);
-    int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n) return;
-    const int by = box_of_pt(off_y, nby, j);
-    float row[W];
-    float ny = 0.f;
-#pragma unroll
-    for (int k = 0; k < D; k++) {
-        float yr = scale * (pts[(size_t)k * n + j] - ctr_y[by * D + k]);
-        ny = fmaf(-yr, yr, ny);
-        row[k] = 2.f * yr;
-    }
-    const float wy = ex2_approx(ny);
-#pragma unroll
-    for (int r = 0; r < RB; r++) row[D + r] = (r0 + r < R) ? bs[(size_t)j * R + r0 + r] * wy : 0.f;
-#pragma unroll
-    for (int c = D + RB; c < W; c++) row[c] = 0.f;
-    float4 *dst = reinterpret_cast<float4 *>(packed + (size_t)j * W);
-#pragma unroll
-    for (int c = 0; c < W / 4; c++) dst[c] = make_float4(row[4 * c], row[4 * c + 1], row[4 * c + 2], row[4 * c + 3]);
-}
-
-// 2^t for small |t| on the FMA pipe: Taylor polynomial of degree DEG in t*ln2 (error <= (|t| ln2)^(DEG+1)/(DEG+1)!)
-template <int DEG>
-__device__ __forceinline__ float exp2_poly(float t) {
-    constexpr float C1 = 0.69314718056f, C2 = 0.24022650696f, C3 = 0.05550410866f;
-    if (DEG == 2) return fmaf(fmaf(C2, t, C1), t, 1.f);
-    return fmaf(fmaf(fmaf(C3, t, C2), t, C1), t, 1.f);
-}
-
-// POLY = 0: every exponential on the MUFU pipe.  POLY = 2 or 3: every third source row uses exp2_poly<POLY>
-// instead, which moves a third of the exponentials to the FMA pipe (the host enables it only when the
-// exponent 2 xr.yr is provably small for every pair of the list).
-template <int D, int RB, int NTH, int POLY>
-__global__ void __launch_bounds__(NTH) near_kernel_exp(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
-                                                      int nbx, const int *__restrict__ tile_off,
-                                                      const int *__restrict__ ptr, const int *__restrict__ idx,
-                                                      const int *__restrict__ off_y, const float *__restrict__ ctr_y,
-                                                      const float *__restrict__ packed, float scale, int R, int r0,
-                                                      float *out) {
-    constexpr int W = row_width(D, RB);
-    __shared__ __align__(16) float smem[ST2 * W];
-    int box, t0, t1;
-    item_to_tile(blockIdx.x, tile_off, nbx, off_x, box, t0, t1);
-    float x[TI2][D], tot[TI2][RB];
-    int ti[TI2];
-#pragma unroll
-    for (int u = 0; u < TI2; u++) {
-        ti[u] = t0 + threadIdx.x + u * NTH;
-        int ii = ti[u] < t1 ? ti[u] : t0;
-#pragma unroll
-        for (int k = 0; k < D; k++) x[u][k] = xpts[(size_t)k * n_x + ii];
-#pragma unroll
-        for (int r = 0; r < RB; r++) tot[u][r] = 0.f;
-    }
-    const int e0 = ptr[box], e1 = ptr[box + 1];
-    for (int e = e0; e < e1; e++) {
-        const int by = idx[e];
-        const int s0 = off_y[by], s1 = off_y[by + 1];
-        float xr[TI2][D], fx[TI2], acc[TI2][RB];
-#pragma unroll
-        for (int u = 0; u < TI2; u++) {
-            float nx = 0.f;
-#pragma unroll
-            for (int k = 0; k < D; k++) {
-                xr[u][k] = scale * (x[u][k] - __ldg(ctr_y + by * D + k));
-                nx = fmaf(-xr[u][k], xr[u][k], nx);
-            }
-            fx[u] = ex2_approx(nx);
-#pragma unroll
-            for (int r = 0; r < RB; r++) acc[u][r] = 0.f;
-        }
-        for (int base = s0; base < s1; base += ST2) {
-            const int cnt = min(ST2, s1 - base);
-            __syncthreads();
-            const float4 *g = reinterpret_cast<const float4 *>(packed + (size_t)base * W);
-            float4 *sdst = reinterpret_cast<float4 *>(smem);
-            for (int q = threadIdx.x; q < cnt * (W / 4); q += NTH) sdst[q] = __ldg(g + q);
-            __syncthreads();
-            auto body = [&](int j, bool poly) {
-                float row[W];
-                const float4 *src = reinterpret_cast<const float4 *>(smem + j * W);
-#pragma unroll
-                for (int c = 0; c < W / 4; c++) {
-                    float4 v = src[c];
-                    row[4 * c] = v.x; row[4 * c + 1] = v.y; row[4 * c + 2] = v.z; row[4 * c + 3] = v.w;
-                }
-#pragma unroll
-                for (int u = 0; u < TI2; u++) {
-                    float t = xr[u][0] * row[0];
-#pragma unroll
-                    for (int k = 1; k < D; k++) t = fmaf(xr[u][k], row[k], t);
-                    const float ev = (POLY && poly) ? exp2_poly<POLY ? POLY : 2>(t) : ex2_approx(t);
-#pragma unroll
-                    for (int r = 0; r < RB; r++) acc[u][r] = fmaf(ev, row[D + r], acc[u][r]);
-                }
-            };
-            int j = 0;
-            if (POLY) {
-#pragma unroll 2
-                for (; j + 3 <= cnt; j += 3) { body(j, false); body(j + 1, true); body(j + 2, false); }
-            } else {
-#pragma unroll 8
-                for (; j + 1 <= cnt; j++) body(j, false);
-            }
-            for (; j < cnt; j++) body(j, false);
-        }
-#pragma unroll
-        for (int u = 0; u < TI2; u++)
-#pragma unroll
-            for (int r = 0; r < RB; r++) tot[u][r] = fmaf(fx[u], acc[u][r], tot[u][r]);
-    }
-#pragma unroll
-    for (int u = 0; u < TI2; u++)
-        if (ti[u] < t1) {
-#pragma unroll
-            for (int r = 0; r < RB; r++)
-                if (r0 + r < R) out[(size_t)ti[u] * R + r0 + r] += tot[u][r];
-        }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -366,7 +240,7 @@ __global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ 
                                                      const int *__restrict__ ptr, const int *__restrict__ idx,
                                                      const int *__restrict__ off_y, const float *__restrict__ ctr_y,
                                                      const float *__restrict__ packed, float scale, int R, int r0,
-                                                     float *out) {
+                                                     float *out, float pc0, float pc1, float pc2, float pc3) {
     constexpr int W = row_width(D, RB);
     __shared__ __align__(16) float smem[SP2 * 2 * W];
     int box, t0, t1;
@@ -382,8 +256,7 @@ __global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ 
 #pragma unroll
         for (int r = 0; r < RB; r++) tot[u][r] = 0.f;
     }
-    constexpr float C1 = 0.69314718056f, C2 = 0.24022650696f, C3 = 0.05550410866f;
-    const f32x2 c1 = pack2(C1, C1), c2 = pack2(C2, C2), c3 = pack2(C3, C3), one = pack2(1.f, 1.f);
+    const f32x2 c1 = pack2(pc1, pc1), c2 = pack2(pc2, pc2), c3 = pack2(pc3, pc3), one = pack2(pc0, pc0);
     const int e0 = ptr[box], e1 = ptr[box + 1];
     for (int e = e0; e < e1; e++) {
         const int by = idx[e];
@@ -469,6 +342,8 @@ __global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ 
         }
 }
 
+#include "near_mma.cuh"
+
 __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__restrict__ off_x, const int *__restrict__ ptr,
                                                          int row_begin, int row_end, int tile_pts, int *tiles) {
     int b = blockIdx.x * blockDim.x + threadIdx.x;
@@ -480,8 +355,6 @@ __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__
     }
     tiles[b] = t;
 }
-
-#include "near_mma.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // Moment form of the near field (optional, F3M_FLAG_NEAR_MOMENTS).  In the expanded form the pair term
@@ -623,6 +496,34 @@ __global__ void __launch_bounds__(128) near_taylor_kernel(const float *__restric
     }
 }
 
+// Polynomial of degree deg (<= 3) through the Chebyshev points of [tlo, thi] for 2^t, as monomial coefficients.
+// Its error is at most h^(deg+1) / (2^deg (deg+1)!) with h = ln2 (thi - tlo) / 2.
+static void exp2_poly_fit(double tlo, double thi, int deg, double (&cf)[4]) {
+    for (int i = 0; i < 4; i++) cf[i] = 0.0;
+    cf[0] = 1.0;
+    if (deg <= 0) return;
+    const int m = deg + 1;
+    double tn[4], dd[4];
+    for (int i = 0; i < m; i++) {
+        tn[i] = 0.5 * (thi + tlo) + 0.5 * (thi - tlo) * cos((2 * i + 1) * 3.14159265358979323846 / (2.0 * m));
+        dd[i] = exp2(tn[i]);
+    }
+    for (int j = 1; j < m; j++)   // Newton divided differences
+        for (int i = m - 1; i >= j; i--) dd[i] = (dd[i] - dd[i - 1]) / (tn[i] - tn[i - j]);
+    cf[0] = 0.0;
+    for (int i = m - 1; i >= 0; i--) {   // Horner on the Newton form: cf(t) = cf(t) (t - tn[i]) + dd[i]
+        for (int q = m - 1; q >= 1; q--) cf[q] = cf[q - 1] - tn[i] * cf[q];
+        cf[0] = -tn[i] * cf[0] + dd[i];
+    }
+}
+// degree that keeps the interpolation error of 2^t on an interval of half width hw below 3e-7 (0: none does)
+static int exp2_poly_degree(double hw) {
+    const double h = hw * 0.6931471805599453;
+    if (h * h * h / 24.0 <= 3e-7) return 2;
+    if (h * h * h * h / 192.0 <= 3e-7) return 3;
+    return 0;
+}
+
 static inline float near_scale(float lcs) { return sqrtf(lcs * 1.4426950408889634f); }
 
 // one list, one block of RB columns starting at r0
@@ -649,35 +550,43 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     if (items <= 0) return;
     DevBuf<float> packed;
     // the pair layout of the expanded form starts every box on an even row
-    packed.alloc((size_t)(ty.n + (expanded && !use_mma ? ly.nb + 2 : 0)) * row_width(D, RB), s);
+    if (!use_mma) packed.alloc((size_t)(ty.n + (expanded ? ly.nb + 2 : 0)) * row_width(D, RB), s);
     const unsigned g = (unsigned)((ty.n + 255) / 256);
     if (use_mma) {
-        // raw coordinates and the column: the kernel forms both operands about the target box centre
+        using S = MmaShape<D>;
+        const size_t rows = mm_rows_total(ty.n, ly.nb);
+        DevBuf<float4> Bc;
+        DevBuf<float> Gb;
+        Bc.alloc(rows * S::KC, s);
+        Gb.alloc(rows, s);
         pl->last.begin(ST_PERMUTE, s);
-        pack_sources<D, 1><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, 1.0f, packed.p);
+        pack_split_rows<D><<<g, 256, 0, s>>>(ty.pts.p, (int)ty.n, bs, R, r0, scale, ly.off.p, ly.nb, ly.ctr.p, Bc.p, rows, Gb.p);
         pl->last.end(s);
         F3M_LAUNCH_CHECK();
         int *counter = pl->d_flags + 32;
         F3M_CUDA(cudaMemsetAsync(counter, 0, sizeof(int), s));
+        // range of t = 2 u.v - |v|^2 over the pairs of the list: |u| <= reach * se, |v| <= se / 2 per dimension
         const bool final_near = (&csr == &pl->lists[level].keep);
-        const float se = scale * ly.edge;
-        const float reach = final_near ? 3.f : 6.f;   // |x - y| per dimension, in box edges, over the pairs of the list
-        const float tmax = D * reach * reach * se * se;
+        const double se = (double)scale * ly.edge, reach = final_near ? 2.5 : 5.5;
+        const double thi = D * se * se * reach, tlo = -D * se * se * (reach + 0.25);
+        const int deg = exp2_poly_degree(0.5 * (thi - tlo));
+        double cf[4];
+        exp2_poly_fit(tlo, thi, deg, cf);
         int dev = 0, nsm = 0;
         F3M_CUDA(cudaGetDevice(&dev));
         F3M_CUDA(cudaDeviceGetAttribute(&nsm, cudaDevAttrMultiProcessorCount, dev));
-        const int grid = std::min(items, nsm);
+        const int grid = std::min(items, 2 * nsm);
         pl->last.begin(ST_DIRECT, s);
-#define F3M_NEAR_MMA(DEG_, NP_)                                                                                              \
-    {                                                                                                                        \
-        F3M_CUDA(cudaFuncSetAttribute(near_mma_kernel<D, DEG_, NP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
-                                      MM_SMEM_BYTES));                                                                       \
-        near_mma_kernel<D, DEG_, NP_><<<grid, MM_THREADS, MM_SMEM_BYTES, s>>>(                                                \
-            tx.pts.p, (int)tx.n, lx.off.p, lx.ctr.p, lx.nb, tiles.p, items, csr.ptr.p, csr.idx.p, ly.off.p, packed.p, scale, \
-            R, r0, out, counter, pl->d_flags);                                                                               \
+#define F3M_NEAR_MMA(DEG_, NP_)                                                                                               \
+    {                                                                                                                         \
+        F3M_CUDA(cudaFuncSetAttribute(near_mma_kernel<D, DEG_, NP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                                      mm_smem_bytes<D>()));                                                                   \
+        near_mma_kernel<D, DEG_, NP_><<<grid, MM_THREADS, mm_smem_bytes<D>(), s>>>(                                                 \
+            tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, items, csr.ptr.p, csr.idx.p, ly.off.p, ly.ctr.p, Bc.p, rows, Gb.p, \
+            scale, R, r0, out, counter, pl->d_flags, (float)cf[0], (float)cf[1], (float)cf[2], (float)cf[3]);                 \
     }
-        if (tmax <= 0.085f) F3M_NEAR_MMA(3, 5)
-        else if (tmax <= 0.2f) F3M_NEAR_MMA(4, 4)
+        if (deg == 2) F3M_NEAR_MMA(2, 6)
+        else if (deg == 3) F3M_NEAR_MMA(3, 5)
         else F3M_NEAR_MMA(0, 0)
 #undef F3M_NEAR_MMA
         pl->last.end(s);
@@ -698,11 +607,14 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
         // for refinement (centres closer than 2 edges), 5.5 edge for "small" pairs (children of kept parents)
         const bool final_near = (&csr == &pl->lists[level].keep);
         const float se = scale * ly.edge;
-        const float tmax = D * (final_near ? 2.5f : 5.5f) * se * se;
-        const int poly = tmax <= 0.02f ? 2 : (tmax <= 0.1f ? 3 : 0);
+        const double tmax = D * (final_near ? 2.5 : 5.5) * (double)se * se;
+        const int poly = exp2_poly_degree(tmax);
+        double cf[4];
+        exp2_poly_fit(-tmax, tmax, poly, cf);
 #define F3M_NEAR_EXP(POLY_, PNUM_, PDEN_)                                                                                     \
     near_kernel_x2<D, RB, POLY_, PNUM_, PDEN_><<<items, NT2, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, \
-                                                                    csr.idx.p, ly.off.p, ly.ctr.p, packed.p, scale, R, r0, out)
+                                                                    csr.idx.p, ly.off.p, ly.ctr.p, packed.p, scale, R, r0, out, \
+                                                                    (float)cf[0], (float)cf[1], (float)cf[2], (float)cf[3])
         if (poly == 2) F3M_NEAR_EXP(2, 2, 5);
         else if (poly == 3) F3M_NEAR_EXP(3, 1, 3);
         else F3M_NEAR_EXP(0, 0, 1);
@@ -750,7 +662,7 @@ template <int D>
 static void direct_d(f3m_plan *pl, int level, const PairCSR &csr, const float *bs, int R, float *out, int rb, int re,
                      cudaStream_t s) {
     if ((pl->prm.flags & F3M_FLAG_NEAR_MOMENTS) && level > 0) {
-        // same exponent bound as the polynomial offload of near_kernel_exp (see direct_impl)
+        // exponent bound of the cross term over the pairs of the list (see direct_impl)
         const float se = near_scale(pl->lcs) * pl->ty->levels[level].edge;
         const bool final_near = (&csr == &pl->lists[level].keep);
         const float tmax = D * (final_near ? 2.5f : 5.5f) * se * se;

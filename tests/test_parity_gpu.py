@@ -196,6 +196,35 @@ def test_near_moments_flag(d, ls, R, cuda):
     assert rel_l2(a1, a0) <= 1e-7
 
 
+@pytest.mark.parametrize("d,ls,n,xy", [(3, 3.0, 40000, False), (3, 0.8, 60000, False), (2, 2.0, 30000, False),
+                                       (1, 1.0, 20000, False), (4, 4.0, 30000, False), (5, 6.0, 20000, False),
+                                       (3, 2.0, 30000, True)])
+def test_near_tensor_cores_flag(d, ls, n, xy, cuda):
+    """Optional tcgen05 form of the direct near sums: the exponent matrix of a target tile against a source tile
+    is a TF32 matrix product of split operands (exact to FP32 rounding).  It computes the same sums as the CUDA-core
+    kernels, so the two must agree to FP32 rounding and share the accuracy against float64."""
+    from f3m_b200 import engine, _lib
+    from oracle.f3m_oracle import dense_kmvm_f64
+    g = torch.Generator().manual_seed(200 + d)
+    X = torch.rand(n, d, generator=g)
+    Y = torch.rand(n // 2, d, generator=g) * 0.9 + 0.05 if xy else None
+    b = torch.randn(Y.shape[0] if xy else n, 1, generator=g)
+    P = {1: 6, 2: 36, 3: 64, 4: 81, 5: 32}[d]
+    outs = {}
+    for flags in (0, _lib.FLAG_NEAR_TENSOR_CORES):
+        prm = engine.make_params(ls, 300.0, P, False, 0.15, P, flags=flags)
+        plan = engine.Plan(X.to(cuda), None if Y is None else Y.to(cuda), prm)
+        outs[flags] = plan.apply(b.to(cuda)).cpu()
+        again = plan.apply(b.to(cuda)).cpu()
+        assert rel_l2(again, outs[flags]) <= 5e-6   # summation order of the far field may differ between runs
+        assert plan.stats()["direct_pairs"] > 0
+    assert rel_l2(outs[_lib.FLAG_NEAR_TENSOR_CORES], outs[0]) <= 5e-6
+    rows = torch.arange(1500)
+    exact = dense_kmvm_f64(X, X if Y is None else Y, b, ls, rows=rows)
+    e0, e1 = rel_l2(outs[0][rows], exact), rel_l2(outs[_lib.FLAG_NEAR_TENSOR_CORES][rows], exact)
+    assert e1 <= max(1.2 * e0, e0 + 2e-6)
+
+
 def test_dense_ops(cuda):
     from f3m_b200 import engine
     from oracle.f3m_oracle import dense_kmvm_f64

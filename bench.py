@@ -238,20 +238,30 @@ def main():
             tms.append(plan.timings())
         direct_ms = statistics.median(t["direct"] for t in tms)
         peaks = engine.measure_peaks(dev)
-        flop_per_pair = 3 * 3 + 2 * 1                       # 3d + 2R
-        slots_per_pair = 2 * 3 + 1 + 1                      # 2d + 1 + R FP32 issue slots, plus one exponential
-        peak_pairs = min(peaks["gfma_per_s"] / slots_per_pair, peaks["gexp_per_s"]) * 1e9
+        d_ = 3
+        flop_per_pair = 3 * d_ + 2 * 1                      # 3d + 2R
+        # The direct-sum kernel (near_kernel_x2) spends per pair d multiply-adds on the inner product, one on the
+        # accumulation and either one exponential (MUFU) or a degree-DEG polynomial (DEG multiply-adds) -- the share of
+        # polynomial pairs and the degree follow the rule in near.cu (direct_impl): same bound on the exponent here.
+        edge = plan.level(st["levels"])["edge"]
+        se = math.sqrt(math.log2(math.e) / (2.0 * a.ls * a.ls)) * edge
+        h = d_ * 2.5 * se * se * math.log(2.0)
+        deg, share = (2, 2 / 5) if h ** 3 / 24 <= 3e-7 else ((3, 1 / 3) if h ** 4 / 192 <= 3e-7 else (0, 0.0))
+        fma_per_pair = d_ + 1 + share * deg
+        exp_per_pair = 1.0 - share
+        peak_pairs = min(peaks["gfma_per_s"] / fma_per_pair, peaks["gexp_per_s"] / exp_per_pair) * 1e9
         achieved_pairs = st["direct_pairs"] / (direct_ms * 1e-3)
-        line["roofline"] = {"bound": "sfu+fp32-issue", "bound_note": "not hbm, not tensor: distance + exponential, no contraction; a source row is reused by every target of a tile",
+        line["roofline"] = {"bound": "fp32-fma+sfu", "bound_note": "not hbm, not tensor in the default path: inner product + exponential per pair; a source row is reused by every target of a tile",
                             "achieved": achieved_pairs * flop_per_pair / 1e12, "peak": peak_pairs * flop_per_pair / 1e12,
                             "unit": "TFLOP/s", "frac": achieved_pairs / peak_pairs,
-                            # DRAM bytes per launch from an ncu capture of this kernel at N=1e7 (377 MB = 37.7 B per point),
-                            # scaled by N: the traffic is per point (sources, targets, output)
+                            # DRAM bytes per launch from an ncu capture of this kernel at N=1e7, scaled by N: the traffic is
+                            # per point (packed sources, targets, output)
                             "traffic": 37.7 * N, "traffic_note": "37.7 B/point from the ncu capture at N=1e7, scaled to N; algorithmic minimum 36 B/point",
-                            "kernel": "near_kernel_exp<3,1,32,POLY> (all direct-sum launches of one product; a third of the exponentials run as a polynomial on the FMA pipe when the exponent is provably small)",
+                            "kernel": f"near_kernel_x2<3,1,{deg},..> (all direct-sum launches of one product; packed f32x2 arithmetic over source pairs; "
+                                      f"{share:.2f} of the pairs evaluate 2^t by a degree-{deg} polynomial on the FMA pipe)",
                             "pairs": st["direct_pairs"], "ms": direct_ms, "launches": tm["direct_launches"],
                             "peak_source": f"measured in this run by register-only probes: {peaks['gexp_per_s']:.0f} Gexp/s, "
-                                           f"{peaks['gfma_per_s']:.0f} Gfma/s; peak = min(fma/{slots_per_pair}, exp) pairs/s x {flop_per_pair} flop"}
+                                           f"{peaks['gfma_per_s']:.0f} Gfma/s; peak = min(fma/{fma_per_pair:.2f}, exp/{exp_per_pair:.2f}) pairs/s x {flop_per_pair} flop"}
         line["stages_ms"] = {k: round(v, 3) for k, v in tm.items() if k != "direct_launches"}
         line["work"] = {"levels": st["levels"], "direct_pairs": st["direct_pairs"], "far_box_pairs": st["far_box_pairs"],
                         "node_pairs_reference_form": st["node_pairs"]}
@@ -276,7 +286,22 @@ def main():
                                      "rel_l2_vs_f64": float((out_m[rows].double() - exact).norm() / exact.norm()),
                                      "note": "F3M_FLAG_NEAR_MOMENTS: near sums from 2nd/3rd-order box moments where the exponent "
                                              "is provably tiny; same pair lists; optional, off by default"}
-        del exact, out_m
+        # ---- and with the optional tcgen05 form of the near sums (same sums, exponent tiles from the tensor cores) -----
+        prm_t = engine.make_params(a.ls, a.min_points, a.nodes, False, 0.15, a.nodes, flags=f3m_lib.FLAG_NEAR_TENSOR_CORES)
+        for _ in range(2):
+            out_t = engine.kmvm(Xs, None, bs, prm_t)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.steps):
+            out_t = engine.kmvm(Xs, None, bs, prm_t)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_t = e0.elapsed_time(e1) / a.steps
+        line["near_tensor_cores_mode"] = {"ms_per_step": ms_t, "value": float(N) * float(N) / (ms_t * 1e-3), "unit": UNIT,
+                                          "rel_l2_vs_f64": float((out_t[rows].double() - exact).norm() / exact.norm()),
+                                          "note": "F3M_FLAG_NEAR_TENSOR_CORES: exponent tiles as TF32 tcgen05 products of split operands "
+                                                  "(TMEM accumulators, bulk copies, mbarrier pipeline); optional, off by default"}
+        del exact, out_m, out_t
         # ---- end to end through the host-buffer entry point ------------------------------------------------------
         Xh = torch.empty(N, 3, pin_memory=True).copy_(Xs)
         bh = torch.empty(N, 1, pin_memory=True).copy_(bs)

@@ -263,6 +263,27 @@ def main():
                             "peak_source": f"measured in this run by register-only probes: {peaks['gexp_per_s']:.0f} Gexp/s, "
                                            f"{peaks['gfma_per_s']:.0f} Gfma/s; peak = min(fma/{fma_per_pair:.2f}, exp/{exp_per_pair:.2f}) pairs/s x {flop_per_pair} flop"}
         line["stages_ms"] = {k: round(v, 3) for k, v in tm.items() if k != "direct_launches"}
+        # ---- per-stage rooflines from the algorithmic work (bytes against the measured copy bandwidth, multiply-adds
+        # against the FMA peak measured above); the slower of the two is the stage's bound ------------------------------
+        try:
+            with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as fh:
+                hbm_gbs, hbm_src = float(json.load(fh)["hbm_gbs"]), "of measured"
+        except Exception:
+            hbm_gbs, hbm_src = 6650.0, "of fallback"
+        nb_leaf = plan.level(st["levels"])["boxes_x"]
+        Pn = plan.level(st["levels"])["nodes_per_dim"] ** d_
+        fma_s = peaks["gfma_per_s"] * 1e9
+        def stage_roof(ms, nbytes, fmas):
+            t_b, t_f = nbytes / (hbm_gbs * 1e9) * 1e3, fmas / fma_s * 1e3
+            return {"ms": round(ms, 3), "hbm_roof_ms": round(t_b, 3), "fma_roof_ms": round(t_f, 3), "frac": round(max(t_b, t_f) / ms, 3)}
+        line["stages_roofline"] = {
+            "hbm_peak_gbs": hbm_gbs, "hbm_peak": hbm_src,
+            "tree+lists": stage_roof(tm["build"], N * (2 * 4 * d_ + 2 * 4 + 8), 0),        # sort traffic: 40 B/point at d=3, R=1
+            "p2m": stage_roof(tm["p2m"], N * (4 * d_ + 4) + nb_leaf * Pn * 4, N * Pn),
+            "m2l": stage_roof(tm["m2l"], 2 * nb_leaf * Pn * 4, st["far_box_pairs"] * d_ * plan.level(st["levels"])["nodes_per_dim"] * Pn),
+            "l2p": stage_roof(tm["l2p"], N * (4 * d_ + 8) + nb_leaf * Pn * 4, N * Pn),
+            "direct": {"ms": round(direct_ms, 3), "frac": round(achieved_pairs / peak_pairs, 3)},
+            "note": "m2l multiply-adds counted in the per-pair form (d axis transforms per far pair); the nested kernel does fewer"}
         line["work"] = {"levels": st["levels"], "direct_pairs": st["direct_pairs"], "far_box_pairs": st["far_box_pairs"],
                         "node_pairs_reference_form": st["node_pairs"]}
         rows = torch.randperm(N, device=dev, generator=g)[:a.check_rows]

@@ -787,6 +787,157 @@ __global__ void __launch_bounds__(128) l2p_leaf(const float *__restrict__ pts, i
 }
 
 // ---------------------------------------------------------------------------------------------
+// P2M / L2P for d = 3 and one column, register-tiled.  A lane is (point stream, m2): it keeps the PP x PP block
+// (m0, m1) of the box's moments (or local expansion) for its m2 in registers, so a point costs the lane PP
+// multiplies and PP^2 multiply-adds against 4 broadcast 16-byte loads and one 4-byte load of the point's Lagrange
+// rows -- the multiply-add rate, not shared memory, is the limit.  32 / PP streams per warp, 4 warps per CTA, one box
+// per CTA (blockIdx.y splits very large boxes).  The rows [L0 (8) | L1 (8) | L2 (8) | pad (4)] are 28 floats apart,
+// which puts the rows of the streams of one warp on different banks.
+// ---------------------------------------------------------------------------------------------
+constexpr int L3_RS = 28;
+template <int PP>
+struct Leaf3 {
+    static constexpr int SUB = 32 / PP;              // point streams per warp
+    static constexpr int NSTREAM = 4 * SUB;          // per CTA
+    static constexpr int TP = NSTREAM * (128 / NSTREAM);   // points per chunk
+};
+
+template <int PP>
+__device__ __forceinline__ void leaf3_rows(const float *__restrict__ pts, int n, int i, const float (&c)[3], float factor,
+                                           const NodeTab2 &nt, float scale2, float *row) {
+    float L[PP];
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+        lagrange_pp<PP>(factor * (pts[(size_t)k * n + i] - c[k]), nt, L);
+#pragma unroll
+        for (int q = 0; q < PP; q++) row[8 * k + q] = (k == 2) ? scale2 * L[q] : L[q];
+    }
+}
+
+template <int PP>
+__global__ void __launch_bounds__(128) p2m_leaf3(const float *__restrict__ pts, int n, const float *__restrict__ bs, int R, int r0,
+                                                const int *__restrict__ off, const float *__restrict__ ctr, float factor,
+                                                NodeTab2 nt, int nsplit, int src_begin, int src_end, float *mom) {
+    using G = Leaf3<PP>;
+    constexpr int P = PP * PP * PP;
+    // the Lagrange rows of a chunk; after the last chunk the same memory holds one partial moment array per stream
+    constexpr int NSCR = (G::TP * L3_RS > G::NSTREAM * P) ? G::TP * L3_RS : G::NSTREAM * P;
+    __shared__ __align__(16) float rows[NSCR];
+    const int box = blockIdx.x;
+    const int a = off[box], b = off[box + 1];
+    if (a < src_begin || a >= src_end) return;      // only the boxes of this slice of the sorted sources
+    const int len = b - a;
+    const int s0 = a + (int)(((long long)len * blockIdx.y) / nsplit), s1 = a + (int)(((long long)len * (blockIdx.y + 1)) / nsplit);
+    if (s0 >= s1) return;
+    const float c[3] = {ctr[box * 3], ctr[box * 3 + 1], ctr[box * 3 + 2]};
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / PP, m2 = lane - sub * PP;
+    const bool active = sub < G::SUB;
+    const int stream = warp * G::SUB + sub;
+    float acc[PP][PP];
+#pragma unroll
+    for (int i = 0; i < PP; i++)
+#pragma unroll
+        for (int j = 0; j < PP; j++) acc[i][j] = 0.f;
+    for (int base = s0; base < s1; base += G::TP) {
+        const int cnt = min(G::TP, s1 - base);
+        __syncthreads();
+        if ((int)threadIdx.x < cnt)   // the column value rides on the L2 row
+            leaf3_rows<PP>(pts, n, base + threadIdx.x, c, factor, nt, bs[(size_t)(base + threadIdx.x) * R + r0], rows + threadIdx.x * L3_RS);
+        __syncthreads();
+        if (active)
+            for (int j = stream; j < cnt; j += G::NSTREAM) {
+                const float *row = rows + j * L3_RS;
+                const float4 a0 = *reinterpret_cast<const float4 *>(row), a1 = *reinterpret_cast<const float4 *>(row + 4);
+                const float4 b0 = *reinterpret_cast<const float4 *>(row + 8), b1 = *reinterpret_cast<const float4 *>(row + 12);
+                const float l0[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                const float l1[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                const float w2 = row[16 + m2];
+#pragma unroll
+                for (int i1 = 0; i1 < PP; i1++) {
+                    const float u = w2 * l1[i1];
+#pragma unroll
+                    for (int i0 = 0; i0 < PP; i0++) acc[i1][i0] = fmaf(u, l0[i0], acc[i1][i0]);
+                }
+            }
+    }
+    __syncthreads();
+    if (active) {
+        float *mine = rows + stream * P + PP * PP * m2;
+#pragma unroll
+        for (int i1 = 0; i1 < PP; i1++)
+#pragma unroll
+            for (int i0 = 0; i0 < PP; i0++) mine[i0 + PP * i1] = acc[i1][i0];
+    }
+    __syncthreads();
+    float *dst = mom + (size_t)box * P;
+    for (int q = threadIdx.x; q < P; q += 128) {
+        float v = 0.f;
+#pragma unroll
+        for (int st = 0; st < G::NSTREAM; st++) v += rows[st * P + q];
+        if (nsplit == 1) dst[q] = v;
+        else atomicAdd(dst + q, v);
+    }
+}
+
+template <int PP>
+__global__ void __launch_bounds__(128) l2p_leaf3(const float *__restrict__ pts, int n, const int *__restrict__ off,
+                                                const float *__restrict__ ctr, float factor, NodeTab2 nt, int nsplit,
+                                                int row_begin, int row_end, const float *__restrict__ loc, int R, int r0,
+                                                float *out) {
+    using G = Leaf3<PP>;
+    constexpr int P = PP * PP * PP;
+    __shared__ __align__(16) float rows[G::TP * L3_RS];
+    __shared__ float part[G::TP * 8];   // per point: the PP partial sums over m2
+    const int box = blockIdx.x;
+    const int a = off[box], b = off[box + 1];
+    if (a < row_begin || a >= row_end) return;    // finest-level boxes belong to the slice their first point is in
+    const int len = b - a;
+    const int s0 = a + (int)(((long long)len * blockIdx.y) / nsplit), s1 = a + (int)(((long long)len * (blockIdx.y + 1)) / nsplit);
+    if (s0 >= s1) return;
+    const float c[3] = {ctr[box * 3], ctr[box * 3 + 1], ctr[box * 3 + 2]};
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane / PP, m2 = lane - sub * PP;
+    const bool active = sub < G::SUB;
+    const int stream = warp * G::SUB + sub;
+    float lc[PP][PP];   // loc[m0][m1][m2] of this lane's m2
+#pragma unroll
+    for (int i1 = 0; i1 < PP; i1++)
+#pragma unroll
+        for (int i0 = 0; i0 < PP; i0++) lc[i1][i0] = active ? __ldg(loc + (size_t)box * P + i0 + PP * i1 + PP * PP * m2) : 0.f;
+    for (int base = s0; base < s1; base += G::TP) {
+        const int cnt = min(G::TP, s1 - base);
+        __syncthreads();
+        if ((int)threadIdx.x < cnt) leaf3_rows<PP>(pts, n, base + threadIdx.x, c, factor, nt, 1.f, rows + threadIdx.x * L3_RS);
+        __syncthreads();
+        if (active)
+            for (int j = stream; j < cnt; j += G::NSTREAM) {
+                const float *row = rows + j * L3_RS;
+                const float4 a0 = *reinterpret_cast<const float4 *>(row), a1 = *reinterpret_cast<const float4 *>(row + 4);
+                const float4 b0 = *reinterpret_cast<const float4 *>(row + 8), b1 = *reinterpret_cast<const float4 *>(row + 12);
+                const float l0[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                const float l1[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                float sacc = 0.f;
+#pragma unroll
+                for (int i1 = 0; i1 < PP; i1++) {
+                    float t = 0.f;
+#pragma unroll
+                    for (int i0 = 0; i0 < PP; i0++) t = fmaf(l0[i0], lc[i1][i0], t);
+                    sacc = fmaf(l1[i1], t, sacc);
+                }
+                part[j * 8 + m2] = row[16 + m2] * sacc;
+            }
+        __syncthreads();
+        if ((int)threadIdx.x < cnt) {
+            float v = 0.f;
+#pragma unroll
+            for (int q = 0; q < PP; q++) v += part[threadIdx.x * 8 + q];
+            out[(size_t)(base + threadIdx.x) * R + r0] += v;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host driver
 // ---------------------------------------------------------------------------------------------
 template <int PP, int RB>
@@ -810,6 +961,11 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
         size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
         F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         pl->last.begin(ST_P2M, s);
+        if (RB == 1 && d == 3)
+            p2m_leaf3<PP><<<dim3(ly.nb, nsplit), 128, 0, s>>>(ty.pts.p, n_y, bs, R, r0, ly.off.p, ly.ctr.p, 2.f / ly.edge, nt,
+                                                            nsplit > 1 ? nsplit : 1, (int)pl->mom_begin, (int)pl->mom_end,
+                                                            pl->moments_out);
+        else
         p2m_leaf<PP, RB><<<dim3(ly.nb, nsplit), 256, smem, s>>>(ty.pts.p, n_y, d, bs, R, r0, ly.off.p, ly.ctr.p, 2.f / ly.edge, nt, P,
                                                               nsplit > 1 ? nsplit : 1, (int)pl->mom_begin, (int)pl->mom_end,
                                                               pl->moments_out);
@@ -851,6 +1007,10 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
             if (nsplit > 1) mom[L].zero();
             size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
             F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (RB == 1 && d == 3)
+                p2m_leaf3<PP><<<dim3(ly.nb, nsplit), 128, 0, s>>>(ty.pts.p, n_y, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt, nsplit, 0, n_y,
+                                                                mom[L].p);
+            else
             p2m_leaf<PP, RB><<<dim3(ly.nb, nsplit), 256, smem, s>>>(ty.pts.p, n_y, d, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt, P,
                                                                   nsplit, 0, n_y, mom[L].p);
             F3M_LAUNCH_CHECK();
@@ -956,6 +1116,10 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
         int nsplit = std::max(1, std::min(64, (lx.max_count + 8191) / 8192));
         size_t smem = ((size_t)PR + (size_t)std::max(1, d - 1) * PP * 128) * sizeof(float);
         F3M_CUDA(cudaFuncSetAttribute(l2p_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (RB == 1 && d == 3)
+            l2p_leaf3<PP><<<dim3(lx.nb, nsplit), 128, 0, s>>>(tx.pts.p, n_x, lx.off.p, lx.ctr.p, factor, nt, nsplit, rb, re, loc[L].p, R,
+                                                            r0, out);
+        else
         l2p_leaf<PP, RB><<<dim3(lx.nb, nsplit), 128, smem, s>>>(tx.pts.p, n_x, d, lx.off.p, lx.ctr.p, factor, nt, P, nsplit, rb, re,
                                                                loc[L].p, R, r0, out);
         F3M_LAUNCH_CHECK();

@@ -128,8 +128,9 @@ __device__ __forceinline__ float tf32_head(float x) { return __uint_as_float(__f
 
 }   // namespace tc
 
-constexpr int MM_M = 128, MM_N = 128, MM_BUFS = 2, MM_AR = MM_BUFS, MM_CONSUMERS = 256, MM_THREADS = MM_CONSUMERS + 32, MM_ROWCHUNK = 256, MM_SLOTS = 8;
-constexpr int MM_PRODUCER = MM_CONSUMERS;   // first lane of the extra warp: copies and MMA issue
+constexpr int MM_M = 128, MM_N = 128, MM_BUFS = 2, MM_AR = MM_BUFS, MM_CONSUMERS = 256, MM_THREADS = MM_CONSUMERS + 64, MM_ROWCHUNK = 256, MM_SLOTS = 8;
+constexpr int MM_PRODUCER = MM_CONSUMERS;      // first lane of the first extra warp: issues the MMAs
+constexpr int MM_COPIER = MM_CONSUMERS + 32;   // first lane of the second extra warp: starts the bulk copies
 
 template <int D>
 struct MmaShape {
@@ -369,52 +370,53 @@ near_mma_kernel(const float *__restrict__ xpts, int n_x, const int *__restrict__
                 }
                 tc::fence_async_smem();
                 __syncthreads();
-                if (tid == MM_PRODUCER) {
-                    // ---- producer: bulk copies MM_SLOTS-1 tiles ahead, MMAs one tile behind the consumers' release ----
-                    auto start_copies = [&](const MmCursor &c, unsigned k) {
-                        const unsigned slot = k % MM_SLOTS;
-                        const uint32_t ncols = (uint32_t)min(MM_N, cntp[c.e] - c.base);
-                        const size_t g = (size_t)rowst[c.e] + c.base;
+                if (tid == MM_COPIER) {
+                    // ---- copy thread: runs as far ahead as the MM_SLOTS slots allow; a slot is free once the tile that
+                    // used it before has been consumed ----
+                    MmCursor cp = first;
+                    for (unsigned kp = gk; valid(cp) && !abort_s; kp++, cp = advance(cp)) {
+                        if (kp >= MM_SLOTS) bounded_wait(bar_late + 8u * (kp % MM_SLOTS), ((kp - MM_SLOTS) / MM_SLOTS) & 1u);
+                        const unsigned slot = kp % MM_SLOTS;
+                        const uint32_t ncols = (uint32_t)min(MM_N, cntp[cp.e] - cp.base);
+                        const size_t g = (size_t)rowst[cp.e] + cp.base;
                         const uint32_t bar = bar_copy + 8u * slot;
                         tc::mbar_expect_tx(bar, ncols * (16u * KC + 4u));
 #pragma unroll
                         for (int kc = 0; kc < KC; kc++)
                             tc::bulk_g2s(b_addr + (slot * B_ONE + kc * MM_N) * 16u, Bc + (size_t)kc * rows + g, ncols * 16u, bar);
                         tc::bulk_g2s(bs_addr + slot * MM_N * 4u, Gb + g, ncols * 4u, bar);
-                    };
-                    MmCursor cp = first, cm = first;
-                    unsigned kp = gk, km = gk;
-                    // Copies run MM_AHEAD tiles ahead of the MMAs.  The MMAs may run MM_BUFS tiles ahead of the consumers, so the
-                    // slot refilled at tile km (that of tile km + MM_AHEAD - MM_SLOTS) belongs to a tile the consumers have left.
-                    constexpr int MM_AHEAD = MM_SLOTS - MM_BUFS - 1;
-                    for (int a = 0; a < MM_AHEAD && valid(cp); a++) {   // the previous row chunk has drained: slots are free
-                        start_copies(cp, kp++);
-                        cp = advance(cp);
                     }
-                    while (valid(cm) && !abort_s) {
+                } else if (tid == MM_PRODUCER) {
+                    // ---- MMA thread: tile km as soon as its copies have landed and TMEM buffer km % MM_BUFS has been read ----
+                    // descriptors of the A buffers (ring position x {A1, A2} x K step) and of slot 0 of B
+                    uint64_t adesc[MM_AR][2][S::KS], bdesc0[S::KS];
+#pragma unroll
+                    for (int r = 0; r < MM_AR; r++)
+#pragma unroll
+                        for (int m = 0; m < 2; m++)
+#pragma unroll
+                            for (int ks = 0; ks < S::KS; ks++)
+                                adesc[r][m][ks] = tc::smem_desc(a_addr + (uint32_t)r * A_ONE * 16u + (m * KC + 2 * ks) * (MM_M * 16), MM_M * 16, 128);
+#pragma unroll
+                    for (int ks = 0; ks < S::KS; ks++) bdesc0[ks] = tc::smem_desc(b_addr + 2 * ks * (MM_N * 16), MM_N * 16, 128);
+                    MmCursor cm = first;
+                    for (unsigned km = gk; valid(cm) && !abort_s; km++, cm = advance(cm)) {
                         bounded_wait(bar_copy + 8u * (km % MM_SLOTS), (km / MM_SLOTS) & 1u);
                         if (km >= MM_BUFS) bounded_wait(bar_read + 8u * (km % MM_BUFS), ((km - MM_BUFS) / MM_BUFS) & 1u);   // buffer read back, A rows built
                         tc::fence_after_sync();
-                        const unsigned slot = km % MM_SLOTS;
                         const uint32_t d_tmem = tmem + (km % MM_BUFS) * MM_N;
-                        const uint32_t a0 = a_addr + (uint32_t)cm.par * A_ONE * 16u, b0 = b_addr + slot * B_ONE * 16u;
+                        const uint64_t bslot = (uint64_t)(((km % MM_SLOTS) * B_ONE * 16u) >> 4);   // start-address field counts 16-byte units
 #pragma unroll
                         for (int m = 0; m < 2; m++)
 #pragma unroll
                             for (int ks = 0; ks < S::KS; ks++) {
-                                const uint64_t ad = tc::smem_desc(a0 + (m * KC + 2 * ks) * (MM_M * 16), MM_M * 16, 128);
-                                const uint64_t bd = tc::smem_desc(b0 + 2 * ks * (MM_N * 16), MM_N * 16, 128);
-                                tc::mma_tf32(d_tmem, ad, bd, IDESC, (m | ks) ? 1u : 0u);
+                                uint64_t ad = adesc[0][m][ks];
+#pragma unroll
+                                for (int r = 1; r < MM_AR; r++)
+                                    if (cm.par == r) ad = adesc[r][m][ks];
+                                tc::mma_tf32(d_tmem, ad, bdesc0[ks] + bslot, IDESC, (m | ks) ? 1u : 0u);
                             }
                         tc::mma_commit(bar_acc + 8u * (km % MM_BUFS));
-                        // keep the copies MM_AHEAD tiles ahead: the slot is free once its previous tile has been consumed
-                        if (valid(cp)) {
-                            if (kp >= MM_SLOTS) bounded_wait(bar_late + 8u * (kp % MM_SLOTS), ((kp - MM_SLOTS) / MM_SLOTS) & 1u);
-                            start_copies(cp, kp++);
-                            cp = advance(cp);
-                        }
-                        km++;
-                        cm = advance(cm);
                     }
                 } else if (consumer) {
                     // ---- consumers ----

@@ -225,6 +225,28 @@ def test_near_tensor_cores_flag(d, ls, n, xy, cuda):
     assert e1 <= max(1.2 * e0, e0 + 2e-6)
 
 
+@pytest.mark.parametrize("p", [2, 3, 4, 5, 6, 7, 8])
+def test_far_field_node_counts_d3(p, cuda):
+    """Every node count of the fast far-field path in three dimensions (P2M/L2P register tiling, nested M2L) against
+    the CPU restatement, and the interpolation error against float64 must fall with the node count."""
+    from f3m_b200 import engine, _lib
+    from oracle.f3m_oracle import f3m_kmvm, dense_kmvm_f64
+    g = torch.Generator().manual_seed(300 + p)
+    n = 12000
+    X = torch.rand(n, 3, generator=g) * 3.0
+    b = torch.randn(n, 1, generator=g)
+    P = p ** 3
+    prm = engine.make_params(1.0, 100.0, P, False, 0.15, 20, math_mode=_lib.MATH_IEEE)
+    out = engine.kmvm(X.to(cuda), None, b.to(cuda), prm).cpu()
+    ref = f3m_kmvm(X, None, b, 1.0, min_points=100.0, nr_of_interpolation=P, small_field_points=20)
+    exact = dense_kmvm_f64(X, X, b, 1.0)
+    e_ref, e_out = rel_l2(ref, exact), rel_l2(out, exact)
+    print(f"p={p}: error of the restatement {e_ref:.3e}, of the engine {e_out:.3e}, between them {rel_l2(out, ref):.3e}")
+    assert rel_l2(out, ref) <= max(1e-5, 0.2 * e_ref)       # same algorithm, different summation order
+    assert e_out <= 1.2 * e_ref + 2e-6
+    assert e_out <= {2: 0.5, 3: 0.2, 4: 5e-2, 5: 1e-2, 6: 3e-3, 7: 6e-4, 8: 2e-4}[p]
+
+
 def test_dense_ops(cuda):
     from f3m_b200 import engine
     from oracle.f3m_oracle import dense_kmvm_f64

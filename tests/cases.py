@@ -45,8 +45,29 @@ def _draw(dist, n, d, g):
     raise ValueError(dist)
 
 
-def make_case(name):
-    c = dict(CASES[name])
+def random_cases(count, seed=2024):
+    """Seeded random configurations (dimension, sizes, distribution, lengthscale, leaf size, node count, list
+    thresholds, variance compression, columns) for the randomized parity sweep."""
+    rng = np.random.RandomState(seed)
+    out = {}
+    for i in range(count):
+        d = int(rng.randint(1, 6))
+        p = int(rng.randint(2, {1: 9, 2: 7, 3: 6, 4: 4, 5: 4}[d]))
+        P = p ** d
+        n = int(rng.randint(300, 7000))
+        xy = rng.rand() < 0.35
+        out[f"rand{i:02d}"] = dict(
+            d=d, N=n, M=int(rng.randint(200, 5000)) if xy else None,
+            dist=["uniform", "uniform_sqrt12", "normal", "clustered", "duplicates"][int(rng.randint(0, 5))],
+            ls=float(np.exp(rng.uniform(np.log(0.08), np.log(4.0)))), min_points=float([20, 50, 100, 300][int(rng.randint(0, 4))]),
+            P=P, small=int([P, 2 * P, 30, 1000][int(rng.randint(0, 4))]), var_comp=bool(rng.rand() < 0.3),
+            eff=float([0.15, 0.3, 0.9, 0.001][int(rng.randint(0, 4))]), R=int([1, 1, 2, 3, 8][int(rng.randint(0, 5))]),
+            seed=1000 + i)
+    return out
+
+
+def make_case(name, table=None):
+    c = dict((table or CASES)[name])
     g = torch.Generator().manual_seed(c["seed"])
     X = _draw(c["dist"], c["N"], c["d"], g).float().contiguous()
     Y = None if c["M"] is None else (_draw(c["dist"], c["M"], c["d"], g) * 0.9 + 0.05 + c.get("y_shift", 0.0)).float().contiguous()

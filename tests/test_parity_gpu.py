@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from cases import CASES, make_case, oracle_kwargs, rel_l2
+from cases import CASES, make_case, oracle_kwargs, random_cases, rel_l2
 
 pytestmark = pytest.mark.gpu
 
@@ -25,11 +25,23 @@ def _run_engine(c, dev, math_mode):
     return plan, out
 
 
+RANDOM_CASES = random_cases(24)
+
+
+@pytest.mark.parametrize("name", list(RANDOM_CASES))
+def test_engine_matches_oracle_random_configs(name, cuda):
+    """Randomized sweep over the parameter space (seeded): same checks as the named cases."""
+    _check_against_oracle(make_case(name, RANDOM_CASES), cuda)
+
+
 @pytest.mark.parametrize("name", list(CASES))
 def test_engine_matches_oracle(name, cuda):
+    _check_against_oracle(make_case(name), cuda)
+
+
+def _check_against_oracle(c, cuda):
     from f3m_b200 import _lib
     from oracle.f3m_oracle import f3m_kmvm, dense_kmvm_f64
-    c = make_case(name)
     trace, stats = [], {}
     ref = f3m_kmvm(c["X"], c["Y"], c["b"], trace=trace, stats=stats, **oracle_kwargs(c))
     plan, out = _run_engine(c, cuda, _lib.MATH_IEEE)

@@ -169,6 +169,11 @@ struct f3m_plan {
     f3m::Timings last;
     // sharded moments (multi-GPU): either write the finest-level moments of a slice of the source boxes
     // into moments_out and stop, or take the complete finest-level moments from ext_mom instead of computing them
+    // finest-level boxes split by size for P2M / L2P (index 0: target tree, 1: source tree): boxes of at most
+    // LEAF_SMALL points are handled one per warp, the others one per CTA; built on first use
+    f3m::DevBuf<int> leaf_small[2], leaf_big[2];
+    int n_leaf_small[2] = {0, 0}, n_leaf_big[2] = {0, 0};
+    bool leaf_split[2] = {false, false};
     float *moments_out = nullptr;
     int64_t mom_begin = 0, mom_end = 0;
     const float *ext_mom = nullptr;

@@ -817,13 +817,14 @@ __device__ __forceinline__ void leaf3_rows(const float *__restrict__ pts, int n,
 template <int PP>
 __global__ void __launch_bounds__(128) p2m_leaf3(const float *__restrict__ pts, int n, const float *__restrict__ bs, int R, int r0,
                                                 const int *__restrict__ off, const float *__restrict__ ctr, float factor,
-                                                NodeTab2 nt, int nsplit, int src_begin, int src_end, float *mom) {
+                                                NodeTab2 nt, int nsplit, int src_begin, int src_end, float *mom,
+                                                const int *__restrict__ box_list) {
     using G = Leaf3<PP>;
     constexpr int P = PP * PP * PP;
     // the Lagrange rows of a chunk; after the last chunk the same memory holds one partial moment array per stream
     constexpr int NSCR = (G::TP * L3_RS > G::NSTREAM * P) ? G::TP * L3_RS : G::NSTREAM * P;
     __shared__ __align__(16) float rows[NSCR];
-    const int box = blockIdx.x;
+    const int box = box_list ? box_list[blockIdx.x] : (int)blockIdx.x;
     const int a = off[box], b = off[box + 1];
     if (a < src_begin || a >= src_end) return;      // only the boxes of this slice of the sorted sources
     const int len = b - a;
@@ -884,12 +885,12 @@ template <int PP>
 __global__ void __launch_bounds__(128) l2p_leaf3(const float *__restrict__ pts, int n, const int *__restrict__ off,
                                                 const float *__restrict__ ctr, float factor, NodeTab2 nt, int nsplit,
                                                 int row_begin, int row_end, const float *__restrict__ loc, int R, int r0,
-                                                float *out) {
+                                                float *out, const int *__restrict__ box_list) {
     using G = Leaf3<PP>;
     constexpr int P = PP * PP * PP;
     __shared__ __align__(16) float rows[G::TP * L3_RS];
     __shared__ float part[G::TP * 8];   // per point: the PP partial sums over m2
-    const int box = blockIdx.x;
+    const int box = box_list ? box_list[blockIdx.x] : (int)blockIdx.x;
     const int a = off[box], b = off[box + 1];
     if (a < row_begin || a >= row_end) return;    // finest-level boxes belong to the slice their first point is in
     const int len = b - a;
@@ -937,6 +938,106 @@ __global__ void __launch_bounds__(128) l2p_leaf3(const float *__restrict__ pts, 
     }
 }
 
+// Small finest-level boxes (clustered data leaves millions of boxes with a handful of points): one warp per box, so
+// that a box costs a few hundred instructions instead of a CTA's launch, barriers and reductions.
+constexpr int LEAF_SMALL = 32;
+
+__global__ void __launch_bounds__(256) split_leaf_boxes(int nb, const int *__restrict__ off, int *small_list, int *big_list, int *counts) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= nb) return;
+    const int len = off[b + 1] - off[b];
+    if (len <= LEAF_SMALL) small_list[atomicAdd(counts, 1)] = b;
+    else big_list[atomicAdd(counts + 1, 1)] = b;
+}
+
+// P2M: lanes = nodes (ceil(P / 32) per lane), points in turn; the points' Lagrange rows go through shared memory
+template <int PP>
+__global__ void __launch_bounds__(128) p2m_small3(const float *__restrict__ pts, int n, const float *__restrict__ bs, int R, int r0,
+                                                 const int *__restrict__ off, const float *__restrict__ ctr, float factor,
+                                                 NodeTab2 nt, int src_begin, int src_end, float *mom,
+                                                 const int *__restrict__ box_list, int nlist) {
+    constexpr int P = PP * PP * PP, NPL = (P + 31) / 32;
+    __shared__ __align__(16) float rows_s[4][LEAF_SMALL * L3_RS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int li = blockIdx.x * 4 + warp;
+    if (li >= nlist) return;
+    const int box = box_list[li];
+    const int a = off[box], len = off[box + 1] - a;
+    if (a < src_begin || a >= src_end) return;
+    const float c[3] = {ctr[box * 3], ctr[box * 3 + 1], ctr[box * 3 + 2]};
+    float *rows = rows_s[warp];
+    if (lane < len) leaf3_rows<PP>(pts, n, a + lane, c, factor, nt, bs[(size_t)(a + lane) * R + r0], rows + lane * L3_RS);
+    __syncwarp();
+    float acc[NPL];
+    int o0[NPL], o1[NPL], o2[NPL];
+#pragma unroll
+    for (int q = 0; q < NPL; q++) {
+        const int m = min(lane + 32 * q, P - 1);
+        acc[q] = 0.f;
+        o0[q] = m % PP; o1[q] = 8 + (m / PP) % PP; o2[q] = 16 + m / (PP * PP);
+    }
+    for (int j = 0; j < len; j++) {
+        const float *row = rows + j * L3_RS;
+#pragma unroll
+        for (int q = 0; q < NPL; q++) acc[q] = fmaf(row[o2[q]] * row[o1[q]], row[o0[q]], acc[q]);
+    }
+#pragma unroll
+    for (int q = 0; q < NPL; q++)
+        if (lane + 32 * q < P) mom[(size_t)box * P + lane + 32 * q] = acc[q];
+}
+
+// L2P: lanes = points; the box's local expansion is staged in shared memory and read by every lane
+template <int PP>
+__global__ void __launch_bounds__(128) l2p_small3(const float *__restrict__ pts, int n, const int *__restrict__ off,
+                                                 const float *__restrict__ ctr, float factor, NodeTab2 nt, int row_begin,
+                                                 int row_end, const float *__restrict__ loc, int R, int r0, float *out,
+                                                 const int *__restrict__ box_list, int nlist) {
+    constexpr int P = PP * PP * PP;
+    __shared__ float loc_s[4][P];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int li = blockIdx.x * 4 + warp;
+    if (li >= nlist) return;
+    const int box = box_list[li];
+    const int a = off[box], len = off[box + 1] - a;
+    if (a < row_begin || a >= row_end) return;
+    for (int q = lane; q < P; q += 32) loc_s[warp][q] = __ldg(loc + (size_t)box * P + q);
+    __syncwarp();
+    if (lane >= len) return;
+    const float c[3] = {ctr[box * 3], ctr[box * 3 + 1], ctr[box * 3 + 2]};
+    float row[24];
+    leaf3_rows<PP>(pts, n, a + lane, c, factor, nt, 1.f, row);
+    float v = 0.f;
+#pragma unroll
+    for (int i2 = 0; i2 < PP; i2++) {
+        float s2 = 0.f;
+#pragma unroll
+        for (int i1 = 0; i1 < PP; i1++) {
+            float s1 = 0.f;
+#pragma unroll
+            for (int i0 = 0; i0 < PP; i0++) s1 = fmaf(row[i0], loc_s[warp][i0 + PP * i1 + PP * PP * i2], s1);
+            s2 = fmaf(row[8 + i1], s1, s2);
+        }
+        v = fmaf(row[16 + i2], s2, v);
+    }
+    out[(size_t)(a + lane) * R + r0] += v;
+}
+
+// lists of the small and the large finest-level boxes of one tree (0: targets, 1: sources), built once per plan
+static void ensure_leaf_split(f3m_plan *pl, int which, Level &lv, cudaStream_t s) {
+    if (pl->leaf_split[which]) return;
+    pl->leaf_small[which].alloc((size_t)lv.nb, s);
+    pl->leaf_big[which].alloc((size_t)lv.nb, s);
+    int *counts = pl->d_flags + 40;
+    F3M_CUDA(cudaMemsetAsync(counts, 0, 2 * sizeof(int), s));
+    split_leaf_boxes<<<(lv.nb + 255) / 256, 256, 0, s>>>(lv.nb, lv.off.p, pl->leaf_small[which].p, pl->leaf_big[which].p, counts);
+    F3M_LAUNCH_CHECK();
+    F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, counts, 2 * sizeof(int), cudaMemcpyDeviceToHost, s));
+    F3M_CUDA(cudaStreamSynchronize(s));
+    pl->n_leaf_small[which] = pl->h_pinned[0];
+    pl->n_leaf_big[which] = pl->h_pinned[1];
+    pl->leaf_split[which] = true;
+}
+
 // ---------------------------------------------------------------------------------------------
 // host driver
 // ---------------------------------------------------------------------------------------------
@@ -952,6 +1053,10 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
     NodeTab2 nt = make_nodes2(PP);
     const KronCfg cfg = make_kron_cfg(d, PP, RB);
     const int n_x = (int)tx.n, n_y = (int)ty.n;
+    if (RB == 1 && d == 3) {
+        ensure_leaf_split(pl, 0, tx.levels[L], s);
+        if (!pl->same) ensure_leaf_split(pl, 1, ty.levels[L], s);
+    }
 
     if (pl->moments_out) {
         // sharded P2M: finest-level moments of the source boxes that start in [mom_begin, mom_end), zero elsewhere
@@ -961,11 +1066,17 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
         size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
         F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         pl->last.begin(ST_P2M, s);
-        if (RB == 1 && d == 3)
-            p2m_leaf3<PP><<<dim3(ly.nb, nsplit), 128, 0, s>>>(ty.pts.p, n_y, bs, R, r0, ly.off.p, ly.ctr.p, 2.f / ly.edge, nt,
-                                                            nsplit > 1 ? nsplit : 1, (int)pl->mom_begin, (int)pl->mom_end,
-                                                            pl->moments_out);
-        else
+        if (RB == 1 && d == 3) {
+            const int wy = pl->same ? 0 : 1;
+            if (pl->n_leaf_big[wy])
+                p2m_leaf3<PP><<<dim3(pl->n_leaf_big[wy], nsplit), 128, 0, s>>>(ty.pts.p, n_y, bs, R, r0, ly.off.p, ly.ctr.p, 2.f / ly.edge, nt,
+                                                                             nsplit > 1 ? nsplit : 1, (int)pl->mom_begin, (int)pl->mom_end,
+                                                                             pl->moments_out, pl->leaf_big[wy].p);
+            if (pl->n_leaf_small[wy])
+                p2m_small3<PP><<<(pl->n_leaf_small[wy] + 3) / 4, 128, 0, s>>>(ty.pts.p, n_y, bs, R, r0, ly.off.p, ly.ctr.p, 2.f / ly.edge, nt,
+                                                                            (int)pl->mom_begin, (int)pl->mom_end, pl->moments_out,
+                                                                            pl->leaf_small[wy].p, pl->n_leaf_small[wy]);
+        } else
         p2m_leaf<PP, RB><<<dim3(ly.nb, nsplit), 256, smem, s>>>(ty.pts.p, n_y, d, bs, R, r0, ly.off.p, ly.ctr.p, 2.f / ly.edge, nt, P,
                                                               nsplit > 1 ? nsplit : 1, (int)pl->mom_begin, (int)pl->mom_end,
                                                               pl->moments_out);
@@ -1007,10 +1118,15 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
             if (nsplit > 1) mom[L].zero();
             size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
             F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            if (RB == 1 && d == 3)
-                p2m_leaf3<PP><<<dim3(ly.nb, nsplit), 128, 0, s>>>(ty.pts.p, n_y, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt, nsplit, 0, n_y,
-                                                                mom[L].p);
-            else
+            if (RB == 1 && d == 3) {
+                const int wy = pl->same ? 0 : 1;
+                if (pl->n_leaf_big[wy])
+                    p2m_leaf3<PP><<<dim3(pl->n_leaf_big[wy], nsplit), 128, 0, s>>>(ty.pts.p, n_y, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt,
+                                                                                 nsplit, 0, n_y, mom[L].p, pl->leaf_big[wy].p);
+                if (pl->n_leaf_small[wy])
+                    p2m_small3<PP><<<(pl->n_leaf_small[wy] + 3) / 4, 128, 0, s>>>(ty.pts.p, n_y, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt, 0,
+                                                                                n_y, mom[L].p, pl->leaf_small[wy].p, pl->n_leaf_small[wy]);
+            } else
             p2m_leaf<PP, RB><<<dim3(ly.nb, nsplit), 256, smem, s>>>(ty.pts.p, n_y, d, bs, R, r0, ly.off.p, ly.ctr.p, factor, nt, P,
                                                                   nsplit, 0, n_y, mom[L].p);
             F3M_LAUNCH_CHECK();
@@ -1116,10 +1232,14 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
         int nsplit = std::max(1, std::min(64, (lx.max_count + 8191) / 8192));
         size_t smem = ((size_t)PR + (size_t)std::max(1, d - 1) * PP * 128) * sizeof(float);
         F3M_CUDA(cudaFuncSetAttribute(l2p_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        if (RB == 1 && d == 3)
-            l2p_leaf3<PP><<<dim3(lx.nb, nsplit), 128, 0, s>>>(tx.pts.p, n_x, lx.off.p, lx.ctr.p, factor, nt, nsplit, rb, re, loc[L].p, R,
-                                                            r0, out);
-        else
+        if (RB == 1 && d == 3) {
+            if (pl->n_leaf_big[0])
+                l2p_leaf3<PP><<<dim3(pl->n_leaf_big[0], nsplit), 128, 0, s>>>(tx.pts.p, n_x, lx.off.p, lx.ctr.p, factor, nt, nsplit, rb, re,
+                                                                            loc[L].p, R, r0, out, pl->leaf_big[0].p);
+            if (pl->n_leaf_small[0])
+                l2p_small3<PP><<<(pl->n_leaf_small[0] + 3) / 4, 128, 0, s>>>(tx.pts.p, n_x, lx.off.p, lx.ctr.p, factor, nt, rb, re, loc[L].p,
+                                                                           R, r0, out, pl->leaf_small[0].p, pl->n_leaf_small[0]);
+        } else
         l2p_leaf<PP, RB><<<dim3(lx.nb, nsplit), 128, smem, s>>>(tx.pts.p, n_x, d, lx.off.p, lx.ctr.p, factor, nt, P, nsplit, rb, re,
                                                                loc[L].p, R, r0, out);
         F3M_LAUNCH_CHECK();

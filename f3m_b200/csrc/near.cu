@@ -234,21 +234,17 @@ constexpr int SP2 = 192;   // source pairs per shared-memory tile
 
 // POLY = 0: every exponential on the MUFU pipe.  POLY = 2 or 3: PNUM of every PDEN source pairs use the
 // polynomial of that degree instead (the host enables it only when the exponent is provably small).
-template <int D, int RB, int POLY, int PNUM, int PDEN>
-__global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
-                                                     int nbx, const int *__restrict__ tile_off,
-                                                     const int *__restrict__ ptr, const int *__restrict__ idx,
-                                                     const int *__restrict__ off_y, const float *__restrict__ ctr_y,
-                                                     const float *__restrict__ packed, float scale, int R, int r0,
-                                                     float *out, float pc0, float pc1, float pc2, float pc3) {
+template <int D, int RB, int POLY, int PNUM, int PDEN, int TI>
+__device__ __forceinline__ void near_tile_x2(const float *__restrict__ xpts, int n_x, const int *__restrict__ ptr,
+                                             const int *__restrict__ idx, const int *__restrict__ off_y,
+                                             const float *__restrict__ ctr_y, const float *__restrict__ packed, float scale, int R,
+                                             int r0, float *out, float pc0, float pc1, float pc2, float pc3, float *smem, int box,
+                                             int t0, int t1) {
     constexpr int W = row_width(D, RB);
-    __shared__ __align__(16) float smem[SP2 * 2 * W];
-    int box, t0, t1;
-    item_to_tile(blockIdx.x, tile_off, nbx, off_x, box, t0, t1);
-    float x[TI2][D], tot[TI2][RB];
-    int ti[TI2];
+    float x[TI][D], tot[TI][RB];
+    int ti[TI];
 #pragma unroll
-    for (int u = 0; u < TI2; u++) {
+    for (int u = 0; u < TI; u++) {
         ti[u] = t0 + threadIdx.x + u * NT2;
         int ii = ti[u] < t1 ? ti[u] : t0;
 #pragma unroll
@@ -263,10 +259,10 @@ __global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ 
         const int s0 = off_y[by], cnt = off_y[by + 1] - s0;
         const int npairs = (cnt + 1) >> 1;
         const float *rows = packed + (size_t)pair_row_start(s0, by) * W;
-        f32x2 xr[TI2][D], acc[TI2][RB];
-        float fx[TI2];
+        f32x2 xr[TI][D], acc[TI][RB];
+        float fx[TI];
 #pragma unroll
-        for (int u = 0; u < TI2; u++) {
+        for (int u = 0; u < TI; u++) {
             float nx = 0.f;
 #pragma unroll
             for (int k = 0; k < D; k++) {
@@ -295,7 +291,7 @@ __global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ 
                     col[2 * q + 1] = v.y;
                 }
 #pragma unroll
-                for (int u = 0; u < TI2; u++) {
+                for (int u = 0; u < TI; u++) {
                     f32x2 t = mul2(xr[u][0], col[0]);
 #pragma unroll
                     for (int k = 1; k < D; k++) t = fma2(xr[u][k], col[k], t);
@@ -325,7 +321,7 @@ __global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ 
             for (; j < np; j++) body(j, false);
         }
 #pragma unroll
-        for (int u = 0; u < TI2; u++)
+        for (int u = 0; u < TI; u++)
 #pragma unroll
             for (int r = 0; r < RB; r++) {
                 float lo, hi;
@@ -334,7 +330,7 @@ __global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ 
             }
     }
 #pragma unroll
-    for (int u = 0; u < TI2; u++)
+    for (int u = 0; u < TI; u++)
         if (ti[u] < t1) {
 #pragma unroll
             for (int r = 0; r < RB; r++)
@@ -342,16 +338,42 @@ __global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ 
         }
 }
 
+// TI = targets per thread.  MIXED: a tile of at most 32 targets (small boxes) runs the one-target form, which does half
+// the work; the host picks this variant only when such tiles exist.
+template <int D, int RB, int POLY, int PNUM, int PDEN, bool MIXED>
+__global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
+                                                     int nbx, const int *__restrict__ tile_off,
+                                                     const int *__restrict__ ptr, const int *__restrict__ idx,
+                                                     const int *__restrict__ off_y, const float *__restrict__ ctr_y,
+                                                     const float *__restrict__ packed, float scale, int R, int r0,
+                                                     float *out, float pc0, float pc1, float pc2, float pc3) {
+    constexpr int W = row_width(D, RB);
+    __shared__ __align__(16) float smem[SP2 * 2 * W];
+    int box, t0, t1;
+    item_to_tile(blockIdx.x, tile_off, nbx, off_x, box, t0, t1);
+    if (MIXED && t1 - t0 <= NT2)
+        near_tile_x2<D, RB, POLY, PNUM, PDEN, 1>(xpts, n_x, ptr, idx, off_y, ctr_y, packed, scale, R, r0, out, pc0, pc1, pc2, pc3, smem,
+                                                 box, t0, t1);
+    else
+        near_tile_x2<D, RB, POLY, PNUM, PDEN, TI2>(xpts, n_x, ptr, idx, off_y, ctr_y, packed, scale, R, r0, out, pc0, pc1, pc2, pc3, smem,
+                                                   box, t0, t1);
+}
+
 #include "near_mma.cuh"
 
+// tiles[b] = tiles of target box b (0 when it has no pairs or lies outside the row range); *n_small counts the boxes
+// whose single tile holds at most 32 targets
 __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__restrict__ off_x, const int *__restrict__ ptr,
-                                                         int row_begin, int row_end, int tile_pts, int *tiles) {
+                                                         int row_begin, int row_end, int tile_pts, int *tiles, int *n_small) {
     int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b > nbx) return;
     int t = 0;
     if (b < nbx && ptr[b + 1] > ptr[b]) {
         int o = off_x[b];
-        if (o >= row_begin && o < row_end) t = (off_x[b + 1] - o + tile_pts - 1) / tile_pts;
+        if (o >= row_begin && o < row_end) {
+            t = (off_x[b + 1] - o + tile_pts - 1) / tile_pts;
+            if (n_small && off_x[b + 1] - o <= 32) atomicAdd(n_small, 1);
+        }
     }
     tiles[b] = t;
 }
@@ -540,13 +562,17 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     const int tile_pts = use_mma ? MM_M : (expanded ? NT2 * TI2 : NT);
     DevBuf<int> tiles;
     tiles.alloc((size_t)lx.nb + 1, s);
+    int *n_small = pl->d_flags + 42;
+    F3M_CUDA(cudaMemsetAsync(n_small, 0, sizeof(int), s));
     near_tiles_per_box<<<(unsigned)((lx.nb + 1 + 255) / 256), 256, 0, s>>>(lx.nb, lx.off.p, csr.ptr.p, row_begin, row_end,
-                                                                           tile_pts, tiles.p);
+                                                                           tile_pts, tiles.p, n_small);
     F3M_LAUNCH_CHECK();
     exclusive_scan_i32(tiles.p, tiles.p, (int64_t)lx.nb + 1, s);
     F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, tiles.p + lx.nb, sizeof(int), cudaMemcpyDeviceToHost, s));
+    F3M_CUDA(cudaMemcpyAsync(pl->h_pinned + 1, n_small, sizeof(int), cudaMemcpyDeviceToHost, s));
     F3M_CUDA(cudaStreamSynchronize(s));
     const int items = pl->h_pinned[0];
+    const bool small_tiles = pl->h_pinned[1] > 0;   // some tiles hold at most 32 targets: use the kernel that halves their work
     if (items <= 0) return;
     DevBuf<float> packed;
     // the pair layout of the expanded form starts every box on an even row
@@ -611,13 +637,19 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
         const int poly = exp2_poly_degree(tmax);
         double cf[4];
         exp2_poly_fit(-tmax, tmax, poly, cf);
-#define F3M_NEAR_EXP(POLY_, PNUM_, PDEN_)                                                                                     \
-    near_kernel_x2<D, RB, POLY_, PNUM_, PDEN_><<<items, NT2, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, \
-                                                                    csr.idx.p, ly.off.p, ly.ctr.p, packed.p, scale, R, r0, out, \
-                                                                    (float)cf[0], (float)cf[1], (float)cf[2], (float)cf[3])
-        if (poly == 2) F3M_NEAR_EXP(2, 2, 5);
-        else if (poly == 3) F3M_NEAR_EXP(3, 1, 3);
-        else F3M_NEAR_EXP(0, 0, 1);
+#define F3M_NEAR_EXP2(POLY_, PNUM_, PDEN_, MIXED_)                                                                                       \
+    near_kernel_x2<D, RB, POLY_, PNUM_, PDEN_, MIXED_><<<items, NT2, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, \
+                                                                            csr.idx.p, ly.off.p, ly.ctr.p, packed.p, scale, R, r0, out, \
+                                                                            (float)cf[0], (float)cf[1], (float)cf[2], (float)cf[3])
+#define F3M_NEAR_EXP(POLY_, PNUM_, PDEN_)                         \
+    {                                                             \
+        if (small_tiles) F3M_NEAR_EXP2(POLY_, PNUM_, PDEN_, true); \
+        else F3M_NEAR_EXP2(POLY_, PNUM_, PDEN_, false);            \
+    }
+        if (poly == 2) F3M_NEAR_EXP(2, 2, 5)
+        else if (poly == 3) F3M_NEAR_EXP(3, 1, 3)
+        else F3M_NEAR_EXP(0, 0, 1)
+#undef F3M_NEAR_EXP2
 #undef F3M_NEAR_EXP
     }
     else
@@ -638,7 +670,7 @@ static void taylor_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     DevBuf<int> tiles;
     tiles.alloc((size_t)lx.nb + 1, s);
     near_tiles_per_box<<<(unsigned)((lx.nb + 1 + 255) / 256), 256, 0, s>>>(lx.nb, lx.off.p, csr.ptr.p, row_begin, row_end, 128,
-                                                                           tiles.p);
+                                                                           tiles.p, nullptr);
     F3M_LAUNCH_CHECK();
     exclusive_scan_i32(tiles.p, tiles.p, (int64_t)lx.nb + 1, s);
     F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, tiles.p + lx.nb, sizeof(int), cudaMemcpyDeviceToHost, s));

@@ -341,7 +341,7 @@ __device__ __forceinline__ void near_tile_x2(const float *__restrict__ xpts, int
 // TI = targets per thread.  MIXED: a tile of at most 32 targets (small boxes) runs the one-target form, which does half
 // the work; the host picks this variant only when such tiles exist.
 template <int D, int RB, int POLY, int PNUM, int PDEN, bool MIXED>
-__global__ void __launch_bounds__(NT2) near_kernel_x2(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
+__global__ void __launch_bounds__(NT2, 32) near_kernel_x2(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
                                                      int nbx, const int *__restrict__ tile_off,
                                                      const int *__restrict__ ptr, const int *__restrict__ idx,
                                                      const int *__restrict__ off_y, const float *__restrict__ ctr_y,

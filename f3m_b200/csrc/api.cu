@@ -286,6 +286,7 @@ static void plan_apply(f3m_plan *pl, const float *b, int R, float *out, int64_t 
     else scatter_rows_nonzero(outs.p, tx.perm.p, out, N, R, s);   // a slice: most rows are zero
     pl->last.end(s);
     F3M_CUDA(cudaEventRecord(pl->last.spans[0].b, s));   // closes the ST_TOTAL span opened first
+    pl->last.spans[0].closed = true;
     F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, pl->d_flags, sizeof(int), cudaMemcpyDeviceToHost, s));
     F3M_CUDA(cudaStreamSynchronize(s));
     pl->last.resolve();

@@ -132,20 +132,29 @@ enum Stage { ST_PERMUTE = 0, ST_DIRECT = 1, ST_P2M = 2, ST_M2L = 3, ST_L2P = 4, 
 struct Timings {
     float ms[8] = {0};
     int direct_launches = 0;
-    struct Span { int stage; cudaEvent_t a, b; };
+    struct Span { int stage; cudaEvent_t a, b; bool closed; };
     std::vector<Span> spans;
     void begin(int stage, cudaStream_t s) {
-        Span sp{stage, nullptr, nullptr};
+        Span sp{stage, nullptr, nullptr, false};
         F3M_CUDA(cudaEventCreate(&sp.a));
         F3M_CUDA(cudaEventCreate(&sp.b));
         F3M_CUDA(cudaEventRecord(sp.a, s));
         spans.push_back(sp);
     }
-    void end(cudaStream_t s) { F3M_CUDA(cudaEventRecord(spans.back().b, s)); }
-    void resolve() {   // call after the stream has been synchronised
+    void end(cudaStream_t s) {
+        F3M_CUDA(cudaEventRecord(spans.back().b, s));
+        spans.back().closed = true;
+    }
+    // Call after the stream has been synchronised.  A span that was never closed (the product failed in between)
+    // is dropped; a failed query must not stay behind as the runtime's last error, or the next launch check of an
+    // unrelated call would report it.
+    void resolve() {
         for (auto &sp : spans) {
             float t = 0.f;
-            if (cudaEventElapsedTime(&t, sp.a, sp.b) == cudaSuccess) ms[sp.stage] += t;
+            if (sp.closed) {
+                if (cudaEventElapsedTime(&t, sp.a, sp.b) == cudaSuccess) ms[sp.stage] += t;
+                else (void)cudaGetLastError();
+            }
             cudaEventDestroy(sp.a);
             cudaEventDestroy(sp.b);
         }

@@ -259,6 +259,39 @@ def test_far_field_node_counts_d3(p, cuda):
     assert e_out <= {2: 0.5, 3: 0.2, 4: 5e-2, 5: 1e-2, 6: 3e-3, 7: 6e-4, 8: 2e-4}[p]
 
 
+def test_failed_call_leaves_library_usable(cuda):
+    """A call that fails (one point: no bounding cube) must not poison the next one: status and message for the
+    failure, then a correct product from the same process.  Degenerate but valid inputs work: two points, points on a
+    line, far-apart clusters, large offsets, extreme lengthscales, leaf size 1."""
+    from f3m_b200 import engine
+    g = torch.Generator().manual_seed(77)
+
+    def product(X, b, ls=1.0, mp=100., P=27):
+        prm = engine.make_params(ls, mp, P, False, 0.15, P)
+        out = engine.kmvm(X.to(cuda), None, b.to(cuda), prm).cpu()
+        exact = engine.rbf_dense(X.double().to(cuda), X.double().to(cuda), b.double().to(cuda), ls).cpu()
+        return rel_l2(out, exact)
+
+    with pytest.raises(RuntimeError, match="bounding cube"):
+        product(torch.rand(1, 3, generator=g), torch.randn(1, 1, generator=g))
+    with pytest.raises(RuntimeError, match="bounding cube"):
+        product(torch.ones(500, 3) * 0.3, torch.randn(500, 1, generator=g))
+    assert product(torch.rand(2, 3, generator=g), torch.randn(2, 1, generator=g)) <= 1e-5
+    assert product(torch.rand(4000, 3, generator=g), torch.randn(4000, 1, generator=g)) <= 5e-3
+    line = torch.cat([torch.rand(5000, 1, generator=g), torch.zeros(5000, 2)], 1)
+    assert product(line, torch.randn(5000, 1, generator=g)) <= 5e-3
+    far = torch.cat([torch.rand(3000, 3, generator=g) * 0.05, torch.rand(3000, 3, generator=g) * 0.05 + 10.0])
+    assert product(far, torch.randn(6000, 1, generator=g)) <= 5e-3
+    # clusters 1e5 times smaller than their distance need more levels than a 30-bit cell index holds: a clean error
+    too_deep = torch.cat([torch.rand(3000, 3, generator=g) * 1e-3, torch.rand(3000, 3, generator=g) * 1e-3 + 100.0])
+    with pytest.raises(RuntimeError, match="level"):
+        product(too_deep, torch.randn(6000, 1, generator=g))
+    assert product(torch.rand(5000, 3, generator=g) + 1e3, torch.randn(5000, 1, generator=g)) <= 5e-3
+    assert product(torch.rand(5000, 3, generator=g), torch.randn(5000, 1, generator=g), ls=1e-3) <= 1e-4
+    assert product(torch.rand(5000, 3, generator=g), torch.randn(5000, 1, generator=g), ls=1e3) <= 1e-4
+    assert product(torch.rand(3000, 3, generator=g), torch.randn(3000, 1, generator=g), mp=1.) <= 5e-3
+
+
 def test_dense_ops(cuda):
     from f3m_b200 import engine
     from oracle.f3m_oracle import dense_kmvm_f64

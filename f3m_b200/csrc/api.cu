@@ -164,13 +164,21 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
     float xmin[MAXD], xmax[MAXD], ymin[MAXD], ymax[MAXD];
     bounding_box(X, N, d, xmin, xmax, pl, s);
     float range = 0.f;
-    for (int k = 0; k < d; k++) range = std::max(range, xmax[k] - xmin[k]);
+    bool finite = true;   // std::max drops a NaN operand, so non-finite extents are checked one by one
+    for (int k = 0; k < d; k++) {
+        finite = finite && std::isfinite(xmin[k]) && std::isfinite(xmax[k]);
+        range = std::max(range, xmax[k] - xmin[k]);
+    }
     if (!pl->same) {
         bounding_box(Y, M, d, ymin, ymax, pl, s);
         float ry = 0.f;
-        for (int k = 0; k < d; k++) ry = std::max(ry, ymax[k] - ymin[k]);
+        for (int k = 0; k < d; k++) {
+            finite = finite && std::isfinite(ymin[k]) && std::isfinite(ymax[k]);
+            ry = std::max(ry, ymax[k] - ymin[k]);
+        }
         range = std::max(range, ry);
     }
+    F3M_REQUIRE(finite, F3M_ERR_ARG, "degenerate or non-finite bounding cube (a coordinate is NaN or infinite)");
     float edge0 = range * 1.01f;
     F3M_REQUIRE(edge0 > 0.f && std::isfinite(edge0), F3M_ERR_ARG, "degenerate or non-finite bounding cube (edge %g)", edge0);
 

@@ -120,16 +120,19 @@ static inline float dec_f32(unsigned u) {
 template <int D>
 __global__ void __launch_bounds__(256) bbox_kernel(const float *__restrict__ X, int64_t n, unsigned *mm) {
     float lo[D], hi[D];
+    bool nan_seen = false;   // fminf / fmaxf skip NaN: a NaN coordinate is reported through the maximum instead
 #pragma unroll
     for (int k = 0; k < D; k++) { lo[k] = INFINITY; hi[k] = -INFINITY; }
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
 #pragma unroll
         for (int k = 0; k < D; k++) {
             float v = X[i * D + k];
+            nan_seen |= (v != v);
             lo[k] = fminf(lo[k], v);
             hi[k] = fmaxf(hi[k], v);
         }
     }
+    if (__any_sync(0xffffffffu, nan_seen) && (threadIdx.x & 31) == 0) atomicMax(&mm[MAXD], 0xffffffffu);   // decodes to NaN
 #pragma unroll
     for (int k = 0; k < D; k++) {
 #pragma unroll

@@ -276,6 +276,13 @@ def test_failed_call_leaves_library_usable(cuda):
         product(torch.rand(1, 3, generator=g), torch.randn(1, 1, generator=g))
     with pytest.raises(RuntimeError, match="bounding cube"):
         product(torch.ones(500, 3) * 0.3, torch.randn(500, 1, generator=g))
+    bad = torch.rand(3000, 3, generator=g)
+    bad[17, 1] = float("nan")
+    with pytest.raises(RuntimeError, match="bounding cube"):
+        product(bad, torch.randn(3000, 1, generator=g))
+    bad[17, 1] = float("inf")
+    with pytest.raises(RuntimeError, match="bounding cube"):
+        product(bad, torch.randn(3000, 1, generator=g))
     assert product(torch.rand(2, 3, generator=g), torch.randn(2, 1, generator=g)) <= 1e-5
     assert product(torch.rand(4000, 3, generator=g), torch.randn(4000, 1, generator=g)) <= 5e-3
     line = torch.cat([torch.rand(5000, 1, generator=g), torch.zeros(5000, 2)], 1)

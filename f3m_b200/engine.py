@@ -60,6 +60,8 @@ class Plan:
         b = _as_f32(b.to(self.device))
         if b.dim() == 1:
             b = b[:, None]
+        if b.shape[0] != self.M:
+            raise AssertionError(f"b has {b.shape[0]} rows, Y has {self.M}")
         mom = torch.empty(self.moments_size(b.shape[1]), device=self.device, dtype=torch.float32)
         with torch.cuda.device(self.device):
             st = _lib.lib().f3m_plan_moments_range(self._h, b.data_ptr(), b.shape[1], int(src_range[0]), int(src_range[1]),
@@ -76,6 +78,9 @@ class Plan:
         out = torch.empty(self.N, b.shape[1], device=self.device, dtype=torch.float32)
         with torch.cuda.device(self.device):
             if moments is not None:
+                if (not moments.is_cuda or moments.dtype != torch.float32 or not moments.is_contiguous()
+                        or moments.numel() != self.moments_size(b.shape[1])):
+                    raise ValueError("moments must be the contiguous float32 CUDA array of moments_size(R) floats that moments() returns")
                 rr = (0, self.N) if row_range is None else row_range
                 st = _lib.lib().f3m_plan_apply_range_moments(self._h, b.data_ptr(), b.shape[1], out.data_ptr(), int(rr[0]),
                                                              int(rr[1]), moments.data_ptr(), _stream_ptr(self.device))

@@ -86,16 +86,16 @@ class FFM:
         if self._plan is None or self._plan_key != key:
             if self._plan is not None:
                 self._plan.close()
-            self._plan = engine.Plan(X, None if Y.data_ptr() == X.data_ptr() else Y, self._params())
+            self._plan = engine.Plan(X, None if engine.is_shared(X, Y) else Y, self._params())
             self._plan_key = key
         return self._plan
 
     def forward(self, X, Y, b):
         self._check(X, Y, b)
-        own = X.data_ptr() == self.X.data_ptr() and Y.data_ptr() == self.Y.data_ptr()
+        own = engine.is_shared(self.X, X) and engine.is_shared(self.Y, Y)   # the tensors given at construction
         if own:
             return self.plan(X, Y).apply(b)
-        return engine.kmvm(X, None if Y.data_ptr() == X.data_ptr() else Y, b, self._params())
+        return engine.kmvm(X, None if engine.is_shared(X, Y) else Y, b, self._params())
 
     def forward_grad(self, X, Y, b):
         if not (Y.shape[1] == X.shape[1] and Y.shape[0] == b.shape[0]):

@@ -74,6 +74,7 @@ SIGNATURES = {
     "f3m_measure_peaks": (C.c_int, [C.POINTER(_F64), C.POINTER(_F64), _P]),
     "f3m_plan_last_timings": (C.c_int, [_P, C.POINTER(_F32)]),
     "f3m_plan_last_direct_launches": (C.c_int, [_P]),
+    "f3m_plan_last_direct_variants": (C.c_int, [_P, C.POINTER(_I32)]),
     "f3m_launch_count": (C.c_longlong, []),
 }
 

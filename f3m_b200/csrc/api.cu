@@ -142,7 +142,6 @@ static void check_common(const void *X, int64_t N, const void *Y, int64_t M, int
     F3M_REQUIRE(d >= 1 && d <= F3M_MAX_DIM, F3M_ERR_ARG, "dimension %d outside 1..%d", d, F3M_MAX_DIM);
     F3M_REQUIRE(prm->ls > 0.f, F3M_ERR_ARG, "lengthscale must be positive");
     F3M_REQUIRE(prm->nr_interpolation >= 1, F3M_ERR_ARG, "nr_interpolation must be >= 1");
-    F3M_REQUIRE(X != Y || N == M, F3M_ERR_ARG, "X and Y share a pointer but N != M");
 }
 
 static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, int64_t M, int d, const f3m_params *prm,
@@ -150,7 +149,9 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
     F3M_CUDA(cudaGetDevice(&pl->device));
     pl->d = d;
     pl->prm = *prm;
-    pl->same = (X == Y);                                  // n_tree.cu:1072
+    // n_tree.cu:1072 tests the address only; a leading slice of X starts at the same address but is another
+    // (smaller) point set, so the sizes must agree too
+    pl->same = (X == Y && N == M);
     pl->lcs = 1 / (2 * prm->ls * prm->ls);                // n_tree.cu:1060
     {
         ScratchSlot sl = take_slot(pl->device);
@@ -267,6 +268,7 @@ static void plan_apply(f3m_plan *pl, const float *b, int R, float *out, int64_t 
     for (float &m : pl->last.ms) m = 0.f;
     pl->last.ms[ST_BUILD] = pl->stats.build_ms;
     pl->last.direct_launches = 0;
+    for (int &v : pl->last.direct_variants) v = 0;
     pl->last.begin(ST_TOTAL, s);
 
     pl->last.begin(ST_PERMUTE, s);
@@ -414,7 +416,7 @@ int f3m_kmvm_host_f32(const float *X, int64_t N, const float *Y, int64_t M, cons
     int st = guarded([&] {
         check_common(X, N, Y, M, d, prm);
         F3M_REQUIRE(b && out && R >= 1, F3M_ERR_ARG, "bad right-hand side");
-            const bool same = (X == Y);
+        const bool same = (X == Y && N == M);
         // two streams: the coordinates go first and the tree is built from them while b is still on the link
         cudaStream_t s = nullptr, sb = nullptr;
         cudaEvent_t ev_x = nullptr, ev_b = nullptr;
@@ -572,5 +574,11 @@ int f3m_plan_last_timings(const f3m_plan *plan, float ms[8]) {
 }
 
 int f3m_plan_last_direct_launches(const f3m_plan *plan) { return plan ? plan->last.direct_launches : 0; }
+
+int f3m_plan_last_direct_variants(const f3m_plan *plan, int32_t counts[6]) {
+    if (!plan || !counts) return F3M_ERR_ARG;
+    for (int i = 0; i < 6; i++) counts[i] = plan->last.direct_variants[i];
+    return F3M_OK;
+}
 
 }  // extern "C"

@@ -129,9 +129,12 @@ struct LevelLists {
 // Device time per stage, from CUDA events recorded on the product's stream and read after its
 // final synchronisation (no extra synchronisation inside the product).
 enum Stage { ST_PERMUTE = 0, ST_DIRECT = 1, ST_P2M = 2, ST_M2L = 3, ST_L2P = 4, ST_UNPERMUTE = 5, ST_TOTAL = 6, ST_BUILD = 7 };
+// forms of the direct-sum kernels (counted per launch, see f3m_plan_last_direct_variants)
+enum DirectVariant { DV_MUFU = 0, DV_POLY2 = 1, DV_POLY3 = 2, DV_DIRECT = 3, DV_MOMENTS = 4, DV_TENSOR = 5, DV_COUNT = 6 };
 struct Timings {
     float ms[8] = {0};
     int direct_launches = 0;
+    int direct_variants[DV_COUNT] = {0};
     struct Span { int stage; cudaEvent_t a, b; bool closed; };
     std::vector<Span> spans;
     void begin(int stage, cudaStream_t s) {

@@ -12,6 +12,7 @@
 // the warp and a pair costs d subtractions, d multiply-adds, one ex2 and RB multiply-adds.  This kernel
 // is bound by the SM's FP32 issue rate and its exponential (MUFU) rate, not by HBM: a source row is
 // reused by every target of the tile.
+#include <math.h>
 #include <algorithm>
 #include "common.cuh"
 
@@ -548,6 +549,26 @@ static int exp2_poly_degree(double hw) {
 
 static inline float near_scale(float lcs) { return sqrtf(lcs * 1.4426950408889634f); }
 
+// Largest |x_k - c_k| / edge over the pairs a list can hold, x a target and c the centre of the source box:
+// 2.5 for pairs kept for refinement (centres closer than two edges), 5.5 for "small" pairs, which are children of
+// kept parents.  Level-1 pairs of two different point sets are children of the root pair, which is kept without
+// any distance test, and the two cubes have separate origins (n_tree.cu:1096-1098): "small" pairs there are
+// classified by size before distance (1_d_conv.cu:916-920), so their distance is bounded only by the offset
+// between the two cubes.
+static double list_reach(const f3m_plan *pl, int level, const PairCSR &csr) {
+    const bool final_near = (&csr == &pl->lists[level].keep);
+    if (final_near) return 2.5;
+    if (level == 1 && !pl->same) {
+        double off = 0.0;
+        for (int k = 0; k < pl->d; k++) off = std::max(off, fabs((double)pl->tx.origin[k] - (double)pl->ty->origin[k]));
+        return off / (double)pl->ty->levels[1].edge + 1.5;
+    }
+    return 5.5;
+}
+// the expanded form multiplies 2^(-|xr|^2) by 2^(2 xr.yr): beyond this bound on the cross term the second factor
+// could overflow while the first underflows, so such lists use the direct form
+constexpr double TMAX_EXPANDED = 64.0;
+
 // one list, one block of RB columns starting at r0
 template <int D, int RB>
 static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float *bs, int R, int r0, float *out,
@@ -555,10 +576,13 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     Tree &tx = pl->tx, &ty = *pl->ty;
     Level &lx = tx.levels[level], &ly = ty.levels[level];
     const float scale = near_scale(pl->lcs);
-    const bool expanded = scale * ly.edge <= 1.0f && level > 0;
+    // bound of the cross term |2 xr.yr| over the pairs of the list: |xr_k| <= reach * se, |yr_k| <= se / 2
+    const double reach = level > 0 ? list_reach(pl, level, csr) : 0.0;
+    const double tmax = D * reach * ((double)scale * ly.edge) * ((double)scale * ly.edge);
+    const bool expanded = scale * ly.edge <= 1.0f && level > 0 && tmax <= TMAX_EXPANDED;
     // tensor-core form (on request): one column, boxes at most half a scaled unit wide, so that the split
     // operands keep the exponent at FP32 accuracy
-    const bool use_mma = RB == 1 && level > 0 && scale * ly.edge <= 0.5f && (pl->prm.flags & F3M_FLAG_NEAR_TENSOR_CORES);
+    const bool use_mma = RB == 1 && expanded && scale * ly.edge <= 0.5f && (pl->prm.flags & F3M_FLAG_NEAR_TENSOR_CORES);
     const int tile_pts = use_mma ? MM_M : (expanded ? NT2 * TI2 : NT);
     DevBuf<int> tiles;
     tiles.alloc((size_t)lx.nb + 1, s);
@@ -592,8 +616,7 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
         int *counter = pl->d_flags + 32;
         F3M_CUDA(cudaMemsetAsync(counter, 0, sizeof(int), s));
         // range of t = 2 u.v - |v|^2 over the pairs of the list: |u| <= reach * se, |v| <= se / 2 per dimension
-        const bool final_near = (&csr == &pl->lists[level].keep);
-        const double se = (double)scale * ly.edge, reach = final_near ? 2.5 : 5.5;
+        const double se = (double)scale * ly.edge;
         const double thi = D * se * se * reach, tlo = -D * se * se * (reach + 0.25);
         const int deg = exp2_poly_degree(0.5 * (thi - tlo));
         double cf[4];
@@ -617,6 +640,7 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
 #undef F3M_NEAR_MMA
         pl->last.end(s);
         pl->last.direct_launches++;
+        pl->last.direct_variants[DV_TENSOR]++;
         F3M_LAUNCH_CHECK();
         return;
     }
@@ -629,12 +653,8 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     F3M_LAUNCH_CHECK();
     pl->last.begin(ST_DIRECT, s);
     if (expanded) {
-        // bound of |2 xr.yr| over the pairs a list can hold: per dimension |x - c_source| <= 2.5 edge for pairs kept
-        // for refinement (centres closer than 2 edges), 5.5 edge for "small" pairs (children of kept parents)
-        const bool final_near = (&csr == &pl->lists[level].keep);
-        const float se = scale * ly.edge;
-        const double tmax = D * (final_near ? 2.5 : 5.5) * (double)se * se;
         const int poly = exp2_poly_degree(tmax);
+        pl->last.direct_variants[poly == 2 ? DV_POLY2 : (poly == 3 ? DV_POLY3 : DV_MUFU)]++;
         double cf[4];
         exp2_poly_fit(-tmax, tmax, poly, cf);
 #define F3M_NEAR_EXP2(POLY_, PNUM_, PDEN_, MIXED_)                                                                                       \
@@ -652,9 +672,11 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
 #undef F3M_NEAR_EXP2
 #undef F3M_NEAR_EXP
     }
-    else
+    else {
+        pl->last.direct_variants[DV_DIRECT]++;
         near_kernel<D, RB, 1><<<items, NT, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, csr.idx.p, ly.off.p,
                                                    packed.p, scale, R, r0, out);
+    }
     pl->last.end(s);
     pl->last.direct_launches++;
     F3M_LAUNCH_CHECK();
@@ -687,6 +709,7 @@ static void taylor_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
                                                     mom.p, scale, R, out);
     pl->last.end(s);
     pl->last.direct_launches++;
+    pl->last.direct_variants[DV_MOMENTS]++;
     F3M_LAUNCH_CHECK();
 }
 
@@ -696,8 +719,7 @@ static void direct_d(f3m_plan *pl, int level, const PairCSR &csr, const float *b
     if ((pl->prm.flags & F3M_FLAG_NEAR_MOMENTS) && level > 0) {
         // exponent bound of the cross term over the pairs of the list (see direct_impl)
         const float se = near_scale(pl->lcs) * pl->ty->levels[level].edge;
-        const bool final_near = (&csr == &pl->lists[level].keep);
-        const float tmax = D * (final_near ? 2.5f : 5.5f) * se * se;
+        const float tmax = (float)(D * list_reach(pl, level, csr)) * se * se;
         if (se <= 1.0f && tmax <= 0.02f) { taylor_impl<D, 2>(pl, level, csr, bs, R, out, rb, re, s); return; }
         if (se <= 1.0f && tmax <= 0.1f) { taylor_impl<D, 3>(pl, level, csr, bs, R, out, rb, re, s); return; }
     }

@@ -22,6 +22,19 @@ def _as_f32(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+def is_shared(X: torch.Tensor, Y: Optional[torch.Tensor]) -> bool:
+    """True when Y is the same point set as X: no Y, or the same storage address AND the same shape.  The address
+    alone is not enough: a leading slice X[:k] starts at X's address but is a different (smaller) point set."""
+    return Y is None or (Y.data_ptr() == X.data_ptr() and tuple(Y.shape) == tuple(X.shape))
+
+
+def _check_product_shapes(X, Y, b):
+    if X.dim() != 2 or Y.dim() != 2 or Y.shape[1] != X.shape[1]:
+        raise AssertionError(f"X {tuple(X.shape)} and Y {tuple(Y.shape)} must be (n, d) arrays of one dimension d")
+    if b.shape[0] != Y.shape[0]:
+        raise AssertionError(f"b has {b.shape[0]} rows, Y has {Y.shape[0]}")
+
+
 def make_params(ls, min_points, nr_of_interpolation, var_compression, eff_var_limit, small_field_points,
                 math_mode=_lib.MATH_FASTMATH, flags=0) -> Params:
     return Params(float(ls), float(min_points), int(nr_of_interpolation), int(bool(var_compression)),
@@ -35,8 +48,10 @@ class Plan:
         if not X.is_cuda:
             raise ValueError("Plan needs CUDA tensors: the engine has no CPU path")
         self.X = _as_f32(X)
-        self.same = Y is None or (Y.data_ptr() == X.data_ptr() and Y.shape == X.shape)
+        self.same = is_shared(X, Y)
         self.Y = self.X if self.same else _as_f32(Y)
+        if self.Y.dim() != 2 or self.X.dim() != 2 or self.Y.shape[1] != self.X.shape[1]:
+            raise AssertionError(f"X {tuple(X.shape)} and Y {tuple(self.Y.shape)} must be (n, d) arrays of one dimension d")
         if self.Y.device != self.X.device:
             raise ValueError("X and Y must be on the same device")
         self.params = params
@@ -111,6 +126,12 @@ class Plan:
         d["direct_launches"] = int(_lib.lib().f3m_plan_last_direct_launches(self._h))
         return d
 
+    def direct_variants(self) -> Dict:
+        """Direct-sum launches of the last apply() by kernel form (f3m_plan_last_direct_variants)."""
+        c = (C.c_int32 * 6)()
+        check(_lib.lib().f3m_plan_last_direct_variants(self._h, c), "f3m_plan_last_direct_variants")
+        return dict(zip(("mufu", "poly2", "poly3", "direct", "moments", "tensor"), (int(v) for v in c)))
+
     def array(self, level: int, tree: int, what: int) -> np.ndarray:
         info = self.level(level) if level >= 1 else None
         nb = (info["boxes_x"] if tree == 0 else info["boxes_y"]) if info else 1
@@ -155,12 +176,13 @@ class Plan:
 
 def kmvm(X, Y, b, params: Params) -> torch.Tensor:
     """One-shot product through f3m_kmvm_f32 (tree built and dropped inside the call)."""
+    same = is_shared(X, Y)
     X = _as_f32(X)
-    same = Y is None or Y.data_ptr() == X.data_ptr()
     Y = X if same else _as_f32(Y)
     b = _as_f32(b)
     if b.dim() == 1:
         b = b[:, None]
+    _check_product_shapes(X, Y, b)
     if not (X.is_cuda and Y.is_cuda and b.is_cuda):
         raise ValueError("kmvm needs CUDA tensors: the engine has no CPU path (use kmvm_host for host buffers)")
     out = torch.empty(X.shape[0], b.shape[1], device=X.device, dtype=torch.float32)
@@ -173,12 +195,13 @@ def kmvm(X, Y, b, params: Params) -> torch.Tensor:
 
 def kmvm_host(X, Y, b, params: Params, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Product with HOST tensors through f3m_kmvm_host_f32: H2D copies, product, D2H copy in one call."""
+    same = is_shared(X, Y)
     X = _as_f32(X)
-    same = Y is None or Y.data_ptr() == X.data_ptr()
     Y = X if same else _as_f32(Y)
     b = _as_f32(b)
     if b.dim() == 1:
         b = b[:, None]
+    _check_product_shapes(X, Y, b)
     if X.is_cuda or Y.is_cuda or b.is_cuda:
         raise ValueError("kmvm_host takes CPU tensors")
     if out is None:

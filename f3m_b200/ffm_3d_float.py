@@ -9,7 +9,7 @@ from . import engine
 
 def _ffm_xy(X, Y, b, device, ls, min_points, nr_of_interpolation, var_compression, eff_var_limit, small_field_limit):
     prm = engine.make_params(ls, min_points, nr_of_interpolation, var_compression, eff_var_limit, small_field_limit)
-    return engine.kmvm(X, None if Y.data_ptr() == X.data_ptr() else Y, b, prm)
+    return engine.kmvm(X, None if engine.is_shared(X, Y) else Y, b, prm)
 
 
 def _rbf(X, Y, b, ls, shared=True):

@@ -85,8 +85,9 @@ const char *f3m_last_error(void);
 
 /* One complete product: replaces FFM_XY<float,d> (F3M_src/n_tree.cu:1056-1125), which
  * ffm_3d_float.FFM_XY_FLOAT_d binds (F3M_src/pybinder_setup.cu:17-36).
- * X (N,d), Y (M,d), b (M,R), out (N,R).  Pass Y == X (same pointer) for the shared-tree case,
- * exactly as the reference detects it (n_tree.cu:1072).  out is overwritten. */
+ * X (N,d), Y (M,d), b (M,R), out (N,R).  Pass Y == X (same pointer, and M == N) for the shared-tree
+ * case; the reference detects it by the pointer alone (n_tree.cu:1072), here a Y that starts at X's address
+ * with another row count (a leading slice of X) is an ordinary second point set.  out is overwritten. */
 int f3m_kmvm_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R,
                  int32_t d, const f3m_params *prm, float *out, void *stream);
 
@@ -201,6 +202,12 @@ int f3m_plan_last_timings(const f3m_plan *plan, float ms[8]);
 /* Number of direct-sum kernel launches inside the last f3m_plan_apply, and kernels launched by the
  * library since it was loaded (all entry points). */
 int f3m_plan_last_direct_launches(const f3m_plan *plan);
+/* Which form of the direct-sum kernel those launches took (the host picks it per list from a bound on the
+ * exponent, see near_field_run n_tree.cu:831-902 for the sums themselves): counts[0] expanded form with every
+ * exponential on the special-function unit, [1] expanded form with 2/5 of the pairs on a degree-2 polynomial,
+ * [2] with 1/3 on a degree-3 polynomial, [3] direct form (differences, wide boxes), [4] moment form
+ * (F3M_FLAG_NEAR_MOMENTS), [5] tensor-core form (F3M_FLAG_NEAR_TENSOR_CORES). */
+int f3m_plan_last_direct_variants(const f3m_plan *plan, int32_t counts[6]);
 long long f3m_launch_count(void);
 
 #ifdef __cplusplus

@@ -71,8 +71,13 @@ def node_list(nd: int, max_nodes: int) -> List[int]:
     return out
 
 
-def cheb_nodes_weights(p: int):
-    """First-kind Chebyshev nodes and barycentric weights (n_tree.cu:265-285), float32."""
+def cheb_nodes_weights(p: int, dtype=F32):
+    """First-kind Chebyshev nodes and barycentric weights (n_tree.cu:265-285), float32 as in the reference
+    (float64 when the algorithm is evaluated in float64: see the `dtype` argument of f3m_kmvm)."""
+    if dtype == torch.float64:
+        k = torch.arange(0, p, dtype=torch.float64)
+        ang = (2. * k + 1.) * math.pi / (2. * p)
+        return torch.cos(ang), torch.where(k.long() % 2 == 0, 1.0, -1.0) * torch.sin(ang)
     pi32 = float(np.float32(math.atan(1.0) * 4.0))
     k = torch.arange(0, p).to(F32)
     nodes = torch.cos((k * 2. + 1.) * pi32 / (2 * (p - 1) + 2))
@@ -111,7 +116,7 @@ def lagrange_basis_1d(t: torch.Tensor, nodes: torch.Tensor, w: torch.Tensor) -> 
     L = (lx * w[None, :]) / safe
     anyhit = hit.any(1)
     if bool(anyhit.any()):
-        L[anyhit] = hit[anyhit].to(F32)
+        L[anyhit] = hit[anyhit].to(L.dtype)
     return L
 
 
@@ -230,8 +235,14 @@ def candidate_pairs(near: torch.Tensor, tx: Tree, ty: Tree) -> torch.Tensor:
 
 
 def classify_pairs(pairs, tx: Tree, ty: Tree, lcs: float, P: int, small_field: int,
-                   var_comp: bool, eff_var_limit: float):
-    """far / small / keep masks (separate_interactions n_tree.cu:701-787; kernels 1_d_conv.cu:903-1029)."""
+                   var_comp: bool, eff_var_limit: float, near_tie_far=None):
+    """far / small / keep masks (separate_interactions n_tree.cu:701-787; kernels 1_d_conv.cu:903-1029).
+
+    near_tie_far: optional callable(level, tie_pairs) -> bool tensor.  Pairs whose centre distance is within a few
+    float32 ulp of the far threshold 2*edge (in 4 and more dimensions whole families of box offsets sit exactly on it)
+    are classified by the reference with sqrt.approx and a fused sum, whose last-bit behaviour no CPU arithmetic
+    reproduces; a test that knows the reference's decision for those pairs passes it in here, and every other
+    decision stays the restatement's own."""
     d = tx.d
     bx, by = pairs[:, 0], pairs[:, 1]
     size = tx.counts[bx] + ty.counts[by]
@@ -251,7 +262,14 @@ def classify_pairs(pairs, tx: Tree, ty: Tree, lcs: float, P: int, small_field: i
         m = size < 2 * P
         small |= m
         undecided &= ~m
-    m = undecided & (norm >= edge * 2)
+    is_far = norm >= edge * 2
+    if near_tie_far is not None:
+        thr = float(edge * 2)
+        tie = undecided & ((norm - thr).abs() <= 8 * float(np.spacing(np.float32(thr))))
+        if bool(tie.any()):
+            is_far = is_far.clone()
+            is_far[tie] = near_tie_far(tx.depth, pairs[tie])
+    m = undecided & is_far
     if do_init:
         far |= m
     undecided &= ~m                                   # var_comp with q>5: pair is dropped
@@ -278,10 +296,11 @@ def classify_pairs(pairs, tx: Tree, ty: Tree, lcs: float, P: int, small_field: i
 # numerical stages
 # --------------------------------------------------------------------------------------
 def direct_sums(pairs, tx: Tree, ty: Tree, b, lcs: float, out):
-    """near_field_run (n_tree.cu:831-902) + skip_conv_1d_shared (1_d_conv.cu:255-335)."""
+    """near_field_run (n_tree.cu:831-902) + skip_conv_1d_shared (1_d_conv.cu:255-335).  Arithmetic in out.dtype."""
     if pairs.shape[0] == 0:
         return 0
-    X, Y = tx.data, ty.data
+    dt = out.dtype
+    X, Y = tx.data.to(dt), ty.data.to(dt)
     left = pairs[:, 0]
     ub, cnt = torch.unique_consecutive(left, return_counts=True)
     starts = torch.cumsum(cnt, 0) - cnt
@@ -291,7 +310,7 @@ def direct_sums(pairs, tx: Tree, ty: Tree, b, lcs: float, out):
         rights = pairs[s:s + c, 1]
         yj = torch.cat([ty.sorted_index[ty.offsets[r]:ty.offsets[r + 1]] for r in rights.tolist()])
         xs, ys = X[xi], Y[yj]
-        d2 = torch.zeros(xs.shape[0], ys.shape[0], dtype=F32)
+        d2 = torch.zeros(xs.shape[0], ys.shape[0], dtype=dt)
         for k in range(X.shape[1]):
             diff = xs[:, k, None] - ys[None, :, k]
             d2 += diff * diff
@@ -301,37 +320,39 @@ def direct_sums(pairs, tx: Tree, ty: Tree, b, lcs: float, out):
 
 
 def far_field(far, tx: Tree, ty: Tree, b, lcs: float, P: int, out, stats):
-    """far_field_compute_v2 (n_tree.cu:489-593): P2M -> node-to-node sums -> L2P."""
+    """far_field_compute_v2 (n_tree.cu:489-593): P2M -> node-to-node sums -> L2P.  Arithmetic in out.dtype."""
     d = tx.d
+    dt = out.dtype
     ps = node_list(d, P)
-    nodes_1d, w_1d = zip(*[cheb_nodes_weights(p) for p in ps])
+    nodes_1d, w_1d = zip(*[cheb_nodes_weights(p, dt) for p in ps])
     _, grid = tensor_grid(list(nodes_1d))                      # (P, d) in [-1,1]
     Pn = grid.shape[0]
-    edge = tx.edge
+    edge = tx.edge.to(dt)
+    xdata, ydata, xctr, yctr = tx.data.to(dt), ty.data.to(dt), tx.centers.to(dt), ty.centers.to(dt)
     R = b.shape[1]
     uy = torch.unique(far[:, 1])
     ux = torch.unique(far[:, 0])
     factor = 2 / edge                                          # 1_d_conv.cu:473
     # P2M (lagrange_shared, 1_d_conv.cu:451-552)
-    mom = torch.zeros(ty.counts.numel(), Pn, R, dtype=F32)
+    mom = torch.zeros(ty.counts.numel(), Pn, R, dtype=dt)
     needed = torch.zeros(ty.counts.numel(), dtype=torch.bool)
     needed[uy] = True
     idx = ty.sorted_index[needed[ty.box_of_point[ty.sorted_index]]]
     for s in range(0, idx.numel(), 1 << 15):
         ii = idx[s:s + (1 << 15)]
         bx = ty.box_of_point[ii]
-        T = factor * (ty.data[ii] - ty.centers[bx])
+        T = factor * (ydata[ii] - yctr[bx])
         B = full_basis(T, nodes_1d, w_1d)
         mom.index_add_(0, bx, B[:, :, None] * b[ii][:, None, :])
     # M2L (setup_skip_conv n_tree.cu:433-486; skip_conv_far_boxes_opt 1_d_conv.cu:741-817)
     g = grid * edge / 2. + edge / 2.                           # n_tree.cu:510
-    loc = torch.zeros(tx.counts.numel(), Pn, R, dtype=F32)
+    loc = torch.zeros(tx.counts.numel(), Pn, R, dtype=dt)
     chunk = max(1, (1 << 24) // (Pn * Pn))
     for s in range(0, far.shape[0], chunk):
         blk = far[s:s + chunk]
-        xi = g[None, :, :] + tx.centers[blk[:, 0]][:, None, :]
-        yj = g[None, :, :] + ty.centers[blk[:, 1]][:, None, :]
-        d2 = torch.zeros(blk.shape[0], Pn, Pn, dtype=F32)
+        xi = g[None, :, :] + xctr[blk[:, 0]][:, None, :]
+        yj = g[None, :, :] + yctr[blk[:, 1]][:, None, :]
+        d2 = torch.zeros(blk.shape[0], Pn, Pn, dtype=dt)
         for k in range(d):
             diff = xi[:, :, None, k] - yj[:, None, :, k]
             d2 += diff * diff
@@ -344,7 +365,7 @@ def far_field(far, tx: Tree, ty: Tree, b, lcs: float, P: int, out, stats):
     for s in range(0, idx.numel(), 1 << 15):
         ii = idx[s:s + (1 << 15)]
         bx = tx.box_of_point[ii]
-        T = factor * (tx.data[ii] - tx.centers[bx])
+        T = factor * (xdata[ii] - xctr[bx])
         B = full_basis(T, nodes_1d, w_1d)
         out[ii] += torch.einsum("np,npr->nr", B, loc[bx])
 
@@ -356,14 +377,19 @@ def f3m_kmvm(X: torch.Tensor, Y: Optional[torch.Tensor], b: torch.Tensor, ls: fl
              min_points: float = 1000., nr_of_interpolation: int = 64, var_compression: bool = False,
              eff_var_limit: float = 0.15, small_field_points: int = 1000,
              trace: Optional[List[Dict]] = None, lists_only: bool = False,
-             stats: Optional[Dict] = None) -> Optional[torch.Tensor]:
-    """FFM_XY<float,d> (n_tree.cu:1056-1125).  Y=None means the shared-tree case X is Y."""
+             stats: Optional[Dict] = None, dtype=F32, near_tie_far=None) -> Optional[torch.Tensor]:
+    """FFM_XY<float,d> (n_tree.cu:1056-1125).  Y=None means the shared-tree case X is Y.
+
+    dtype=torch.float64 evaluates the SAME algorithm -- the float32 tree, box assignment and interaction lists of
+    the reference, per-level P2M -> M2L -> L2P and the direct sums -- with all arithmetic on b in float64.  Its
+    distance from the float32 result is the reference algorithm's own rounding error, which is what separates
+    "differs from the reference" from "differs from what the reference computes up to its rounding"."""
     X = X.to(F32).contiguous()
-    b = b.to(F32).contiguous()
+    b = b.to(dtype).contiguous()
     same = Y is None
     stats = stats if stats is not None else {}
     lcs = float(np.float32(1) / (np.float32(2) * np.float32(ls) * np.float32(ls)))   # n_tree.cu:1060
-    out = torch.zeros(X.shape[0], b.shape[1], dtype=F32)
+    out = torch.zeros(X.shape[0], b.shape[1], dtype=dtype)
     edge, xmin, ymin = bounding_cube(X, None if same else Y.to(F32))
     tx = Tree(X, edge, xmin)
     ty = tx if same else Tree(Y.to(F32).contiguous(), edge, ymin)
@@ -384,7 +410,7 @@ def f3m_kmvm(X: torch.Tensor, Y: Optional[torch.Tensor], b: torch.Tensor, ls: fl
         pairs = candidate_pairs(near, tx, ty)
         P_level = nr_of_interpolation
         far_m, small_m, keep_m = classify_pairs(pairs, tx, ty, lcs, nr_of_interpolation,
-                                                small_field_points, var_compression, eff_var_limit)
+                                                small_field_points, var_compression, eff_var_limit, near_tie_far)
         far, small, near = pairs[far_m], pairs[small_m], pairs[keep_m]
         if var_compression:                      # get_interpolation_rule (n_tree.cu:971-978,1022-1028)
             e = np.float32(float(tx.edge))

@@ -14,6 +14,9 @@ CASES = {
     "u1_shared": dict(d=1, N=8000, M=None, dist="uniform", ls=0.2, min_points=200., P=8, small=8, var_comp=False, eff=0.15, R=1, seed=7),
     "n4_r8": dict(d=4, N=20000, M=None, dist="normal", ls=1.0, min_points=500., P=81, small=81, var_comp=False, eff=0.15, R=8, seed=8),
     "n5_r8": dict(d=5, N=12000, M=None, dist="normal", ls=1.5, min_points=1000., P=32, small=32, var_comp=False, eff=0.15, R=8, seed=9),
+    # 4-D uniform with few nodes: at level 2 the list holds whole families of pairs exactly on the far threshold
+    # (offsets (+-2,0,0,0) and (+-1,+-1,+-1,+-1): centre distance = 2 edges), the ties of 1_d_conv.cu:903-953
+    "u4_shared": dict(d=4, N=30000, M=None, dist="uniform", ls=0.8, min_points=100., P=16, small=16, var_comp=False, eff=0.15, R=1, seed=18),
     "clustered3": dict(d=3, N=30000, M=None, dist="clustered", ls=0.5, min_points=300., P=64, small=64, var_comp=False, eff=0.15, R=1, seed=10),
     # per-level far path (more than 8 nodes per dimension, or node counts that change between levels)
     "u2_p10": dict(d=2, N=20000, M=None, dist="uniform", ls=0.5, min_points=300., P=100, small=100, var_comp=False, eff=0.15, R=1, seed=13),

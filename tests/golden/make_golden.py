@@ -1,14 +1,15 @@
 """Generates the golden fixtures in this folder by running the UNMODIFIED reference (MrHuff/F3M) on a GPU.
 
 The reference has no CPU path, so it cannot run where it is built: oracle/Makefile compiles it for
-sm_100a from the reference's own sources into oracle/_ref/f3m_ref_d3.so, and this script is run on a
-machine with a B200:
+sm_100a from the reference's own sources into oracle/_ref/f3m_ref_d{3,4,5}.so (one module per dimension),
+and this script is run on a machine with a B200:
 
-    python tests/golden/make_golden.py [out_dir]      # default out_dir: ./golden_out ; copy the files here afterwards
+    python tests/golden/make_golden.py [out_dir] [case ...]   # default out_dir: ./golden_out, default: all cases;
+                                                              # copy the files here afterwards
 
 For every seeded case of tests/cases.py listed in GOLDEN_CASES it stores, per level, the reference's
 box offsets (unique_counts_cum_reindexed), box centres, the box of every point at the finest level,
-the far / small / keep pair lists (get_field), and the product FFM_XY<float,3>(X, Y, b); plus the
+the far / small / keep pair lists (get_field), and the product FFM_XY<float,d>(X, Y, b); plus the
 reference's own dense product on the first rows.  Files are small .npz archives.
 """
 import importlib.util
@@ -23,7 +24,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 from cases import make_case  # noqa: E402
 
-GOLDEN_CASES = ["u3_default", "u3_shared", "u3_sqrt12_ls01", "u3_xy", "u3_varcomp", "clustered3", "dup_points", "n3_p125_r3"]
+GOLDEN_CASES = ["u3_default", "u3_shared", "u3_sqrt12_ls01", "u3_xy", "u3_varcomp", "clustered3", "dup_points", "n3_p125_r3",
+                "n4_r8", "u4_shared", "n5_r8"]
 
 
 def load_ref(d=3):
@@ -50,10 +52,14 @@ def canon(pairs):
 def main():
     out_dir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "golden_out")
     os.makedirs(out_dir, exist_ok=True)
-    ref = load_ref(3)
+    names = sys.argv[2:] or GOLDEN_CASES
+    refs = {}
     dev = "cuda:0"
-    for name in GOLDEN_CASES:
+    for name in names:
         c = make_case(name)
+        if c["d"] not in refs:
+            refs[c["d"]] = load_ref(c["d"])
+        ref = refs[c["d"]]
         X = c["X"].to(dev)
         Y = X if c["Y"] is None else c["Y"].to(dev)
         b = c["b"].to(dev)

@@ -108,6 +108,14 @@ def test_engine_matches_reference_golden(name, cuda):
         assert np.array_equal(box_of_point, g[f"{key}_box_of_point_finest"]), "box of point at the finest level"
     err = rel_l2(out.cpu(), g["out"])
     assert err <= TOL_VS_ORACLE, f"rel-L2 vs reference product {err:.3e}"
+    # the reference's own exact dense op (rbf_float_d, F3M_src/pybinder_setup.cu:40-50) on the first rows, stored in the
+    # fixture, against this engine's dense op: both are float32 sums with an approximate exponential
+    from f3m_b200 import engine
+    ref_rows = g["dense_ref_rows"]
+    X = c["X"].to(cuda)
+    Y = X if c["Y"] is None else c["Y"].to(cuda)
+    dense = engine.rbf_dense(X[:ref_rows.shape[0]].contiguous(), Y, c["b"].to(cuda), c["ls"]).cpu()
+    assert rel_l2(dense, ref_rows) <= 5e-6, f"dense op vs the reference's dense op {rel_l2(dense, ref_rows):.3e}"
 
 
 @pytest.mark.parametrize("name", ["u3_shared", "u3_xy", "n4_r8"])
@@ -396,3 +404,110 @@ def test_engine_vs_reference_live(n, m, ls, P, var_comp, cuda):
     # 1e-5 of the reference, unless the reference itself is further than that from the exact product: then the
     # engine cannot be closer to the reference than the reference is to the truth, and must beat it instead
     assert err <= max(TOL_VS_ORACLE, 1.1 * e_ref), f"rel-L2 vs reference {err:.3e} (reference's own error vs float64 {e_ref:.3e})"
+    if err > TOL_VS_ORACLE:
+        # The relaxed bound above was used.  Show where the gap comes from: evaluate the reference ALGORITHM (same
+        # float32 tree and lists, per-level P2M -> M2L -> L2P, direct sums) in float64.  The engine must be within
+        # 1e-5 of that, and the reference's distance from it -- its own float32 rounding -- must account for the gap.
+        from oracle.f3m_oracle import f3m_kmvm
+        alg64 = f3m_kmvm(X.cpu(), None if m is None else Y.cpu(), b.cpu(), ls, min_points=1000.0, nr_of_interpolation=P,
+                         var_compression=var_comp, eff_var_limit=0.3, small_field_points=P, dtype=torch.float64)
+        e_alg, r_alg = rel_l2(out.cpu(), alg64), rel_l2(out_ref.cpu(), alg64)
+        print(f"   reference algorithm in float64: engine {e_alg:.3e}, reference {r_alg:.3e}")
+        assert e_alg <= TOL_VS_ORACLE, f"engine vs the reference algorithm in float64 {e_alg:.3e}"
+        assert r_alg >= 0.8 * err and abs(r_alg - err) <= 0.5 * err, \
+            f"gap to the reference {err:.3e} is not explained by the reference's rounding {r_alg:.3e}"
+
+
+def test_reference_algorithm_in_float64_p216(cuda):
+    """At 216 nodes the reference's float32 rounding (atomic float32 P2M sums, exp of float32 node distances) is larger
+    than 1e-5 of the product.  The engine is compared with the reference ALGORITHM evaluated in float64 (same float32 tree
+    and lists): within 1e-5, and closer to it than the float32 restatement of the same algorithm is."""
+    from f3m_b200 import engine, _lib
+    from oracle.f3m_oracle import f3m_kmvm
+    g = torch.Generator().manual_seed(216)
+    n = 60000
+    X = torch.rand(n, 3, generator=g)
+    b = torch.randn(n, 1, generator=g)
+    kw = dict(ls=1.0, min_points=400.0, nr_of_interpolation=216, var_compression=False, eff_var_limit=0.15, small_field_points=216)
+    alg32 = f3m_kmvm(X, None, b, **kw)
+    alg64 = f3m_kmvm(X, None, b, dtype=torch.float64, **kw)
+    prm = engine.make_params(1.0, 400.0, 216, False, 0.15, 216, math_mode=_lib.MATH_IEEE)
+    out = engine.kmvm(X.to(cuda), None, b.to(cuda), prm).cpu()
+    e_engine, e_alg32 = rel_l2(out, alg64), rel_l2(alg32, alg64)
+    print(f"P=216: engine vs algorithm-in-float64 {e_engine:.3e}; float32 restatement vs the same {e_alg32:.3e}")
+    assert e_engine <= TOL_VS_ORACLE
+    assert e_engine <= max(e_alg32, 2e-6)
+
+
+def test_polynomial_exponent_variants_run(cuda):
+    """Which form of the direct-sum kernel a list takes depends on (scaled box edge)^2: the all-MUFU form, the form
+    that evaluates 2/5 of the exponentials by a degree-2 polynomial, and the degree-3 form must each run for the
+    lengthscales chosen here, and each must agree with the CPU restatement of the same algorithm to 1e-5."""
+    from f3m_b200 import engine, _lib
+    from oracle.f3m_oracle import f3m_kmvm
+    g = torch.Generator().manual_seed(31)
+    n = 40000
+    X = torch.rand(n, 3, generator=g)
+    b = torch.randn(n, 1, generator=g)
+    seen = {}
+    for ls in (0.2, 1.6, 4.0):
+        prm = engine.make_params(ls, 300.0, 64, False, 0.15, 64, math_mode=_lib.MATH_IEEE)
+        plan = engine.Plan(X.to(cuda), None, prm)
+        out = plan.apply(b.to(cuda)).cpu()
+        v = plan.direct_variants()
+        ref = f3m_kmvm(X, None, b, ls, min_points=300.0, nr_of_interpolation=64, small_field_points=64)
+        err = rel_l2(out, ref)
+        print(f"ls={ls}: variants {v}, rel-L2 vs the restatement {err:.3e}")
+        assert err <= TOL_VS_ORACLE
+        for k, c in v.items():
+            seen[k] = seen.get(k, 0) + c
+    assert seen["mufu"] > 0 and seen["poly2"] > 0 and seen["poly3"] > 0, seen
+
+
+def test_two_separate_point_sets_level1_reach(cuda):
+    """X and Y in two small cubes a few lengthscales apart: the level-1 boxes hold fewer than 2P points, so every
+    level-1 pair is "small" whatever its distance (size is tested before distance, 1_d_conv.cu:916-920) and the
+    direct sums see targets far outside the usual reach of a source box.  The result must match the float64 dense
+    product; 150 lengthscales apart it must be finite and (numerically) zero."""
+    from f3m_b200 import engine
+    g = torch.Generator().manual_seed(41)
+    for edge, sep, tol in ((0.1, 1.4, 2e-5), (0.15, 2.5, 2e-5), (0.2, 4.0, 1e-4), (1.0, 150.0, None)):
+        X = torch.rand(300, 3, generator=g) * edge
+        Y = torch.rand(250, 3, generator=g) * edge + sep
+        b = torch.randn(250, 2, generator=g)
+        prm = engine.make_params(1.0, 20.0, 64, False, 0.15, 64)
+        plan = engine.Plan(X.to(cuda), Y.to(cuda), prm)
+        out = plan.apply(b.to(cuda)).cpu()
+        st = plan.stats()
+        assert st["levels"] >= 1 and plan.level(1)["n_small"] > 0
+        assert torch.isfinite(out).all()
+        exact = engine.rbf_dense(X.double().to(cuda), Y.double().to(cuda), b.double().to(cuda), 1.0).cpu()
+        if tol is None:
+            assert float(out.abs().max()) <= 1e-30 and float(exact.abs().max()) <= 1e-30
+        else:
+            err = rel_l2(out, exact)
+            print(f"edge {edge} separation {sep}: variants {plan.direct_variants()}, rel-L2 vs float64 {err:.3e}")
+            assert err <= tol
+
+
+def test_leading_slice_is_not_the_shared_tree(cuda):
+    """Y = X[:k] starts at X's address but is another point set: it must not be taken for the shared-tree case
+    (which would read N rows of a k-row b)."""
+    from f3m_b200 import engine
+    from F3M_src.FFM_classes import FFM
+    g = torch.Generator().manual_seed(51)
+    X = torch.rand(9000, 3, generator=g).to(cuda)
+    b = torch.randn(9000, 1, generator=g).to(cuda)
+    k = 2500
+    prm = engine.make_params(1.0, 300.0, 64, False, 0.15, 64)
+    out = engine.kmvm(X, X[:k], b[:k], prm)
+    exact = engine.rbf_dense(X.double(), X[:k].double(), b[:k].double(), 1.0)
+    assert rel_l2(out.cpu(), exact.cpu()) <= 1e-4
+    with pytest.raises(AssertionError):
+        engine.kmvm(X, X[:k], b, prm)                       # b has N rows, Y has k
+    op = FFM(X, ls=1.0, min_points=300, nr_of_interpolation=64, small_field_points=64, device="cuda:0")
+    full = op @ b
+    chunked = op.chunk_forward_example(b, chunks=3)        # first chunk of Y is a leading slice of X
+    assert rel_l2(chunked.cpu(), full.cpu()) <= 1e-4
+    plan = engine.Plan(X, X[:k], prm)
+    assert not plan.same and plan.M == k

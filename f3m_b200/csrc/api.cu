@@ -12,7 +12,7 @@
 
 namespace f3m {
 
-long long g_launches = 0;
+std::atomic<long long> g_launches{0};
 static thread_local char g_err[512] = "";
 
 void set_error(const char *fmt, ...) {
@@ -88,7 +88,7 @@ void dev_free(void *p, size_t granted) {
 
 using namespace f3m;
 
-// Small per-plan scratch (64 pinned host words for read-backs, 64 device words for flags and counters).
+// Small per-plan scratch (FLAG_WORDS pinned host words for read-backs, as many device words for flags and counters).
 // cudaHostAlloc / cudaMalloc / cudaFree serialise the device, so slots are created once and recycled:
 // a plan takes a slot of its device from a free list and gives it back when it is destroyed.
 namespace {
@@ -107,8 +107,8 @@ ScratchSlot take_slot(int device) {
             }
     }
     ScratchSlot sl{device, nullptr, nullptr};
-    F3M_CUDA(cudaHostAlloc((void **)&sl.h_pinned, 64 * sizeof(int), cudaHostAllocDefault));
-    F3M_CUDA(cudaMalloc((void **)&sl.d_flags, 64 * sizeof(int)));
+    F3M_CUDA(cudaHostAlloc((void **)&sl.h_pinned, FLAG_WORDS * sizeof(int), cudaHostAllocDefault));
+    F3M_CUDA(cudaMalloc((void **)&sl.d_flags, FLAG_WORDS * sizeof(int)));
     return sl;
 }
 void give_slot(const ScratchSlot &sl) {
@@ -158,7 +158,7 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
         pl->h_pinned = sl.h_pinned;
         pl->d_flags = sl.d_flags;
     }
-    F3M_CUDA(cudaMemsetAsync(pl->d_flags, 0, 64 * sizeof(int), s));
+    F3M_CUDA(cudaMemsetAsync(pl->d_flags, 0, FLAG_WORDS * sizeof(int), s));
     pl->last.begin(ST_BUILD, s);
 
     // bounding cube: calculate_edge_X / calculate_edge (n_tree.cu:25-46), float32 throughout
@@ -183,11 +183,25 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
     float edge0 = range * 1.01f;
     F3M_REQUIRE(edge0 > 0.f && std::isfinite(edge0), F3M_ERR_ARG, "degenerate or non-finite bounding cube (edge %g)", edge0);
 
-    build_sorted_tree(pl->tx, X, N, d, xmin, edge0, prm->math_mode, pl, s);
+    // Only the key bits of the levels the loop below will visit are sorted.  The loop stops at the first level whose
+    // largest box holds at most min_points points; for evenly spread points that is the level where the mean
+    // occupancy falls below min_points (one more when the mean is within a factor two of it).  If the loop does
+    // go deeper (clustered points), the trees are sorted again to the full key depth.
+    auto estimate_depth = [&](int64_t n) {
+        const int lmax = std::min(30 / d, 20);
+        int L = 1;
+        auto mean = [&](int l) { return (double)n / pow(2.0, (double)d * l); };
+        while (L < lmax && mean(L) > (double)prm->min_points) L++;
+        if (L < lmax && mean(L) > 0.5 * (double)prm->min_points) L++;
+        return L;
+    };
+    int depth = estimate_depth(N);
+    if (!pl->same) depth = std::min(depth, estimate_depth(M));
+    build_sorted_tree(pl->tx, X, N, d, xmin, edge0, prm->math_mode, depth, s);
     build_root(pl->tx, s);
     if (pl->same) pl->ty = &pl->tx;
     else {
-        build_sorted_tree(pl->ty_store, Y, M, d, ymin, edge0, prm->math_mode, pl, s);
+        build_sorted_tree(pl->ty_store, Y, M, d, ymin, edge0, prm->math_mode, depth, s);
         build_root(pl->ty_store, s);
         pl->ty = &pl->ty_store;
     }
@@ -216,8 +230,20 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
     const int p_full = nodes_per_dim(d, prm->nr_interpolation);
     int p_small = nodes_per_dim(d, std::min((int)lround(pow(3.0, d)), prm->nr_interpolation));
     while (go_on()) {
-        build_next_level(tx, pl, s);
-        if (!pl->same) build_next_level(ty, pl, s);
+        const int need = level + 1;
+        F3M_REQUIRE(need <= tx.lmax, F3M_ERR_DEPTH,
+                    "tree needs level %d but a 30-bit cell index holds %d levels in %d dimensions", need, tx.lmax, d);
+        if (need > tx.sorted_depth) {
+            // deeper than estimated: sort to the full key depth (levels already built keep their boxes)
+            build_sorted_tree(tx, X, N, d, xmin, edge0, prm->math_mode, tx.lmax, s);
+            if (!pl->same) build_sorted_tree(ty, Y, M, d, ymin, edge0, prm->math_mode, ty.lmax, s);
+        }
+        if ((int)tx.levels.size() <= need) {
+            // a first batch up to the estimated depth, later batches three levels at a time
+            const int last = tx.sorted_depth < tx.lmax ? tx.sorted_depth : std::min(tx.sorted_depth, need + 2);
+            build_levels(tx, last, pl, s);
+            if (!pl->same) build_levels(ty, last, pl, s);
+        }
         level++;
         pl->lists.emplace_back();
         build_level_lists(pl, level, s);
@@ -234,12 +260,12 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
         pl->stats.far_box_pairs += ll.far.count;
         pl->stats.node_pairs += ll.far.count * (int64_t)P * P;
         pl->stats.near_box_pairs += ll.small.count;
-        accumulate_pair_work(pl, level, ll.small, &pl->stats.direct_pairs, s);
+        accumulate_pair_work(pl, level, ll.small, s);
     }
     pl->levels = level;
     if (level > 0) {
         pl->stats.near_box_pairs += pl->lists[level].keep.count;
-        accumulate_pair_work(pl, level, pl->lists[level].keep, &pl->stats.direct_pairs, s);
+        accumulate_pair_work(pl, level, pl->lists[level].keep, s);
     } else {
         // no level was built: the root pair is summed directly
         pl->stats.near_box_pairs = 1;
@@ -249,7 +275,9 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
     pl->stats.shared_tree = pl->same;
     pl->stats.edge0 = edge0;
     pl->last.end(s);
+    F3M_CUDA(cudaMemcpyAsync(pl->h_pinned + FL_PAIRWORK, pl->d_flags + FL_PAIRWORK, sizeof(long long), cudaMemcpyDeviceToHost, s));
     F3M_CUDA(cudaStreamSynchronize(s));
+    if (level > 0) pl->stats.direct_pairs = *reinterpret_cast<long long *>(pl->h_pinned + FL_PAIRWORK);
     pl->last.ms[ST_BUILD] = 0.f;
     pl->last.resolve();
     pl->stats.build_ms = pl->last.ms[ST_BUILD];
@@ -322,7 +350,7 @@ const char *f3m_status_string(int st) {
 }
 
 const char *f3m_last_error(void) { return g_err; }
-long long f3m_launch_count(void) { return g_launches; }
+long long f3m_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int f3m_plan_create(f3m_plan **plan, const float *X, int64_t N, const float *Y, int64_t M, int32_t d,
                     const f3m_params *prm, void *stream) {
@@ -361,6 +389,10 @@ int f3m_plan_moments_range(f3m_plan *plan, const float *b, int32_t R, int64_t sr
     if (!plan || !b || !mom_out) return F3M_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     int st = guarded([&] {
+        F3M_REQUIRE(R >= 1, F3M_ERR_ARG, "bad right-hand side (R=%d)", R);
+        int dev;
+        F3M_CUDA(cudaGetDevice(&dev));
+        F3M_REQUIRE(dev == plan->device, F3M_ERR_ARG, "plan was built on device %d, current device is %d", plan->device, dev);
         F3M_REQUIRE(far_moments_size(plan, R) > 0, F3M_ERR_UNSUPPORTED, "this plan does not exchange moments (see f3m_plan_moments_size)");
         Tree &ty = *plan->ty;
         DevBuf<float> bs;
@@ -386,6 +418,130 @@ int f3m_plan_apply_range_moments(f3m_plan *plan, const float *b, int32_t R, floa
     int st = f3m_plan_apply_range(plan, b, R, out, row_begin, row_end, stream);
     plan->ext_mom = nullptr;
     return st;
+}
+
+/* ---- one product shared by several GPUs, in phases ------------------------------------------------------------ */
+
+int f3m_plan_partition_rows(f3m_plan *plan, int32_t R, int32_t nparts, int64_t *bounds, void *stream) {
+    if (!plan || !bounds || nparts < 1 || R < 1) return F3M_ERR_ARG;
+    return guarded([&] {
+        int dev;
+        F3M_CUDA(cudaGetDevice(&dev));
+        F3M_REQUIRE(dev == plan->device, F3M_ERR_ARG, "plan was built on device %d, current device is %d", plan->device, dev);
+        shard_partition(plan, R, nparts, bounds, (cudaStream_t)stream);
+    });
+}
+
+int f3m_plan_shard_begin(f3m_plan *plan, const float *b, int32_t R, int64_t row_begin, int64_t row_end, int64_t box_begin,
+                         int64_t box_end, float *mom_slice, void *stream) {
+    if (!plan || !b) return F3M_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    int st = guarded([&] {
+        F3M_REQUIRE(R >= 1, F3M_ERR_ARG, "bad right-hand side (R=%d)", R);
+        int dev;
+        F3M_CUDA(cudaGetDevice(&dev));
+        F3M_REQUIRE(dev == plan->device, F3M_ERR_ARG, "plan was built on device %d, current device is %d", plan->device, dev);
+        Tree &tx = plan->tx, &ty = *plan->ty;
+        const int L = plan->levels;
+        f3m_plan::Shard &sh = plan->shard;
+        sh.active = false;
+        sh.R = R;
+        sh.row_begin = std::max<int64_t>(0, row_begin);
+        sh.row_end = std::min<int64_t>(tx.n, row_end);
+        for (float &m : plan->last.ms) m = 0.f;
+        plan->last.ms[ST_BUILD] = plan->stats.build_ms;
+        plan->last.direct_launches = 0;
+        for (int &v : plan->last.direct_variants) v = 0;
+        const int64_t msize = far_moments_size(plan, R);
+        const bool exchange = msize > 0 && mom_slice != nullptr;
+        const int nby = ty.levels[L].nb;
+        box_begin = std::max<int64_t>(0, std::min<int64_t>(box_begin, nby));
+        box_end = std::max<int64_t>(box_begin, std::min<int64_t>(box_end, nby));
+        plan->last.begin(ST_PERMUTE, s);
+        shard_mark_and_gather(plan, b, R, (int)sh.row_begin, (int)sh.row_end, exchange ? (int)box_begin : 0, exchange ? (int)box_end : 0,
+                              !exchange, s);
+        plan->last.end(s);
+        if (exchange && box_end > box_begin) {
+            // sorted-row range of the source boxes [box_begin, box_end)
+            const int *off = ty.levels[L].off.p;
+            F3M_CUDA(cudaMemcpyAsync(plan->h_pinned + 0, off + box_begin, sizeof(int), cudaMemcpyDeviceToHost, s));
+            F3M_CUDA(cudaMemcpyAsync(plan->h_pinned + 1, off + box_end, sizeof(int), cudaMemcpyDeviceToHost, s));
+            F3M_CUDA(cudaStreamSynchronize(s));
+            const int64_t per_box = msize / nby;
+            plan->moments_out = mom_slice - box_begin * per_box;   // the kernels address moments by box number
+            plan->mom_begin = plan->h_pinned[0];
+            plan->mom_end = plan->h_pinned[1];
+            plan->mom_box_begin = box_begin;
+            plan->mom_box_end = box_end;
+            far_field(plan, sh.bs.p, R, nullptr, 0, 0, s);
+        }
+        F3M_CUDA(cudaStreamSynchronize(s));
+        sh.active = true;
+    });
+    plan->moments_out = nullptr;
+    plan->mom_box_begin = plan->mom_box_end = -1;
+    if (st != F3M_OK) cudaStreamSynchronize(s);
+    plan->last.resolve();
+    return st;
+}
+
+int f3m_plan_shard_near(f3m_plan *plan, float *acc_sorted, void *stream) {
+    if (!plan || !acc_sorted) return F3M_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    int st = guarded([&] {
+        f3m_plan::Shard &sh = plan->shard;
+        F3M_REQUIRE(sh.active, F3M_ERR_ARG, "f3m_plan_shard_near without f3m_plan_shard_begin");
+        const int L = plan->levels, R = sh.R;
+        const int64_t rb = sh.row_begin, re = sh.row_end;
+        if (re > rb) F3M_CUDA(cudaMemsetAsync(acc_sorted + rb * R, 0, (size_t)(re - rb) * R * sizeof(float), s));
+        if (L == 0) direct_sums(plan, 0, plan->lists[0].keep, sh.bs.p, R, acc_sorted, rb, re, s);
+        for (int level = 1; level <= L; level++) direct_sums(plan, level, plan->lists[level].small, sh.bs.p, R, acc_sorted, rb, re, s);
+        if (L > 0) direct_sums(plan, L, plan->lists[L].keep, sh.bs.p, R, acc_sorted, rb, re, s);
+        F3M_CUDA(cudaStreamSynchronize(s));
+    });
+    if (st != F3M_OK) cudaStreamSynchronize(s);
+    plan->last.resolve();
+    return st;
+}
+
+int f3m_plan_shard_far(f3m_plan *plan, const float *mom, float *acc_sorted, void *stream) {
+    if (!plan || !acc_sorted) return F3M_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    int st = guarded([&] {
+        f3m_plan::Shard &sh = plan->shard;
+        F3M_REQUIRE(sh.active, F3M_ERR_ARG, "f3m_plan_shard_far without f3m_plan_shard_begin");
+        F3M_REQUIRE(mom || sh.all_sources, F3M_ERR_ARG, "this product exchanges moments: pass the gathered moment array");
+        plan->ext_mom = sh.all_sources ? nullptr : mom;
+        far_field(plan, sh.bs.p, sh.R, acc_sorted, sh.row_begin, sh.row_end, s);
+        F3M_CUDA(cudaMemcpyAsync(plan->h_pinned, plan->d_flags + FL_ERR, sizeof(int), cudaMemcpyDeviceToHost, s));
+        F3M_CUDA(cudaStreamSynchronize(s));
+        F3M_REQUIRE(plan->h_pinned[0] == 0, F3M_ERR_INTERNAL, "device-side consistency check failed (code %d)", plan->h_pinned[0]);
+    });
+    plan->ext_mom = nullptr;
+    if (st != F3M_OK) cudaStreamSynchronize(s);
+    plan->last.resolve();
+    return st;
+}
+
+int f3m_plan_shard_end(f3m_plan *plan) {
+    if (!plan) return F3M_ERR_ARG;
+    plan->shard.active = false;
+    plan->shard.bs.release();
+    plan->shard.need.clear();
+    return F3M_OK;
+}
+
+int f3m_plan_rows_to_input_order(const f3m_plan *plan, const float *acc_sorted, int32_t R, int64_t in_lo, int64_t in_hi, float *out,
+                                 void *stream) {
+    if (!plan || !acc_sorted || !out || R < 1 || in_lo < 0 || in_hi < in_lo || in_hi > plan->tx.n) return F3M_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    return guarded([&] {
+        int dev;
+        F3M_CUDA(cudaGetDevice(&dev));
+        F3M_REQUIRE(dev == plan->device, F3M_ERR_ARG, "plan was built on device %d, current device is %d", plan->device, dev);
+        shard_rows_to_input_order(plan, acc_sorted, R, in_lo, in_hi, out, s);
+        F3M_CUDA(cudaStreamSynchronize(s));
+    });
 }
 
 int f3m_plan_apply(f3m_plan *plan, const float *b, int32_t R, float *out, void *stream) {

@@ -1,9 +1,11 @@
 // Internal declarations shared by the translation units of libf3m.so.
 #pragma once
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
+#include <atomic>
 #include <vector>
 #include "f3m.h"
 
@@ -27,10 +29,10 @@ struct Fail {
             throw f3m::Fail{F3M_ERR_CUDA};                                                       \
         }                                                                                        \
     } while (0)
-extern long long g_launches;   // kernels launched by this library (all threads; informational)
+extern std::atomic<long long> g_launches;   // kernels launched by this library (all threads; informational)
 #define F3M_LAUNCH_CHECK()                                                                       \
     do {                                                                                         \
-        ++f3m::g_launches;                                                                       \
+        f3m::g_launches.fetch_add(1, std::memory_order_relaxed);                                                                   \
         F3M_CUDA(cudaGetLastError());                                                            \
     } while (0)
 #define F3M_REQUIRE(cond, code, ...)                                                             \
@@ -86,6 +88,70 @@ struct DevBuf {
     ~DevBuf() { release(); }
 };
 
+// ---- block-wide exclusive scan (all threads of the block call it; blockDim.x a multiple of 32, at most 1024) ----
+__device__ __forceinline__ int block_exclusive_scan(int v, int *total_out, int *smem /* >= 33 ints */) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) smem[wid] = inc;
+    __syncthreads();
+    if (wid == 0) {
+        int w = lane < nw ? smem[lane] : 0;
+        int winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int t = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += t;
+        }
+        smem[lane] = winc - w;
+        if (lane == 31) smem[32] = winc;
+    }
+    __syncthreads();
+    int res = smem[wid] + inc - v;
+    if (total_out) *total_out = smem[32];
+    __syncthreads();
+    return res;
+}
+
+// largest b with off[b] <= i: the box of sorted row i (off = box offsets of a level, nb boxes)
+__device__ __forceinline__ int box_of_row(const int *__restrict__ off, int nb, int i) {
+    int lo = 0, hi = nb;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (off[mid] <= i) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// chebyshev_nodes_1D / get_w_j_first_kind (F3M_src/n_tree.cu:265-285): first-kind Chebyshev nodes and barycentric
+// weights with the reference's float32 expression (PI as a float, arguments rounded to float before cos / sin).
+inline void cheb_nodes_weights(int p, float *node, float *w) {
+    const float PI = (float)(atan(1.) * 4.);
+    for (int i = 0; i < p; i++) {
+        const float arg = ((float)i * 2.f + 1.f) * PI / (float)(2 * (p - 1) + 2);
+        node[i] = (float)cos((double)arg);
+        w[i] = (float)(pow(-1.0, i) * sin(((2. * (float)i + 1.) * PI) / (2. * (float)(p - 1.0) + 2.)));
+    }
+}
+
+// ---- small per-plan device words (f3m_plan::d_flags) and their pinned host mirror ------------------
+constexpr int FLAG_WORDS = 256;
+enum FlagSlot {
+    FL_ERR = 0,          // device-side consistency check failed
+    FL_LISTTOT = 8,      // 6 words: 64-bit far / small / keep pair counts of the level being built
+    FL_BBOX = 16,        // 2 * MAXD words
+    FL_MMA_COUNTER = 32, // tile cursor of the tensor-core near kernel
+    FL_LEAF = 40,        // 2 words: small / big finest-level boxes
+    FL_NSMALL = 42,      // target tiles of at most 32 points
+    FL_LVTOT = 64,       // boxes per level of the batch being built (F3M_MAX_LEVELS words)
+    FL_LVMAX = 96,       // largest box per level (F3M_MAX_LEVELS words)
+    FL_PAIRWORK = 128    // 2 words per level: 64-bit sum of n_x * n_y over the level's direct lists
+};
+
 // ---- tree ------------------------------------------------------------------------------------
 struct Level {
     int nb = 0;             // occupied boxes
@@ -104,8 +170,9 @@ struct Tree {
     const float *data = nullptr;   // caller's rows
     float origin[MAXD] = {0};      // per-dimension minimum
     float edge0 = 0.f;             // cube edge
-    int lmax = 0;                  // depth of the sort key
-    DevBuf<uint32_t> keys;         // (n) sorted Morton keys at depth lmax
+    int lmax = 0;                  // depth of the Morton key
+    int sorted_depth = 0;          // the keys are sorted by their first sorted_depth levels (d bits each)
+    DevBuf<uint32_t> keys;         // (n) Morton keys at depth lmax, sorted by their first sorted_depth levels
     DevBuf<int> perm;              // (n) sorted position -> input row
     DevBuf<float> pts;             // (d,n) sorted coordinates, one plane per dimension
     std::vector<Level> levels;     // levels[0] is the root
@@ -188,9 +255,19 @@ struct f3m_plan {
     bool leaf_split[2] = {false, false};
     float *moments_out = nullptr;
     int64_t mom_begin = 0, mom_end = 0;
+    int64_t mom_box_begin = -1, mom_box_end = -1;   // >= 0: moments_out covers these source boxes only
     const float *ext_mom = nullptr;
-    int *h_pinned = nullptr;              // pinned host words for count read-back
-    int *d_flags = nullptr;               // device status / counters (64 ints)
+    // a product shared by several GPUs, in phases (f3m_plan_shard_begin / _near / _far): state kept between the calls
+    struct Shard {
+        bool active = false;
+        bool all_sources = false;                          // no halo bookkeeping: bs holds every row
+        int R = 0;
+        int64_t row_begin = 0, row_end = 0;
+        f3m::DevBuf<float> bs;                             // b in sorted order, filled for the boxes this rank reads
+        std::vector<f3m::DevBuf<unsigned char>> need;      // per level: source boxes named by the rank's direct lists
+    } shard;
+    int *h_pinned = nullptr;              // pinned host words for count read-back (FLAG_WORDS ints)
+    int *d_flags = nullptr;               // device status / counters (FLAG_WORDS ints, see FlagSlot)
     ~f3m_plan();
 };
 
@@ -199,17 +276,19 @@ namespace f3m {
 // ---- sort.cu ---------------------------------------------------------------------------------
 void bounding_box(const float *X, int64_t n, int d, float *h_min, float *h_max, f3m_plan *pl, cudaStream_t s);
 void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *origin, float edge0,
-                       int math_mode, f3m_plan *pl, cudaStream_t s);
-void exclusive_scan_i32(const int *in, int *out, int64_t n, cudaStream_t s);  // out may alias in; writes n+1? no: n values
+                       int math_mode, int depth, cudaStream_t s);
+void exclusive_scan_i32(const int *in, int *out, int64_t n, cudaStream_t s);  // n values; out may alias in
+// up to four arrays of n values scanned in place by one set of launches; their sums as 64-bit numbers -> totals64 (device)
+void exclusive_scan_multi(int *const *arrays, int narr, int64_t n, long long *totals64, cudaStream_t s);
 void gather_rows(const float *src, const int *perm, float *dst, int64_t n, int cols, cudaStream_t s);
 void scatter_rows(const float *src, const int *perm, float *dst, int64_t n, int cols, cudaStream_t s);
 void scatter_rows_nonzero(const float *src, const int *perm, float *dst, int64_t n, int cols, cudaStream_t s);
 
 // ---- tree.cu ---------------------------------------------------------------------------------
 void build_root(Tree &t, cudaStream_t s);
-void build_next_level(Tree &t, f3m_plan *pl, cudaStream_t s);        // appends levels[l+1]
+void build_levels(Tree &t, int l_last, f3m_plan *pl, cudaStream_t s);   // appends levels up to l_last (<= sorted_depth)
 void build_level_lists(f3m_plan *pl, int level, cudaStream_t s);     // uses lists[level-1].keep
-void accumulate_pair_work(f3m_plan *pl, int level, const PairCSR &csr, int64_t *h_pairs, cudaStream_t s);
+void accumulate_pair_work(f3m_plan *pl, int level, const PairCSR &csr, cudaStream_t s);   // adds into FL_PAIRWORK (device)
 
 // ---- far.cu ----------------------------------------------------------------------------------
 int nodes_per_dim(int d, int nr_interpolation);   // get_node_list for perfect powers, floor otherwise
@@ -218,6 +297,13 @@ void far_field_level(f3m_plan *pl, int level, const float *b_sorted, int R, floa
 void far_field(f3m_plan *pl, const float *b_sorted, int R, float *out_sorted, int64_t row_begin, int64_t row_end,
                cudaStream_t s);                                               // whole product (far_fast.cu)
 int64_t far_moments_size(const f3m_plan *pl, int R);
+
+// ---- shard.cu --------------------------------------------------------------------------------
+void shard_partition(f3m_plan *pl, int R, int nparts, int64_t *h_bounds, cudaStream_t s);
+void shard_mark_and_gather(f3m_plan *pl, const float *b, int R, int row_begin, int row_end, int box_begin, int box_end,
+                           bool everything, cudaStream_t s);
+void shard_rows_to_input_order(const f3m_plan *pl, const float *acc_sorted, int R, int64_t in_lo, int64_t in_hi, float *out,
+                               cudaStream_t s);
 
 // ---- near.cu ---------------------------------------------------------------------------------
 void direct_sums(f3m_plan *pl, int level, const PairCSR &csr, const float *b_sorted, int R, float *out_sorted,

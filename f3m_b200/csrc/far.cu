@@ -35,17 +35,10 @@ struct NodeTab {
     float w[MAXP];
 };
 
-// chebyshev_nodes_1D / get_w_j_first_kind (n_tree.cu:265-285): first-kind Chebyshev nodes and
-// barycentric weights, evaluated in double and rounded to float32.
 static NodeTab make_nodes(int p) {
     NodeTab t{};
     t.p = p;
-    const float PI = (float)(atan(1.) * 4.);
-    for (int i = 0; i < p; i++) {
-        float arg = ((float)i * 2.f + 1.f) * PI / (float)(2 * (p - 1) + 2);
-        t.node[i] = (float)cos((double)arg);
-        t.w[i] = (float)(pow(-1.0, i) * sin(((2. * (float)i + 1.) * PI) / (2. * (float)(p - 1.0) + 2.)));
-    }
+    cheb_nodes_weights(p, t.node, t.w);
     return t;
 }
 
@@ -70,14 +63,6 @@ __device__ __forceinline__ void lagrange_1d(float t, const NodeTab &nt, float *d
     }
 }
 
-__device__ __forceinline__ int box_of(const int *__restrict__ off, int nb, int i) {
-    int lo = 0, hi = nb;          // largest b with off[b] <= i
-    while (hi - lo > 1) {
-        int mid = (lo + hi) >> 1;
-        if (off[mid] <= i) lo = mid; else hi = mid;
-    }
-    return lo;
-}
 
 __global__ void __launch_bounds__(256) mark_sources(const int *__restrict__ idx, int64_t n, unsigned char *need) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -101,7 +86,7 @@ __global__ void __launch_bounds__(CH) p2m_kernel(const float *__restrict__ pts, 
     const int j = threadIdx.x, i = c0 + j;
     int mybox = -1;
     if (i < n) {
-        mybox = box_of(off, nb, i);
+        mybox = box_of_row(off, nb, i);
         if (!need[mybox]) mybox = -1;
     }
     s_box[j] = mybox;
@@ -116,7 +101,7 @@ __global__ void __launch_bounds__(CH) p2m_kernel(const float *__restrict__ pts, 
     }
     __syncthreads();
     const int last = min(n - c0, CH) - 1;
-    const int box_first = box_of(off, nb, c0), box_last = box_of(off, nb, c0 + last);
+    const int box_first = box_of_row(off, nb, c0), box_last = box_of_row(off, nb, c0 + last);
     // thread -> (node, point group)
     int groups = CH / P;
     if (groups < 1) groups = 1;
@@ -270,7 +255,7 @@ __global__ void __launch_bounds__(CH) l2p_kernel(const float *__restrict__ pts, 
     float *Ls = sm;   // [D*p][CH]
     const int j = threadIdx.x, i = blockIdx.x * CH + j;
     if (i >= n) return;
-    const int box = box_of(off, nb, i);
+    const int box = box_of_row(off, nb, i);
     if (fptr[box + 1] == fptr[box]) return;
     { int o = off[box]; if (o < row_begin || o >= row_end) return; }
 #pragma unroll
@@ -368,7 +353,7 @@ static void far_level_impl(f3m_plan *pl, int level, const float *bs, int R, int 
         size_t smem = (size_t)2 * PR * sizeof(float);
         F3M_REQUIRE(ept <= 32 && smem <= 200 * 1024, F3M_ERR_UNSUPPORTED,
                     "%d interpolation nodes x %d columns exceed the node-to-node kernel's capacity", P, RB);
-        int *d_err = pl->d_flags + 0;
+        int *d_err = pl->d_flags + FL_ERR;
 #define F3M_M2L(E)                                                                                                   \
     {                                                                                                                \
         F3M_CUDA(cudaFuncSetAttribute(m2l_kernel<D, RB, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \

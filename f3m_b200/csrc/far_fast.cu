@@ -44,16 +44,10 @@ struct Geom2 {
 
 __host__ __device__ constexpr int mat_stride(int p) { return (p * p + 3) / 4 * 4; }
 
-// chebyshev_nodes_1D / get_w_j_first_kind (n_tree.cu:265-285)
 static NodeTab2 make_nodes2(int p) {
     NodeTab2 t{};
     t.p = p;
-    const float PI = (float)(atan(1.) * 4.);
-    for (int i = 0; i < p; i++) {
-        float arg = ((float)i * 2.f + 1.f) * PI / (float)(2 * (p - 1) + 2);
-        t.node[i] = (float)cos((double)arg);
-        t.w[i] = (float)(pow(-1.0, i) * sin(((2. * (float)i + 1.) * PI) / (2. * (float)(p - 1.0) + 2.)));
-    }
+    cheb_nodes_weights(p, t.node, t.w);
     return t;
 }
 
@@ -1027,7 +1021,7 @@ static void ensure_leaf_split(f3m_plan *pl, int which, Level &lv, cudaStream_t s
     if (pl->leaf_split[which]) return;
     pl->leaf_small[which].alloc((size_t)lv.nb, s);
     pl->leaf_big[which].alloc((size_t)lv.nb, s);
-    int *counts = pl->d_flags + 40;
+    int *counts = pl->d_flags + FL_LEAF;
     F3M_CUDA(cudaMemsetAsync(counts, 0, 2 * sizeof(int), s));
     split_leaf_boxes<<<(lv.nb + 255) / 256, 256, 0, s>>>(lv.nb, lv.off.p, pl->leaf_small[which].p, pl->leaf_big[which].p, counts);
     F3M_LAUNCH_CHECK();
@@ -1061,7 +1055,11 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
     if (pl->moments_out) {
         // sharded P2M: finest-level moments of the source boxes that start in [mom_begin, mom_end), zero elsewhere
         Level &ly = ty.levels[L];
-        F3M_CUDA(cudaMemsetAsync(pl->moments_out, 0, (size_t)ly.nb * PR * sizeof(float), s));
+        if (pl->mom_box_end >= 0)   // the caller's array holds the boxes [mom_box_begin, mom_box_end) only
+            F3M_CUDA(cudaMemsetAsync(pl->moments_out + pl->mom_box_begin * PR, 0,
+                                     (size_t)(pl->mom_box_end - pl->mom_box_begin) * PR * sizeof(float), s));
+        else
+            F3M_CUDA(cudaMemsetAsync(pl->moments_out, 0, (size_t)ly.nb * PR * sizeof(float), s));
         int nsplit = std::max(1, std::min(64, (ly.max_count + 8191) / 8192));
         size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
         F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -83,8 +83,10 @@ __device__ __forceinline__ void tile_accumulate(const float *__restrict__ smem, 
 // are wide compared with the lengthscale (see near_kernel_x2 below for the usual case).
 // items: (target box, tile) ; tile_off[b] = first item of box b (exclusive scan of tiles per box)
 // ---------------------------------------------------------------------------------------------
+// (rows outside [row_begin, row_end) belong to another slice of the targets and are not touched)
 __device__ __forceinline__ void item_to_tile(int item, const int *__restrict__ tile_off, int nbx,
-                                             const int *__restrict__ off_x, int &box, int &t0, int &t1) {
+                                             const int *__restrict__ off_x, int row_begin, int row_end, int &box, int &t0,
+                                             int &t1) {
     int lo = 0, hi = nbx;   // largest b with tile_off[b] <= item
     while (hi - lo > 1) {
         int mid = (lo + hi) >> 1;
@@ -92,7 +94,7 @@ __device__ __forceinline__ void item_to_tile(int item, const int *__restrict__ t
     }
     box = lo;
     const int tile = item - tile_off[box], ntiles = tile_off[box + 1] - tile_off[box];
-    const int a = off_x[box], nb = off_x[box + 1] - a;
+    const int a = max(off_x[box], row_begin), nb = min(off_x[box + 1], row_end) - a;
     t0 = a + (int)(((long long)nb * tile) / ntiles);          // tiles of one box are equally full
     t1 = a + (int)(((long long)nb * (tile + 1)) / ntiles);
 }
@@ -102,11 +104,11 @@ __global__ void __launch_bounds__(NT) near_kernel(const float *__restrict__ xpts
                                                  int nbx, const int *__restrict__ tile_off,
                                                  const int *__restrict__ ptr, const int *__restrict__ idx,
                                                  const int *__restrict__ off_y, const float *__restrict__ packed,
-                                                 float scale, int R, int r0, float *out) {
+                                                 float scale, int R, int r0, float *out, int row_begin, int row_end) {
     constexpr int W = row_width(D, RB);
     __shared__ __align__(16) float smem[ST * W];
     int box, t0, t1;
-    item_to_tile(blockIdx.x, tile_off, nbx, off_x, box, t0, t1);
+    item_to_tile(blockIdx.x, tile_off, nbx, off_x, row_begin, row_end, box, t0, t1);
     float tx[TI][D], tot[TI][RB];
     int ti[TI];
 #pragma unroll
@@ -164,14 +166,6 @@ constexpr int NT2 = 32;     // threads per CTA: one warp, so a tile holds 64 tar
                             // splits into tiles that are nearly full (measured: 64-thread CTAs lose 7% to padding)
 constexpr int TI2 = 2;      // targets per thread
 
-__device__ __forceinline__ int box_of_pt(const int *__restrict__ off, int nb, int i) {
-    int lo = 0, hi = nb;
-    while (hi - lo > 1) {
-        int mid = (lo + hi) >> 1;
-        if (off[mid] <= i) lo = mid; else hi = mid;
-    }
-    return lo;
-}
 
 // ---------------------------------------------------------------------------------------------
 // Expanded form with packed FP32 pairs (fma.rn.f32x2, sm_100): two SOURCES share every instruction of
@@ -202,11 +196,13 @@ __host__ __device__ __forceinline__ int pair_row_start(int off, int box) { retur
 template <int D, int RB>
 __global__ void __launch_bounds__(256) pack_pairs_rel(const float *__restrict__ pts, int n, const float *__restrict__ bs,
                                                      int R, int r0, float scale, const int *__restrict__ off_y, int nby,
-                                                     const float *__restrict__ ctr_y, float *packed) {
+                                                     const float *__restrict__ ctr_y, const unsigned char *__restrict__ need,
+                                                     float *packed) {
     constexpr int W = row_width(D, RB);
     int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= n) return;
-    const int by = box_of_pt(off_y, nby, j);
+    const int by = box_of_row(off_y, nby, j);
+    if (need && !need[by]) return;   // a slice of the targets reads only the source boxes its lists name
     const int s0 = off_y[by], s1 = off_y[by + 1];
     float row[W];
     float ny = 0.f;
@@ -342,16 +338,17 @@ __device__ __forceinline__ void near_tile_x2(const float *__restrict__ xpts, int
 // TI = targets per thread.  MIXED: a tile of at most 32 targets (small boxes) runs the one-target form, which does half
 // the work; the host picks this variant only when such tiles exist.
 template <int D, int RB, int POLY, int PNUM, int PDEN, bool MIXED>
-__global__ void __launch_bounds__(NT2, 32) near_kernel_x2(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
+__global__ void __launch_bounds__(NT2, RB == 1 ? 32 : (RB <= 4 ? 20 : 12)) near_kernel_x2(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
                                                      int nbx, const int *__restrict__ tile_off,
                                                      const int *__restrict__ ptr, const int *__restrict__ idx,
                                                      const int *__restrict__ off_y, const float *__restrict__ ctr_y,
                                                      const float *__restrict__ packed, float scale, int R, int r0,
-                                                     float *out, float pc0, float pc1, float pc2, float pc3) {
+                                                     float *out, float pc0, float pc1, float pc2, float pc3, int row_begin,
+                                                     int row_end) {
     constexpr int W = row_width(D, RB);
     __shared__ __align__(16) float smem[SP2 * 2 * W];
     int box, t0, t1;
-    item_to_tile(blockIdx.x, tile_off, nbx, off_x, box, t0, t1);
+    item_to_tile(blockIdx.x, tile_off, nbx, off_x, row_begin, row_end, box, t0, t1);
     if (MIXED && t1 - t0 <= NT2)
         near_tile_x2<D, RB, POLY, PNUM, PDEN, 1>(xpts, n_x, ptr, idx, off_y, ctr_y, packed, scale, R, r0, out, pc0, pc1, pc2, pc3, smem,
                                                  box, t0, t1);
@@ -362,18 +359,18 @@ __global__ void __launch_bounds__(NT2, 32) near_kernel_x2(const float *__restric
 
 #include "near_mma.cuh"
 
-// tiles[b] = tiles of target box b (0 when it has no pairs or lies outside the row range); *n_small counts the boxes
-// whose single tile holds at most 32 targets
+// tiles[b] = tiles of the rows of target box b inside [row_begin, row_end) (0 when the box has no pairs or no row
+// there); *n_small counts the boxes whose single tile holds at most 32 targets
 __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__restrict__ off_x, const int *__restrict__ ptr,
                                                          int row_begin, int row_end, int tile_pts, int *tiles, int *n_small) {
     int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b > nbx) return;
     int t = 0;
     if (b < nbx && ptr[b + 1] > ptr[b]) {
-        int o = off_x[b];
-        if (o >= row_begin && o < row_end) {
-            t = (off_x[b + 1] - o + tile_pts - 1) / tile_pts;
-            if (n_small && off_x[b + 1] - o <= 32) atomicAdd(n_small, 1);
+        const int len = min(off_x[b + 1], row_end) - max(off_x[b], row_begin);
+        if (len > 0) {
+            t = (len + tile_pts - 1) / tile_pts;
+            if (n_small && len <= 32) atomicAdd(n_small, 1);
         }
     }
     tiles[b] = t;
@@ -475,10 +472,10 @@ __global__ void __launch_bounds__(128) near_taylor_kernel(const float *__restric
                                                          int nbx, const int *__restrict__ tile_off,
                                                          const int *__restrict__ ptr, const int *__restrict__ idx,
                                                          const float *__restrict__ ctr_y, const float *__restrict__ mom,
-                                                         float scale, int R, float *out) {
+                                                         float scale, int R, float *out, int row_begin, int row_end) {
     using ML = MomLayout<D, ORD>;
     int box, t0, t1;
-    item_to_tile(blockIdx.x, tile_off, nbx, off_x, box, t0, t1);
+    item_to_tile(blockIdx.x, tile_off, nbx, off_x, row_begin, row_end, box, t0, t1);
     const int i = t0 + threadIdx.x;
     if (i >= t1) return;
     float x[D];
@@ -586,7 +583,7 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     const int tile_pts = use_mma ? MM_M : (expanded ? NT2 * TI2 : NT);
     DevBuf<int> tiles;
     tiles.alloc((size_t)lx.nb + 1, s);
-    int *n_small = pl->d_flags + 42;
+    int *n_small = pl->d_flags + FL_NSMALL;
     F3M_CUDA(cudaMemsetAsync(n_small, 0, sizeof(int), s));
     near_tiles_per_box<<<(unsigned)((lx.nb + 1 + 255) / 256), 256, 0, s>>>(lx.nb, lx.off.p, csr.ptr.p, row_begin, row_end,
                                                                            tile_pts, tiles.p, n_small);
@@ -613,7 +610,7 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
         pack_split_rows<D><<<g, 256, 0, s>>>(ty.pts.p, (int)ty.n, bs, R, r0, scale, ly.off.p, ly.nb, ly.ctr.p, Bc.p, rows, Gb.p);
         pl->last.end(s);
         F3M_LAUNCH_CHECK();
-        int *counter = pl->d_flags + 32;
+        int *counter = pl->d_flags + FL_MMA_COUNTER;
         F3M_CUDA(cudaMemsetAsync(counter, 0, sizeof(int), s));
         // range of t = 2 u.v - |v|^2 over the pairs of the list: |u| <= reach * se, |v| <= se / 2 per dimension
         const double se = (double)scale * ly.edge;
@@ -632,7 +629,8 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
                                       mm_smem_bytes<D>()));                                                                   \
         near_mma_kernel<D, DEG_, NP_><<<grid, MM_THREADS, mm_smem_bytes<D>(), s>>>(                                                 \
             tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, items, csr.ptr.p, csr.idx.p, ly.off.p, ly.ctr.p, Bc.p, rows, Gb.p, \
-            scale, R, r0, out, counter, pl->d_flags, (float)cf[0], (float)cf[1], (float)cf[2], (float)cf[3]);                 \
+            scale, R, r0, out, counter, pl->d_flags, (float)cf[0], (float)cf[1], (float)cf[2], (float)cf[3], row_begin,       \
+            row_end);                                                                                                         \
     }
         if (deg == 2) F3M_NEAR_MMA(2, 6)
         else if (deg == 3) F3M_NEAR_MMA(3, 5)
@@ -646,7 +644,8 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     }
     pl->last.begin(ST_PERMUTE, s);
     if (expanded) {
-        pack_pairs_rel<D, RB><<<g, 256, 0, s>>>(ty.pts.p, (int)ty.n, bs, R, r0, scale, ly.off.p, ly.nb, ly.ctr.p, packed.p);
+        pack_pairs_rel<D, RB><<<g, 256, 0, s>>>(ty.pts.p, (int)ty.n, bs, R, r0, scale, ly.off.p, ly.nb, ly.ctr.p,
+                                                (pl->shard.active && !pl->shard.all_sources) ? pl->shard.need[level].p : nullptr, packed.p);
     } else
         pack_sources<D, RB><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
     pl->last.end(s);
@@ -660,7 +659,7 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
 #define F3M_NEAR_EXP2(POLY_, PNUM_, PDEN_, MIXED_)                                                                                       \
     near_kernel_x2<D, RB, POLY_, PNUM_, PDEN_, MIXED_><<<items, NT2, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, \
                                                                             csr.idx.p, ly.off.p, ly.ctr.p, packed.p, scale, R, r0, out, \
-                                                                            (float)cf[0], (float)cf[1], (float)cf[2], (float)cf[3])
+                                                                            (float)cf[0], (float)cf[1], (float)cf[2], (float)cf[3], row_begin, row_end)
 #define F3M_NEAR_EXP(POLY_, PNUM_, PDEN_)                         \
     {                                                             \
         if (small_tiles) F3M_NEAR_EXP2(POLY_, PNUM_, PDEN_, true); \
@@ -675,7 +674,7 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     else {
         pl->last.direct_variants[DV_DIRECT]++;
         near_kernel<D, RB, 1><<<items, NT, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, csr.idx.p, ly.off.p,
-                                                   packed.p, scale, R, r0, out);
+                                                   packed.p, scale, R, r0, out, row_begin, row_end);
     }
     pl->last.end(s);
     pl->last.direct_launches++;
@@ -706,7 +705,7 @@ static void taylor_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
                                                                                              ly.off.p, ly.nb, ly.ctr.p, mom.p);
     F3M_LAUNCH_CHECK();
     near_taylor_kernel<D, ORD><<<items, 128, 0, s>>>(tx.pts.p, (int)tx.n, lx.off.p, lx.nb, tiles.p, csr.ptr.p, csr.idx.p, ly.ctr.p,
-                                                    mom.p, scale, R, out);
+                                                    mom.p, scale, R, out, row_begin, row_end);
     pl->last.end(s);
     pl->last.direct_launches++;
     pl->last.direct_variants[DV_MOMENTS]++;

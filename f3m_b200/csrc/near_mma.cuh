@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(256) pack_split_rows(const float *__restrict__
     using S = MmaShape<D>;
     int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= n) return;
-    const int by = box_of_pt(off_y, nby, j);
+    const int by = box_of_row(off_y, nby, j);
     const int s0 = off_y[by], s1 = off_y[by + 1];
     float vh[D], vl[D], nv = 0.f;
 #pragma unroll
@@ -232,7 +232,8 @@ __global__ void __launch_bounds__(MM_THREADS, 2)
 near_mma_kernel(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x, int nbx, const int *__restrict__ tile_off,
                 int n_items, const int *__restrict__ ptr, const int *__restrict__ idx, const int *__restrict__ off_y,
                 const float *__restrict__ ctr_y, const float4 *__restrict__ Bc, size_t rows, const float *__restrict__ Gb,
-                float scale, int R, int r0, float *out, int *counter, int *err, float pc0, float pc1, float pc2, float pc3) {
+                float scale, int R, int r0, float *out, int *counter, int *err, float pc0, float pc1, float pc2, float pc3,
+                int row_begin, int row_end) {
     using S = MmaShape<D>;
     constexpr int KC = S::KC;
     constexpr int A_ONE = 2 * KC * MM_M;   // float4 per A buffer (A1 and A2)
@@ -303,8 +304,9 @@ near_mma_kernel(const float *__restrict__ xpts, int n_x, const int *__restrict__
             }
             box = lo;
         }
-        const int t0 = off_x[box] + MM_M * (item - tile_off[box]);
-        const int nrows = min(MM_M, off_x[box + 1] - t0);
+        // only the rows inside [row_begin, row_end): the others belong to another slice of the targets
+        const int t0 = max(off_x[box], row_begin) + MM_M * (item - tile_off[box]);
+        const int nrows = min(MM_M, min(off_x[box + 1], row_end) - t0);
         const bool row_ok = consumer && row < nrows;
         const bool warp_rows = 32 * (warp & 3) < nrows;   // does this warp hold any target
         float x[D];

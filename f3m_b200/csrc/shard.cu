@@ -1,0 +1,244 @@
+// One product shared by several GPUs: helpers of the phase entry points (f3m_plan_partition_rows,
+// f3m_plan_shard_begin / _near / _far, f3m_plan_rows_to_input_order).
+//
+// The reference has no counterpart: its multi-GPU mode runs independent block products in separate processes
+// (par_FFM_block, experiments/FFM_classes.py:128-211).  Here every rank holds the same plan and owns a contiguous
+// slice of the sorted target rows, cut at finest-level box starts.  What a rank reads from the sources is limited
+// to the boxes its own direct lists name (its slice plus a halo) and to the boxes whose moments it computes.
+#include <algorithm>
+#include "common.cuh"
+
+namespace f3m {
+
+__device__ __forceinline__ int lower_bound_i32(const int *__restrict__ a, int n, int v) {
+    int lo = 0, hi = n;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (a[mid] < v) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+// ---------------------------------------------------------------------------------------------
+// which source boxes does a slice of the targets read?
+// ---------------------------------------------------------------------------------------------
+// one warp per target box of the level: boxes with a row inside [row_begin, row_end) mark the sources of their row
+__global__ void __launch_bounds__(256) mark_list_sources(int nbx, const int *__restrict__ off_x, const int *__restrict__ ptr,
+                                                   const int *__restrict__ idx, int row_begin, int row_end, unsigned char *need) {
+    const int lane = threadIdx.x & 31;
+    const int box = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (box >= nbx) return;
+    if (off_x[box + 1] <= row_begin || off_x[box] >= row_end) return;
+    for (int e = ptr[box] + lane; e < ptr[box + 1]; e += 32) need[idx[e]] = 1;
+}
+
+// one block per source box of a coarser level: a marked box marks the finest-level boxes it contains
+__global__ void __launch_bounds__(128) need_to_finest(int nb, const int *__restrict__ off, const unsigned char *__restrict__ need,
+                                                     int nb_fine, const int *__restrict__ off_fine, unsigned char *need_fine) {
+    const int b = blockIdx.x;
+    if (b >= nb || !need[b]) return;
+    const int j0 = lower_bound_i32(off_fine, nb_fine, off[b]), j1 = lower_bound_i32(off_fine, nb_fine, off[b + 1]);
+    for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) need_fine[j] = 1;
+}
+
+__global__ void __launch_bounds__(256) mark_box_range(int box_begin, int box_end, unsigned char *need) {
+    const int j = box_begin + blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < box_end) need[j] = 1;
+}
+
+// one warp per finest-level source box: rows of b of the marked boxes, in sorted order
+__global__ void __launch_bounds__(256) gather_rows_of_boxes(int nb, const int *__restrict__ off, const unsigned char *__restrict__ need,
+                                                           const float *__restrict__ b, const int *__restrict__ perm, int cols,
+                                                           float *bs) {
+    const int lane = threadIdx.x & 31;
+    const int box = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (box >= nb || !need[box]) return;
+    const int64_t e0 = (int64_t)off[box] * cols, e1 = (int64_t)off[box + 1] * cols;
+    for (int64_t e = e0 + lane; e < e1; e += 32) {
+        const int64_t i = e / cols;
+        const int c = (int)(e - i * cols);
+        bs[e] = b[(int64_t)perm[i] * cols + c];
+    }
+}
+
+void shard_mark_and_gather(f3m_plan *pl, const float *b, int R, int row_begin, int row_end, int box_begin, int box_end,
+                           bool everything, cudaStream_t s) {
+    Tree &tx = pl->tx, &ty = *pl->ty;
+    const int L = pl->levels;
+    f3m_plan::Shard &sh = pl->shard;
+    sh.need.resize(L + 1);
+    sh.bs.alloc((size_t)ty.n * R, s);
+    if (everything || L == 0) {
+        // no halo bookkeeping: all sources (plans without far pairs, or whose moments cannot be exchanged)
+        for (int l = 0; l <= L; l++) sh.need[l].release();
+        gather_rows(b, ty.perm.p, sh.bs.p, ty.n, R, s);
+        sh.all_sources = true;
+        return;
+    }
+    sh.all_sources = false;
+    for (int l = 1; l <= L; l++) {
+        sh.need[l].alloc((size_t)ty.levels[l].nb, s);
+        sh.need[l].zero();
+    }
+    auto mark = [&](int level, const PairCSR &csr) {
+        if (csr.count == 0) return;
+        Level &lx = tx.levels[level];
+        mark_list_sources<<<(unsigned)(((int64_t)lx.nb * 32 + 255) / 256), 256, 0, s>>>(lx.nb, lx.off.p, csr.ptr.p, csr.idx.p, row_begin,
+                                                                                   row_end, sh.need[level].p);
+        F3M_LAUNCH_CHECK();
+    };
+    for (int l = 1; l <= L; l++) mark(l, pl->lists[l].small);
+    mark(L, pl->lists[L].keep);
+    Level &lf = ty.levels[L];
+    for (int l = 1; l < L; l++) {
+        if (pl->lists[l].small.count == 0) continue;
+        Level &ly = ty.levels[l];
+        need_to_finest<<<ly.nb, 128, 0, s>>>(ly.nb, ly.off.p, sh.need[l].p, lf.nb, lf.off.p, sh.need[L].p);
+        F3M_LAUNCH_CHECK();
+    }
+    // rows of b for the direct sums (marked boxes) and for this rank's share of the moments
+    DevBuf<unsigned char> rows_need;
+    rows_need.alloc((size_t)lf.nb, s);
+    F3M_CUDA(cudaMemcpyAsync(rows_need.p, sh.need[L].p, (size_t)lf.nb, cudaMemcpyDeviceToDevice, s));
+    if (box_end > box_begin) {
+        mark_box_range<<<(unsigned)((box_end - box_begin + 255) / 256), 256, 0, s>>>(box_begin, box_end, rows_need.p);
+        F3M_LAUNCH_CHECK();
+    }
+    gather_rows_of_boxes<<<(unsigned)(((int64_t)lf.nb * 32 + 255) / 256), 256, 0, s>>>(lf.nb, lf.off.p, rows_need.p, b, ty.perm.p, R,
+                                                                                      sh.bs.p);
+    F3M_LAUNCH_CHECK();
+    // rows_need is released here; the kernel above is already queued on the stream the next user of the block is on
+}
+
+// ---------------------------------------------------------------------------------------------
+// rows of the sorted result that belong to one range of INPUT rows, written in input order
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rows_to_input_order(const float *__restrict__ acc, const int *__restrict__ perm, int64_t n,
+                                                          int cols, int64_t in_lo, int64_t in_hi, float *out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t r = perm[i];
+    if (r < in_lo || r >= in_hi) return;
+    for (int c = 0; c < cols; c++) out[(r - in_lo) * cols + c] = acc[i * cols + c];
+}
+
+void shard_rows_to_input_order(const f3m_plan *pl, const float *acc_sorted, int R, int64_t in_lo, int64_t in_hi, float *out,
+                               cudaStream_t s) {
+    const Tree &tx = pl->tx;
+    rows_to_input_order<<<(unsigned)((tx.n + 255) / 256), 256, 0, s>>>(acc_sorted, tx.perm.p, tx.n, R, in_lo, in_hi, out);
+    F3M_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
+// slices of equal estimated work
+// ---------------------------------------------------------------------------------------------
+// one warp per target box of a level: estimated cost of its direct lists and of its far row, added to the
+// finest-level box that holds the box's first row (the slice of that row computes the whole box, apart from the
+// clipping of coarse direct tiles, which only matters for boxes that straddle a cut)
+__global__ void __launch_bounds__(256) box_work_kernel(int nbx, const int *__restrict__ off_x, const int *__restrict__ off_y,
+                                                      const int *__restrict__ ptr_a, const int *__restrict__ idx_a,
+                                                      const int *__restrict__ ptr_b, const int *__restrict__ idx_b,
+                                                      const int *__restrict__ far_ptr, double w_pair, double w_far, double w_point,
+                                                      int nb_fine, const int *__restrict__ off_fine, double *work) {
+    const int lane = threadIdx.x & 31;
+    const int box = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (box >= nbx) return;
+    long long ny = 0;
+    if (ptr_a)
+        for (int e = ptr_a[box] + lane; e < ptr_a[box + 1]; e += 32) { const int by = idx_a[e]; ny += off_y[by + 1] - off_y[by]; }
+    if (ptr_b)
+        for (int e = ptr_b[box] + lane; e < ptr_b[box + 1]; e += 32) { const int by = idx_b[e]; ny += off_y[by + 1] - off_y[by]; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ny += __shfl_xor_sync(0xffffffffu, ny, o);
+    if (lane) return;
+    const double nx = (double)(off_x[box + 1] - off_x[box]);
+    double w = w_pair * nx * (double)ny + w_point * nx;
+    if (far_ptr) w += w_far * (double)(far_ptr[box + 1] - far_ptr[box]);
+    if (w > 0.0) atomicAdd(&work[lower_bound_i32(off_fine, nb_fine, off_x[box])], w);
+}
+
+// one block: running sum of the work over the finest-level boxes, cuts where it passes k / nparts of the total
+__global__ void __launch_bounds__(1024) partition_kernel(int nb, const double *__restrict__ work, const int *__restrict__ off,
+                                                        int nparts, long long *bounds) {
+    __shared__ double part[1024];
+    __shared__ double total_s;
+    const int per = (nb + 1023) / 1024;
+    const int j0 = min(nb, (int)threadIdx.x * per), j1 = min(nb, j0 + per);
+    double s = 0.0;
+    for (int j = j0; j < j1; j++) s += work[j];
+    part[threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double run = 0.0;
+        for (int t = 0; t < 1024; t++) { const double v = part[t]; part[t] = run; run += v; }
+        total_s = run;
+        bounds[0] = 0;
+        bounds[nparts] = off[nb];
+        for (int k = 1; k < nparts; k++) bounds[k] = -1;
+    }
+    __syncthreads();
+    const double total = total_s;
+    if (total <= 0.0) {   // no work estimate (no lists): even row counts
+        if (threadIdx.x == 0)
+            for (int k = 1; k < nparts; k++) {
+                const int target = (int)(((long long)off[nb] * k) / nparts);
+                bounds[k] = off[lower_bound_i32(off, nb, target)];
+            }
+        return;
+    }
+    // the same additions as above, so that the sum at the end of a thread's boxes equals the next thread's start
+    const double base = part[threadIdx.x];
+    double loc = 0.0;
+    for (int j = j0; j < j1; j++) {
+        const double before = base + loc;
+        loc += work[j];
+        const double after = base + loc;
+        // cut k lies after box j when the running sum passes k * total / nparts inside this box
+        const int k0 = (int)floor(before * nparts / total), k1 = (int)floor(after * nparts / total);
+        for (int k = k0 + 1; k <= k1 && k < nparts; k++) bounds[k] = off[j + 1];
+    }
+}
+
+void shard_partition(f3m_plan *pl, int R, int nparts, int64_t *h_bounds, cudaStream_t s) {
+    Tree &tx = pl->tx, &ty = *pl->ty;
+    const int L = pl->levels, d = pl->d;
+    if (L == 0) {   // one box: nothing to cut
+        for (int k = 0; k <= nparts; k++) h_bounds[k] = k == 0 ? 0 : tx.n;
+        return;
+    }
+    Level &lf = tx.levels[L];
+    DevBuf<double> work;
+    work.alloc((size_t)lf.nb, s);
+    work.zero();
+    // cost per unit, relative to one direct pair of one column in three dimensions (measured on the N = 1e8 uniform
+    // workload: direct sums 2.0e-13 s per pair, node-to-node step 7.8e-14 s per multiply-add, finest-level
+    // interpolation 1.8e-13 s per point and node)
+    for (int l = 1; l <= L; l++) {
+        LevelLists &ll = pl->lists[l];
+        Level &lx = tx.levels[l], &ly = ty.levels[l];
+        int P = 1;
+        for (int k = 0; k < d; k++) P *= std::max(1, ll.p);
+        const double w_pair = (double)(d + R + 1) / 5.0;
+        const double w_far = 0.39 * (double)d * ll.p * P * R;
+        const double w_point = (l == L) ? 0.9 * (double)P * R : 0.0;
+        const bool has_keep = (l == L) && ll.keep.count > 0;
+        if (ll.small.count == 0 && ll.far.count == 0 && !has_keep && w_point == 0.0) continue;
+        box_work_kernel<<<(unsigned)(((int64_t)lx.nb * 32 + 255) / 256), 256, 0, s>>>(
+            lx.nb, lx.off.p, ly.off.p, ll.small.count ? ll.small.ptr.p : nullptr, ll.small.idx.p, has_keep ? ll.keep.ptr.p : nullptr,
+            ll.keep.idx.p, ll.far.count ? ll.far.ptr.p : nullptr, w_pair, w_far, w_point, lf.nb, lf.off.p, work.p);
+        F3M_LAUNCH_CHECK();
+    }
+    DevBuf<long long> bounds;
+    bounds.alloc((size_t)nparts + 1, s);
+    partition_kernel<<<1, 1024, 0, s>>>(lf.nb, work.p, lf.off.p, nparts, bounds.p);
+    F3M_LAUNCH_CHECK();
+    std::vector<long long> h((size_t)nparts + 1);
+    F3M_CUDA(cudaMemcpyAsync(h.data(), bounds.p, ((size_t)nparts + 1) * sizeof(long long), cudaMemcpyDeviceToHost, s));
+    F3M_CUDA(cudaStreamSynchronize(s));
+    // a cut that no box produced (more parts than boxes with work) repeats the previous one: that part is empty
+    h_bounds[0] = 0;
+    for (int k = 1; k <= nparts; k++) h_bounds[k] = h[k] < 0 ? h_bounds[k - 1] : std::max<int64_t>(h[k], h_bounds[k - 1]);
+    h_bounds[nparts] = tx.n;
+}
+
+}  // namespace f3m

@@ -5,49 +5,27 @@
 // box_division_cum_hash / box_division_assign_hash, F3M_src/1_d_conv.cu:1127-1191).  Here every
 // point gets ONE key -- its cell at the deepest level a 30-bit index can hold, bits interleaved so
 // that every level's box is a key prefix -- the keys are sorted once, and the points are gathered
-// into sorted planes.  All levels are then read off the sorted keys (tree.cu).  All kernels in this
-// file are HBM-bound streaming passes.
+// into sorted planes by the sort itself (the coordinates travel with the keys).  All levels are then read
+// off the sorted keys (tree.cu).  All kernels in this file are HBM-bound streaming passes.
+#include <algorithm>
 #include "common.cuh"
 
 namespace f3m {
 
 // ---------------------------------------------------------------------------------------------
-// device-wide exclusive scan (three launches, no inter-block waiting)
+// device-wide exclusive scan of up to four arrays of one length at once (three launches, no inter-block waiting)
 // ---------------------------------------------------------------------------------------------
 constexpr int SCAN_THREADS = 512;
 constexpr int SCAN_ITEMS = 8;
 constexpr int SCAN_TILE = SCAN_THREADS * SCAN_ITEMS;
+struct ScanArrays {
+    const int *in[4];
+    int *out[4];
+};
 
-__device__ __forceinline__ int block_exclusive_scan(int v, int *total_out, int *smem /* >= 33 ints */) {
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    int inc = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        int t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += t;
-    }
-    if (lane == 31) smem[wid] = inc;
-    __syncthreads();
-    if (wid == 0) {
-        int w = lane < nw ? smem[lane] : 0;
-        int winc = w;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            int t = __shfl_up_sync(0xffffffffu, winc, o);
-            if (lane >= o) winc += t;
-        }
-        smem[lane] = winc - w;
-        if (lane == 31) smem[32] = winc;
-    }
-    __syncthreads();
-    int res = smem[wid] + inc - v;
-    if (total_out) *total_out = smem[32];
-    __syncthreads();
-    return res;
-}
-
-__global__ void __launch_bounds__(SCAN_THREADS) scan_tile_sums(const int *__restrict__ in, int64_t n, int *part) {
+__global__ void __launch_bounds__(SCAN_THREADS) scan_tile_sums(ScanArrays a, int64_t n, int nt, int *part) {
     __shared__ int sm[33];
+    const int *__restrict__ in = a.in[blockIdx.y];
     int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
     int s = 0;
 #pragma unroll
@@ -55,25 +33,29 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_tile_sums(const int *__rest
         if (base + k < n) s += in[base + k];
     int total;
     block_exclusive_scan(s, &total, sm);
-    if (threadIdx.x == 0) part[blockIdx.x] = total;
+    if (threadIdx.x == 0) part[(size_t)blockIdx.y * nt + blockIdx.x] = total;
 }
 
-__global__ void __launch_bounds__(1024) scan_partials(int *part, int nparts) {
+// one block per array; the array's sum goes to totals64 as a 64-bit number (an int32 sum can wrap unnoticed)
+__global__ void __launch_bounds__(1024) scan_partials(int *part, int nparts, long long *totals64) {
     __shared__ int sm[33];
-    int carry = 0;
+    int *row = part + (size_t)blockIdx.x * nparts;
+    long long carry = 0;
     for (int base = 0; base < nparts; base += 1024) {
         int i = base + threadIdx.x;
-        int v = i < nparts ? part[i] : 0;
+        int v = i < nparts ? row[i] : 0;
         int total;
         int ex = block_exclusive_scan(v, &total, sm);
-        if (i < nparts) part[i] = ex + carry;
+        if (i < nparts) row[i] = ex + (int)carry;
         carry += total;
     }
+    if (threadIdx.x == 0 && totals64) totals64[blockIdx.x] = carry;
 }
 
-__global__ void __launch_bounds__(SCAN_THREADS) scan_tile_write(const int *in, int *out, int64_t n,
-                                                               const int *__restrict__ part) {
+__global__ void __launch_bounds__(SCAN_THREADS) scan_tile_write(ScanArrays a, int64_t n, int nt, const int *__restrict__ part) {
     __shared__ int sm[33];
+    const int *in = a.in[blockIdx.y];
+    int *out = a.out[blockIdx.y];
     int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
     int v[SCAN_ITEMS];
     int s = 0;
@@ -82,7 +64,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_tile_write(const int *in, i
         v[k] = (base + k < n) ? in[base + k] : 0;
         s += v[k];
     }
-    int ex = block_exclusive_scan(s, nullptr, sm) + part[blockIdx.x];
+    int ex = block_exclusive_scan(s, nullptr, sm) + part[(size_t)blockIdx.y * nt + blockIdx.x];
 #pragma unroll
     for (int k = 0; k < SCAN_ITEMS; k++) {
         if (base + k < n) out[base + k] = ex;
@@ -90,16 +72,35 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_tile_write(const int *in, i
     }
 }
 
+// arrays[k] is scanned in place, k < narr <= 4; totals64 (device, narr entries, may be null) receives the sums
+void exclusive_scan_multi(int *const *arrays, int narr, int64_t n, long long *totals64, cudaStream_t s) {
+    if (n <= 0 || narr <= 0) return;
+    F3M_REQUIRE(narr <= 4, F3M_ERR_INTERNAL, "exclusive_scan_multi takes at most four arrays");
+    const int nt = (int)((n + SCAN_TILE - 1) / SCAN_TILE);
+    ScanArrays a{};
+    for (int k = 0; k < narr; k++) { a.in[k] = arrays[k]; a.out[k] = arrays[k]; }
+    DevBuf<int> part;
+    part.alloc((size_t)nt * narr, s);
+    scan_tile_sums<<<dim3(nt, narr), SCAN_THREADS, 0, s>>>(a, n, nt, part.p);
+    F3M_LAUNCH_CHECK();
+    scan_partials<<<narr, 1024, 0, s>>>(part.p, nt, totals64);
+    F3M_LAUNCH_CHECK();
+    scan_tile_write<<<dim3(nt, narr), SCAN_THREADS, 0, s>>>(a, n, nt, part.p);
+    F3M_LAUNCH_CHECK();
+}
+
 void exclusive_scan_i32(const int *in, int *out, int64_t n, cudaStream_t s) {
     if (n <= 0) return;
-    int nt = (int)((n + SCAN_TILE - 1) / SCAN_TILE);
+    const int nt = (int)((n + SCAN_TILE - 1) / SCAN_TILE);
+    ScanArrays a{};
+    a.in[0] = in; a.out[0] = out;
     DevBuf<int> part;
     part.alloc(nt, s);
-    scan_tile_sums<<<nt, SCAN_THREADS, 0, s>>>(in, n, part.p);
+    scan_tile_sums<<<dim3(nt, 1), SCAN_THREADS, 0, s>>>(a, n, nt, part.p);
     F3M_LAUNCH_CHECK();
-    scan_partials<<<1, 1024, 0, s>>>(part.p, nt);
+    scan_partials<<<1, 1024, 0, s>>>(part.p, nt, nullptr);
     F3M_LAUNCH_CHECK();
-    scan_tile_write<<<nt, SCAN_THREADS, 0, s>>>(in, out, n, part.p);
+    scan_tile_write<<<dim3(nt, 1), SCAN_THREADS, 0, s>>>(a, n, nt, part.p);
     F3M_LAUNCH_CHECK();
 }
 
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(256) bbox_kernel(const float *__restrict__ X, 
 }
 
 void bounding_box(const float *X, int64_t n, int d, float *h_min, float *h_max, f3m_plan *pl, cudaStream_t s) {
-    unsigned *mm = reinterpret_cast<unsigned *>(pl->d_flags) + 16;   // 2*MAXD words
+    unsigned *mm = reinterpret_cast<unsigned *>(pl->d_flags) + FL_BBOX;   // 2*MAXD words
     unsigned init[2 * MAXD];
     for (int k = 0; k < MAXD; k++) { init[k] = 0xffffffffu; init[MAXD + k] = 0u; }
     F3M_CUDA(cudaMemcpyAsync(mm, init, sizeof(init), cudaMemcpyHostToDevice, s));
@@ -188,135 +189,321 @@ __device__ __forceinline__ float div_mode(float a, float b, int ieee) {
     return r;
 }
 
+// ---------------------------------------------------------------------------------------------
+// LSD radix sort of (key, input row, coordinates), least significant digit first, digits of up to 10 bits.
+// Only the key bits the tree will use are sorted (d bits per level).  The coordinates travel with the keys, so the
+// last pass leaves the points in sorted planes and no gather through the permutation is needed; every pass reads
+// and writes its arrays once, in streams (HBM-bound: 8 + 4 d bytes per point read and written).
+//
+// A fixed grid of blocks (one wave: SM count x resident blocks) each owns a contiguous run of tiles.  Per pass:
+// digit histogram per block (the first one is taken while the keys are computed), one scan per digit over the
+// blocks, stable scatter.  The scatter ranks a tile's keys with warp-level match (warp-private counters), stages
+// every array of the tile in shared memory in digit order and writes runs of consecutive addresses.
+// No block waits for another block.
+// ---------------------------------------------------------------------------------------------
+constexpr int RS_T = 256;                 // threads per block
+constexpr int RS_I = 8;                   // keys per thread and tile
+constexpr int RS_W = RS_T / 32;
+constexpr int RS_TILE = RS_T * RS_I;      // 2048 keys
+constexpr int RS_MAXBITS = 10;
+constexpr int RS_MAXBINS = 1 << RS_MAXBITS;
+constexpr int RS_DPT = RS_MAXBINS / RS_T; // digits owned by a thread
+
+struct MortonCfg {
+    float org[MAXD];
+    float side, edge0;
+    int L, ieee;
+};
+
+// keys of a block's chunk and the histogram of their first digit
 template <int D>
-__global__ void __launch_bounds__(256) morton_kernel(const float *__restrict__ X, int64_t n, float side, float edge0,
-                                                    float o0, float o1, float o2, float o3, float o4, int L, int ieee,
-                                                    uint32_t *keys, int *vals) {
-    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const float org[5] = {o0, o1, o2, o3, o4};
-    uint32_t key = 0;
-    const int qmax = (1 << L) - 1;
-#pragma unroll
-    for (int k = 0; k < D; k++) {
-        float t = __fsub_rn(X[i * D + k], org[k]);
-        float v = floorf(div_mode(__fmul_rn(side, t), edge0, ieee));
-        int q = (int)v;
-        q = max(0, min(qmax, q));
-        for (int j = 0; j < L; j++) key |= (uint32_t)((q >> j) & 1) << (D * j + k);
+__global__ void __launch_bounds__(512) morton_hist_kernel(const float *__restrict__ X, int64_t n, MortonCfg cfg, int shift,
+                                                         int dbits, int64_t chunk, uint32_t *keys, int *counts, int G) {
+    __shared__ int hist[RS_MAXBINS];
+    __shared__ uint32_t spread[32];   // bit j of a 5-bit value -> bit D*j
+    for (int q = threadIdx.x; q < RS_MAXBINS; q += blockDim.x) hist[q] = 0;
+    if (threadIdx.x < 32) {
+        uint32_t v = 0;
+        for (int j = 0; j < 5; j++) v |= ((threadIdx.x >> j) & 1u) << (D * j);
+        spread[threadIdx.x] = v;
     }
-    keys[i] = key;
-    vals[i] = (int)i;
+    __syncthreads();
+    const int qmax = (1 << cfg.L) - 1;
+    const uint32_t mask = (1u << dbits) - 1u;
+    const int64_t beg = (int64_t)blockIdx.x * chunk, end = min(n, beg + chunk);
+    constexpr int U = 4;   // points per thread and round: all their loads are issued before the first is used
+    for (int64_t i0 = beg + threadIdx.x; i0 < end; i0 += (int64_t)U * blockDim.x) {
+        float x[U][D];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int64_t i = i0 + (int64_t)u * blockDim.x;
+#pragma unroll
+            for (int k = 0; k < D; k++) x[u][k] = i < end ? X[i * D + k] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int64_t i = i0 + (int64_t)u * blockDim.x;
+            if (i >= end) break;
+            uint32_t key = 0;
+#pragma unroll
+            for (int k = 0; k < D; k++) {
+                float t = __fsub_rn(x[u][k], cfg.org[k]);
+                int q = (int)floorf(div_mode(__fmul_rn(cfg.side, t), cfg.edge0, cfg.ieee));
+                q = max(0, min(qmax, q));
+                uint32_t sk = 0;
+#pragma unroll
+                for (int c = 0; c < 4; c++)   // 5 bits at a time; 20 bits hold the deepest key (d = 1)
+                    if (5 * c < cfg.L) sk |= spread[(q >> (5 * c)) & 31] << (5 * D * c);
+                key |= sk << k;
+            }
+            keys[i] = key;
+            atomicAdd(&hist[(key >> shift) & mask], 1);
+        }
+    }
+    __syncthreads();
+    const int nbins = 1 << dbits;
+    for (int q = threadIdx.x; q < nbins; q += blockDim.x) counts[(size_t)q * G + blockIdx.x] = hist[q];
 }
 
-// ---------------------------------------------------------------------------------------------
-// LSD radix sort, 8 bits per pass.  A fixed grid of blocks (a multiple of the SM count) each owns
-// a contiguous chunk of the input; per pass: per-block digit histogram, one scan over the
-// (digit, block) matrix, stable scatter with warp-level multi-split ranking.
-// ---------------------------------------------------------------------------------------------
-constexpr int RS_THREADS = 256;
-constexpr int RS_ITEMS = 8;
-constexpr int RS_WARPS = RS_THREADS / 32;
-constexpr int RS_TILE = RS_THREADS * RS_ITEMS;
-
-__global__ void __launch_bounds__(RS_THREADS) rs_hist(const uint32_t *__restrict__ keys, int64_t n, int shift,
-                                                     int64_t chunk, int *counts, int G) {
-    __shared__ int h[256];
-    h[threadIdx.x] = 0;
+__global__ void __launch_bounds__(512) rs_hist(const uint32_t *__restrict__ keys, int64_t n, int shift, int dbits, int64_t chunk,
+                                              int *counts, int G) {
+    __shared__ int hist[RS_MAXBINS];
+    for (int q = threadIdx.x; q < RS_MAXBINS; q += blockDim.x) hist[q] = 0;
     __syncthreads();
-    int64_t beg = (int64_t)blockIdx.x * chunk, end = min(n, beg + chunk);
-    for (int64_t i = beg + threadIdx.x; i < end; i += RS_THREADS) atomicAdd(&h[(keys[i] >> shift) & 255], 1);
+    const uint32_t mask = (1u << dbits) - 1u;
+    const int64_t beg = (int64_t)blockIdx.x * chunk, end = min(n, beg + chunk);
+    for (int64_t i = beg + threadIdx.x; i < end; i += blockDim.x) atomicAdd(&hist[(keys[i] >> shift) & mask], 1);
     __syncthreads();
-    counts[threadIdx.x * G + blockIdx.x] = h[threadIdx.x];
+    const int nbins = 1 << dbits;
+    for (int q = threadIdx.x; q < nbins; q += blockDim.x) counts[(size_t)q * G + blockIdx.x] = hist[q];
 }
 
-// Stable scatter of one pass.  Keys of a tile are first ranked (warp-level multi-split), then staged in
-// shared memory in digit order, so that the global writes of a tile are runs of consecutive addresses
-// per digit instead of 4-byte scatters.
-__global__ void __launch_bounds__(RS_THREADS) rs_scatter(const uint32_t *__restrict__ keys, const int *__restrict__ vals,
-                                                        int64_t n, int shift, int64_t chunk,
-                                                        const int *__restrict__ scanned, int G, uint32_t *okeys,
-                                                        int *ovals) {
-    __shared__ int base[256];              // next global position per digit for this block
-    __shared__ int dstart[256];            // start of the digit inside the staged tile
-    __shared__ int wcnt[RS_WARPS][256];    // per-warp digit counts, then per-warp bases
-    __shared__ uint32_t skeys[RS_TILE];
-    __shared__ int svals[RS_TILE];
+// one block per digit: exclusive scan of the digit's counts over the blocks, and the digit's total
+__global__ void __launch_bounds__(256) rs_scan_rows(int *counts, int G, int *tot) {
+    __shared__ int sm[33];
+    int *row = counts + (size_t)blockIdx.x * G;
+    int carry = 0;
+    for (int base = 0; base < G; base += 256) {
+        const int i = base + threadIdx.x;
+        const int v = i < G ? row[i] : 0;
+        int total;
+        const int ex = block_exclusive_scan(v, &total, sm);
+        if (i < G) row[i] = ex + carry;
+        carry += total;
+    }
+    if (threadIdx.x == 0) tot[blockIdx.x] = carry;
+}
+
+// Words of the record that travels with a key: [input row, x_0 .. x_{D-1}], padded so that it moves as 8- or
+// 16-byte vectors.
+template <int D> struct Rec { static constexpr int VW = 2, RV = (D + 2) / 2; };   // D = 1: 1 x 8 B; D = 4, 5: 3 x 8 B
+template <> struct Rec<2> { static constexpr int VW = 4, RV = 1; };                // 16 B
+template <> struct Rec<3> { static constexpr int VW = 4, RV = 1; };                // 16 B
+template <int VW> struct VecOf;
+template <> struct VecOf<2> { typedef uint2 type; };
+template <> struct VecOf<4> { typedef uint4 type; };
+
+struct SortIO {
+    const uint32_t *kin;       // keys of this pass's input order
+    const float *X;            // first pass: the caller's row-major points (the record is built from them)
+    const void *rin;           // later passes: records of the input order
+    uint32_t *kout;
+    void *rout;                // records of the output order
+    int first;
+};
+
+__host__ __device__ constexpr size_t rs_smem_bytes(int nbins, int rec_words) {
+    // per-warp counters (u16), gofs + bbase (int), staged keys, staged records
+    return (size_t)RS_W * nbins * 2 + (size_t)2 * nbins * 4 + (size_t)RS_TILE * 4 + (size_t)RS_TILE * rec_words * 4;
+}
+
+// STABLE = false: the rank of a key among the tile's keys of its digit is whatever order the shared-memory atomics
+// grant.  That is enough for the FIRST pass (nothing is ordered yet: points that agree in every sorted bit lie in
+// one finest-level box, where their order does not matter); every later pass must keep the order of its input.
+template <int D, bool STABLE>
+__global__ void __launch_bounds__(RS_T, 3) rs_scatter(SortIO io, int64_t n, int shift, int dbits, int64_t chunk,
+                                                  const int *__restrict__ rowex, const int *__restrict__ tot, int G) {
+    constexpr int VW = Rec<D>::VW, RV = Rec<D>::RV, RW = VW * RV;
+    typedef typename VecOf<VW>::type vec_t;
+    extern __shared__ __align__(16) unsigned char rs_smem[];
     __shared__ int scan_sm[33];
+    const int nbins = 1 << dbits;
+    vec_t *stage_rec = reinterpret_cast<vec_t *>(rs_smem);                                  // [RS_TILE][RV]
+    uint32_t *stage_key = reinterpret_cast<uint32_t *>(rs_smem + (size_t)RS_TILE * RW * 4);   // [RS_TILE]
+    int *gofs = reinterpret_cast<int *>(stage_key + RS_TILE);   // global position of staged slot q of digit g: gofs[g] + q
+    int *bbase = gofs + nbins;                                  // next global position per digit for this block
+    unsigned short *wcnt = reinterpret_cast<unsigned short *>(bbase + nbins);   // [RS_W][nbins] counts, then start slots
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    base[threadIdx.x] = scanned[threadIdx.x * G + blockIdx.x];
-    for (int q = 0; q < RS_WARPS; q++) wcnt[q][threadIdx.x] = 0;
+    const uint32_t mask = (uint32_t)nbins - 1u;
+    unsigned short *wrow = wcnt + (size_t)w * nbins;
+    // digits [d0, d0 + dpt) belong to this thread (none when the block has more threads than digits)
+    const int dpt = (nbins + RS_T - 1) / RS_T;
+    const int d0 = threadIdx.x * dpt;
+    const bool owner = d0 < nbins;
+    {
+        int t[RS_DPT], sum = 0;
+#pragma unroll
+        for (int q = 0; q < RS_DPT; q++) {
+            t[q] = (q < dpt && owner) ? tot[d0 + q] : 0;
+            sum += t[q];
+        }
+        int ex = block_exclusive_scan(sum, nullptr, scan_sm);
+#pragma unroll
+        for (int q = 0; q < RS_DPT; q++) {
+            if (q < dpt && owner) {
+                bbase[d0 + q] = ex + rowex[(size_t)(d0 + q) * G + blockIdx.x];
+                ex += t[q];
+                for (int ww = 0; ww < RS_W; ww++) wcnt[(size_t)ww * nbins + d0 + q] = 0;
+                gofs[d0 + q] = 0;
+            }
+        }
+    }
     __syncthreads();
-    int64_t beg = (int64_t)blockIdx.x * chunk, end = min(n, beg + chunk);
+    const int64_t beg = (int64_t)blockIdx.x * chunk, end = min(n, beg + chunk);
     for (int64_t tile = beg; tile < end; tile += RS_TILE) {
         const int tile_cnt = (int)min((int64_t)RS_TILE, end - tile);
-        uint32_t k[RS_ITEMS];
-        int v[RS_ITEMS], off[RS_ITEMS];
+        const int j0 = w * (32 * RS_I) + lane;   // item r of this lane: point tile + j0 + 32 r
+        const uint32_t *__restrict__ kin = io.kin + tile;
+        uint32_t key[RS_I];
+        vec_t rec[RS_I][RV];
+        int sp[RS_I];
 #pragma unroll
-        for (int r = 0; r < RS_ITEMS; r++) {
-            int64_t i = tile + (int64_t)w * (32 * RS_ITEMS) + r * 32 + lane;
-            bool valid = i < end;
-            k[r] = valid ? keys[i] : 0u;
-            v[r] = valid ? vals[i] : 0;
-            int dg = valid ? (int)((k[r] >> shift) & 255) : 256;
-            unsigned m = __match_any_sync(0xffffffffu, dg);
-            int leader = __ffs(m) - 1;
-            int rank = __popc(m & ((1u << lane) - 1));
-            int old = 0;
-            if (lane == leader && valid) {
-                old = wcnt[w][dg];
-                wcnt[w][dg] = old + __popc(m);
+        for (int r = 0; r < RS_I; r++) key[r] = (j0 + 32 * r < tile_cnt) ? kin[j0 + 32 * r] : 0u;
+        if (io.first) {
+            const float *__restrict__ xin = io.X + tile * D;
+#pragma unroll
+            for (int r = 0; r < RS_I; r++) {
+                const int j = j0 + 32 * r;
+                uint32_t wds[RW];
+#pragma unroll
+                for (int q = 0; q < RW; q++) wds[q] = 0u;
+                if (j < tile_cnt) {
+                    wds[0] = (uint32_t)(tile + j);
+#pragma unroll
+                    for (int k = 0; k < D; k++) wds[1 + k] = __float_as_uint(xin[j * D + k]);
+                }
+#pragma unroll
+                for (int v = 0; v < RV; v++) {
+                    if (VW == 4) rec[r][v] = *reinterpret_cast<vec_t *>(&wds[4 * v]);
+                    else { uint2 t2 = make_uint2(wds[2 * v], wds[2 * v + 1]); rec[r][v] = *reinterpret_cast<vec_t *>(&t2); }
+                }
             }
-            old = __shfl_sync(m, old, leader);
-            off[r] = valid ? old + rank : -1;
-            __syncwarp();
+        } else {
+            const vec_t *__restrict__ rin = reinterpret_cast<const vec_t *>(io.rin) + tile * RV;
+#pragma unroll
+            for (int r = 0; r < RS_I; r++) {
+                const int j = j0 + 32 * r;
+#pragma unroll
+                for (int v = 0; v < RV; v++)
+                    if (j < tile_cnt) rec[r][v] = rin[j * RV + v];
+            }
+        }
+        if (STABLE) {
+            // rank inside the warp: items in (r, lane) order = input order.  The lanes that hold the same digit are
+            // found with one ballot per digit bit (the match instruction costs a step per distinct value, and nearly
+            // all 32 digits of a warp are distinct).
+#pragma unroll
+            for (int r = 0; r < RS_I; r++) {
+                const bool valid = j0 + 32 * r < tile_cnt;
+                const int dg = (int)((key[r] >> shift) & mask);
+                unsigned m = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+                for (int bit = 0; bit < RS_MAXBITS; bit++) {
+                    if (bit < dbits) {
+                        const unsigned bal = __ballot_sync(0xffffffffu, (dg >> bit) & 1);
+                        m &= ((dg >> bit) & 1) ? bal : ~bal;
+                    }
+                }
+                // m: valid lanes with this lane's digit (meaningless on invalid lanes, which take no part)
+                const int leader = __ffs(m) - 1;
+                int old = 0;
+                if (valid && lane == leader) {
+                    old = wrow[dg];
+                    wrow[dg] = (unsigned short)(old + __popc(m));
+                }
+                old = __shfl_sync(0xffffffffu, old, valid ? leader : lane);
+                sp[r] = valid ? old + __popc(m & ((1u << lane) - 1u)) : -1;
+                __syncwarp();
+            }
+        } else {
+            // one counter per digit for the whole tile (kept in gofs until the scan below replaces it)
+#pragma unroll
+            for (int r = 0; r < RS_I; r++)
+                sp[r] = (j0 + 32 * r < tile_cnt) ? atomicAdd(&gofs[(key[r] >> shift) & mask], 1) : -1;
         }
         __syncthreads();
-        int tile_total;
+        // per digit: start slot in the staged tile (per warp in the stable form), global position of slot 0
+        int tsum[RS_DPT];
         {
-            int run = 0;
+            int sum = 0;
 #pragma unroll
-            for (int q = 0; q < RS_WARPS; q++) {
-                int c = wcnt[q][threadIdx.x];
-                wcnt[q][threadIdx.x] = run;
-                run += c;
+            for (int q = 0; q < RS_DPT; q++) {
+                int run = 0;
+                if (q < dpt && owner) {
+                    if (STABLE) for (int ww = 0; ww < RS_W; ww++) run += wcnt[(size_t)ww * nbins + d0 + q];
+                    else run = gofs[d0 + q];
+                }
+                tsum[q] = run;
+                sum += run;
             }
-            tile_total = run;
+            int ex = block_exclusive_scan(sum, nullptr, scan_sm);
+#pragma unroll
+            for (int q = 0; q < RS_DPT; q++) {
+                if (q < dpt && owner) {
+                    gofs[d0 + q] = bbase[d0 + q] - ex;
+                    if (STABLE) {
+                        int run = ex;
+                        for (int ww = 0; ww < RS_W; ww++) {
+                            const int c = wcnt[(size_t)ww * nbins + d0 + q];
+                            wcnt[(size_t)ww * nbins + d0 + q] = (unsigned short)run;
+                            run += c;
+                        }
+                    } else
+                        wcnt[d0 + q] = (unsigned short)ex;   // row 0 holds the start slots
+                    ex += tsum[q];
+                }
+            }
         }
-        dstart[threadIdx.x] = block_exclusive_scan(tile_total, nullptr, scan_sm);   // ends with a barrier
         __syncthreads();
 #pragma unroll
-        for (int r = 0; r < RS_ITEMS; r++) {
-            if (off[r] >= 0) {
-                int dg = (k[r] >> shift) & 255;
-                int sp = dstart[dg] + wcnt[w][dg] + off[r];
-                skeys[sp] = k[r];
-                svals[sp] = v[r];
+        for (int r = 0; r < RS_I; r++) {
+            if (sp[r] >= 0) {
+                const int slot = sp[r] + (STABLE ? wrow : wcnt)[(key[r] >> shift) & mask];
+                stage_key[slot] = key[r];
+#pragma unroll
+                for (int v = 0; v < RV; v++) stage_rec[slot * RV + v] = rec[r][v];
             }
         }
         __syncthreads();
-        for (int q = threadIdx.x; q < tile_cnt; q += RS_THREADS) {
-            uint32_t kk = skeys[q];
-            int dg = (kk >> shift) & 255;
-            int64_t pos = (int64_t)base[dg] + (q - dstart[dg]);
-            okeys[pos] = kk;
-            ovals[pos] = svals[q];
+        // positions of the staged slots (runs of consecutive global positions per digit); then the counters are
+        // cleared for the next tile and the block's positions advance
+        int pos[RS_I];
+#pragma unroll
+        for (int k = 0; k < RS_I; k++) {
+            const int q = threadIdx.x + k * RS_T;
+            pos[k] = q < tile_cnt ? gofs[(stage_key[q] >> shift) & mask] + q : -1;
         }
-        __syncthreads();
-        base[threadIdx.x] += tile_total;
-        for (int q = 0; q < RS_WARPS; q++) wcnt[q][threadIdx.x] = 0;
+        if (!STABLE) __syncthreads();   // gofs is cleared below: every thread must have read it
+#pragma unroll
+        for (int q = 0; q < RS_DPT; q++) {
+            if (q < dpt && owner) {
+                bbase[d0 + q] += tsum[q];
+                if (STABLE) for (int ww = 0; ww < RS_W; ww++) wcnt[(size_t)ww * nbins + d0 + q] = 0;
+                else gofs[d0 + q] = 0;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < RS_I; k++) {
+            if (pos[k] >= 0) {
+                const int q = threadIdx.x + k * RS_T;
+                io.kout[pos[k]] = stage_key[q];
+                vec_t *rout = reinterpret_cast<vec_t *>(io.rout) + (size_t)pos[k] * RV;
+#pragma unroll
+                for (int v = 0; v < RV; v++) rout[v] = stage_rec[q * RV + v];
+            }
+        }
         __syncthreads();
     }
-}
-
-template <int D>
-__global__ void __launch_bounds__(256) gather_points(const float *__restrict__ X, const int *__restrict__ perm, int64_t n,
-                                                    float *pts) {
-    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    int64_t src = perm[i];
-#pragma unroll
-    for (int k = 0; k < D; k++) pts[(int64_t)k * n + i] = X[src * D + k];
 }
 
 __global__ void __launch_bounds__(256) gather_rows_kernel(const float *__restrict__ src, const int *__restrict__ perm,
@@ -366,9 +553,85 @@ void scatter_rows(const float *src, const int *perm, float *dst, int64_t n, int 
     F3M_LAUNCH_CHECK();
 }
 
-void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *origin, float edge0, int math_mode,
-                       f3m_plan *pl, cudaStream_t s) {
-    (void)pl;
+// records [input row, x_0 .. x_{D-1}] of the sorted order -> permutation and coordinate planes
+template <int D>
+__global__ void __launch_bounds__(256) unpack_records(const void *__restrict__ recs, int64_t n, int *perm, float *pts) {
+    constexpr int VW = Rec<D>::VW, RV = Rec<D>::RV, RW = VW * RV;
+    typedef typename VecOf<VW>::type vec_t;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint32_t wds[RW];
+#pragma unroll
+    for (int v = 0; v < RV; v++) {
+        const vec_t t = reinterpret_cast<const vec_t *>(recs)[i * RV + v];
+        const uint32_t *tw = reinterpret_cast<const uint32_t *>(&t);
+#pragma unroll
+        for (int c = 0; c < VW; c++) wds[VW * v + c] = tw[c];
+    }
+    perm[i] = (int)wds[0];
+#pragma unroll
+    for (int c = 0; c < D; c++) pts[(size_t)c * n + i] = __uint_as_float(wds[1 + c]);
+}
+
+template <int D>
+static void sort_passes(Tree &t, const float *X, const MortonCfg &cfg, int shift0, int bits, cudaStream_t s) {
+    constexpr int RW = Rec<D>::VW * Rec<D>::RV;
+    const int64_t n = t.n;
+    const int passes = (bits + RS_MAXBITS - 1) / RS_MAXBITS;
+    const int dbits_all = (bits + passes - 1) / passes;
+    const size_t smem = rs_smem_bytes(1 << dbits_all, RW);
+    // one wave of blocks, each with a contiguous run of whole tiles
+    int dev = 0, sms = NUM_SMS_HINT, occ = 1;
+    F3M_CUDA(cudaGetDevice(&dev));
+    F3M_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    F3M_CUDA(cudaFuncSetAttribute(rs_scatter<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    F3M_CUDA(cudaFuncSetAttribute(rs_scatter<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    F3M_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, rs_scatter<D, true>, RS_T, smem));
+    const int64_t ntiles = (n + RS_TILE - 1) / RS_TILE;
+    const int64_t wave = (int64_t)sms * std::max(1, occ);
+    const int64_t tpb = (ntiles + wave - 1) / wave;
+    const int G = (int)((ntiles + tpb - 1) / tpb);
+    const int64_t chunk = tpb * RS_TILE;
+
+    DevBuf<uint32_t> kA, kB, rA, rB;   // keys and records, ping-pong
+    DevBuf<int> counts, tot;
+    kA.alloc(n, s); kB.alloc(n, s);
+    rB.alloc((size_t)n * RW, s);
+    if (passes > 1) rA.alloc((size_t)n * RW, s);
+    t.perm.alloc(n, s);
+    t.pts.alloc((size_t)n * D, s);
+    counts.alloc((size_t)RS_MAXBINS * G, s);
+    tot.alloc(RS_MAXBINS, s);
+
+    for (int pass = 0; pass < passes; pass++) {
+        const int shift = shift0 + pass * dbits_all;
+        const int dbits = std::min(dbits_all, shift0 + bits - shift);
+        const bool to_b = (pass % 2) == 0;
+        if (pass == 0) morton_hist_kernel<D><<<G, 512, 0, s>>>(X, n, cfg, shift, dbits, chunk, kA.p, counts.p, G);
+        else rs_hist<<<G, 512, 0, s>>>(to_b ? kA.p : kB.p, n, shift, dbits, chunk, counts.p, G);
+        F3M_LAUNCH_CHECK();
+        rs_scan_rows<<<1 << dbits, 256, 0, s>>>(counts.p, G, tot.p);
+        F3M_LAUNCH_CHECK();
+        SortIO io{};
+        io.first = pass == 0;
+        io.kin = to_b ? kA.p : kB.p;
+        io.kout = to_b ? kB.p : kA.p;
+        io.X = X;
+        io.rin = to_b ? rA.p : rB.p;
+        io.rout = to_b ? rB.p : rA.p;
+        if (pass == 0) rs_scatter<D, false><<<G, RS_T, rs_smem_bytes(1 << dbits, RW), s>>>(io, n, shift, dbits, chunk, counts.p, tot.p, G);
+        else rs_scatter<D, true><<<G, RS_T, rs_smem_bytes(1 << dbits, RW), s>>>(io, n, shift, dbits, chunk, counts.p, tot.p, G);
+        F3M_LAUNCH_CHECK();
+    }
+    unpack_records<D><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(passes % 2 == 1 ? rB.p : rA.p, n, t.perm.p, t.pts.p);
+    F3M_LAUNCH_CHECK();
+    t.keys = std::move(passes % 2 == 1 ? kB : kA);
+}
+
+// Sorts the points of one tree by the first `depth` levels of their Morton key (all later levels are read off the
+// sorted keys, tree.cu) and leaves keys, permutation and coordinate planes in the tree.
+void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *origin, float edge0, int math_mode, int depth,
+                       cudaStream_t s) {
     F3M_REQUIRE(n < (int64_t)0x7fffffff, F3M_ERR_OVERFLOW, "point count %lld does not fit a 31-bit index", (long long)n);
     t.n = n;
     t.d = d;
@@ -377,54 +640,23 @@ void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *o
     for (int k = 0; k < d; k++) t.origin[k] = origin[k];
     // deepest level a 30-bit cell index holds (the reference's int cell index overflows beyond that)
     t.lmax = std::min(30 / d, 20);
-    const int L = t.lmax;
-    const int bits = d * L;
-    DevBuf<uint32_t> k0, k1;
-    DevBuf<int> v0, v1;
-    k0.alloc(n, s); k1.alloc(n, s); v0.alloc(n, s); v1.alloc(n, s);
-    const float side = (float)(1u << L);
-    unsigned grid = (unsigned)((n + 255) / 256);
-    const float *o = t.origin;
-    const int ieee = math_mode == F3M_MATH_IEEE;
+    depth = std::max(1, std::min(depth, t.lmax));
+    t.sorted_depth = depth;
+    t.keys.release(); t.perm.release(); t.pts.release();   // a second sort (deeper) replaces the first
+    MortonCfg cfg{};
+    for (int k = 0; k < d; k++) cfg.org[k] = origin[k];
+    cfg.side = (float)(1u << t.lmax);
+    cfg.edge0 = edge0;
+    cfg.L = t.lmax;
+    cfg.ieee = math_mode == F3M_MATH_IEEE;
+    const int shift0 = d * (t.lmax - depth), bits = d * depth;
     switch (d) {
-        case 1: morton_kernel<1><<<grid, 256, 0, s>>>(X, n, side, edge0, o[0], o[1], o[2], o[3], o[4], L, ieee, k0.p, v0.p); break;
-        case 2: morton_kernel<2><<<grid, 256, 0, s>>>(X, n, side, edge0, o[0], o[1], o[2], o[3], o[4], L, ieee, k0.p, v0.p); break;
-        case 3: morton_kernel<3><<<grid, 256, 0, s>>>(X, n, side, edge0, o[0], o[1], o[2], o[3], o[4], L, ieee, k0.p, v0.p); break;
-        case 4: morton_kernel<4><<<grid, 256, 0, s>>>(X, n, side, edge0, o[0], o[1], o[2], o[3], o[4], L, ieee, k0.p, v0.p); break;
-        default: morton_kernel<5><<<grid, 256, 0, s>>>(X, n, side, edge0, o[0], o[1], o[2], o[3], o[4], L, ieee, k0.p, v0.p); break;
+        case 1: sort_passes<1>(t, X, cfg, shift0, bits, s); break;
+        case 2: sort_passes<2>(t, X, cfg, shift0, bits, s); break;
+        case 3: sort_passes<3>(t, X, cfg, shift0, bits, s); break;
+        case 4: sort_passes<4>(t, X, cfg, shift0, bits, s); break;
+        default: sort_passes<5>(t, X, cfg, shift0, bits, s); break;
     }
-    F3M_LAUNCH_CHECK();
-
-    int G = (int)std::min<int64_t>((n + RS_TILE - 1) / RS_TILE, NUM_SMS_HINT * 10);
-    if (G < 1) G = 1;
-    int64_t chunk = (n + G - 1) / G;
-    chunk = (chunk + RS_TILE - 1) / RS_TILE * RS_TILE;
-    DevBuf<int> counts;
-    counts.alloc((size_t)256 * G + 1, s);
-    uint32_t *ka = k0.p, *kb = k1.p;
-    int *va = v0.p, *vb = v1.p;
-    bool in_first = true;
-    for (int shift = 0; shift < bits; shift += 8) {
-        rs_hist<<<G, RS_THREADS, 0, s>>>(ka, n, shift, chunk, counts.p, G);
-        F3M_LAUNCH_CHECK();
-        exclusive_scan_i32(counts.p, counts.p, (int64_t)256 * G, s);
-        rs_scatter<<<G, RS_THREADS, 0, s>>>(ka, va, n, shift, chunk, counts.p, G, kb, vb);
-        F3M_LAUNCH_CHECK();
-        std::swap(ka, kb);
-        std::swap(va, vb);
-        in_first = !in_first;
-    }
-    if (in_first) { t.keys = std::move(k0); t.perm = std::move(v0); }
-    else { t.keys = std::move(k1); t.perm = std::move(v1); }
-    t.pts.alloc((size_t)n * d, s);
-    switch (d) {
-        case 1: gather_points<1><<<grid, 256, 0, s>>>(X, t.perm.p, n, t.pts.p); break;
-        case 2: gather_points<2><<<grid, 256, 0, s>>>(X, t.perm.p, n, t.pts.p); break;
-        case 3: gather_points<3><<<grid, 256, 0, s>>>(X, t.perm.p, n, t.pts.p); break;
-        case 4: gather_points<4><<<grid, 256, 0, s>>>(X, t.perm.p, n, t.pts.p); break;
-        default: gather_points<5><<<grid, 256, 0, s>>>(X, t.perm.p, n, t.pts.p); break;
-    }
-    F3M_LAUNCH_CHECK();
 }
 
 }  // namespace f3m

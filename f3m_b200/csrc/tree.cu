@@ -7,92 +7,141 @@
 // one warp per target box walks its parent's row, classifies the child pairs in registers and writes
 // the three lists directly as CSR rows (count pass, scan, write pass).  Box ids are dense ranks, so
 // no hash table is needed anywhere.
+#include <algorithm>
 #include "common.cuh"
 
 namespace f3m {
 
 // ---------------------------------------------------------------------------------------------
-// boxes of one level = runs of equal key prefix in the sorted key array
+// Boxes of a level = runs of equal key prefix in the sorted key array.  A point starts a box at level l and at
+// every deeper level when its key differs from its predecessor's in a bit of level l or above, so ONE pass over
+// the keys finds the box starts of a whole batch of levels: count per tile and level, scan per level over the
+// tiles, write offsets and prefixes.
 // ---------------------------------------------------------------------------------------------
 constexpr int HT = 256, HI = 8, HTILE = HT * HI;
+constexpr int HB = 8;   // levels per batch
 
-__device__ __forceinline__ int block_scan_excl(int v, int *total, int *sm) {
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    int inc = v;
+// coarsest level at which point i starts a box (lmax + 1: at none of the levels the key holds)
+__device__ __forceinline__ int first_head_level(uint32_t key, uint32_t prev, bool first, int d, int lmax) {
+    if (first) return 1;
+    const uint32_t x = key ^ prev;
+    if (!x) return lmax + 1;
+    // bit h belongs to the d-bit group of level lmax - h / d; h < 32 and d <= 5, so h / d = (h * ceil(2^16 / d)) >> 16
+    const int h = 31 - __clz(x);
+    return lmax - ((h * ((65536 + d - 1) / d)) >> 16);
+}
+
+// the HI consecutive keys of a thread and the one before them
+__device__ __forceinline__ void load_head_levels(const uint32_t *__restrict__ keys, int64_t n, int64_t base, int d, int lmax,
+                                                 int (&l0)[8]) {
+    uint32_t k[9];
+    k[0] = (base > 0 && base - 1 < n) ? keys[base - 1] : 0u;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        int t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += t;
-    }
-    if (lane == 31) sm[wid] = inc;
+    for (int q = 0; q < 8; q++) k[q + 1] = (base + q < n) ? keys[base + q] : 0u;
+#pragma unroll
+    for (int q = 0; q < 8; q++) l0[q] = (base + q < n) ? first_head_level(k[q + 1], k[q], base + q == 0, d, lmax) : lmax + 1;
+}
+
+// part[v * nt + tile] = boxes of level l_first + v that start inside the tile
+__global__ void __launch_bounds__(HT) heads_count(const uint32_t *__restrict__ keys, int64_t n, int d, int lmax, int l_first,
+                                                 int nlev, int nt, int *part) {
+    __shared__ int tot[HB];
+    if (threadIdx.x < HB) tot[threadIdx.x] = 0;
     __syncthreads();
-    if (wid == 0) {
-        int w = lane < nw ? sm[lane] : 0, winc = w;
+    const int64_t base = (int64_t)blockIdx.x * HTILE + (int64_t)threadIdx.x * HI;
+    int l0[HI], c[HB];
+    load_head_levels(keys, n, base, d, lmax, l0);
+    int deepest = lmax + 1;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            int t = __shfl_up_sync(0xffffffffu, winc, o);
-            if (lane >= o) winc += t;
+    for (int k = 0; k < HI; k++) deepest = min(deepest, l0[k]);
+    // most warps hold no box start at any level of the batch (a box has hundreds of points)
+    if (!__any_sync(0xffffffffu, deepest <= l_first + nlev - 1)) deepest = lmax + 1;
+#pragma unroll
+    for (int v = 0; v < HB; v++) c[v] = 0;
+    if (deepest <= l_first + nlev - 1) {
+#pragma unroll
+        for (int k = 0; k < HI; k++)
+#pragma unroll
+            for (int v = 0; v < HB; v++) c[v] += (l0[k] <= l_first + v);
+    }
+#pragma unroll
+    for (int v = 0; v < HB; v++) {
+        if (v < nlev && __any_sync(0xffffffffu, c[v] > 0)) {
+            int x = c[v];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+            if ((threadIdx.x & 31) == 0 && x) atomicAdd(&tot[v], x);
         }
-        sm[lane] = winc - w;
-        if (lane == 31) sm[32] = winc;
     }
     __syncthreads();
-    int r = sm[wid] + inc - v;
-    if (total) *total = sm[32];
-    __syncthreads();
-    return r;
+    if (threadIdx.x < nlev) part[(size_t)threadIdx.x * nt + blockIdx.x] = tot[threadIdx.x];
 }
 
-__device__ __forceinline__ bool is_head(const uint32_t *keys, int64_t i, int shift) {
-    return i == 0 || (keys[i] >> shift) != (keys[i - 1] >> shift);
-}
-
-__global__ void __launch_bounds__(HT) head_count(const uint32_t *__restrict__ keys, int64_t n, int shift, int *part) {
+// one block per level of the batch: exclusive scan of the level's tile counts, total -> totals[level]
+__global__ void __launch_bounds__(1024) heads_scan(int *part, int nt, int *totals) {
     __shared__ int sm[33];
-    int64_t base = (int64_t)blockIdx.x * HTILE + (int64_t)threadIdx.x * HI;
-    int c = 0;
-#pragma unroll
-    for (int k = 0; k < HI; k++)
-        if (base + k < n) c += is_head(keys, base + k, shift);
-    int total;
-    block_scan_excl(c, &total, sm);
-    if (threadIdx.x == 0) part[blockIdx.x] = total;
-}
-
-__global__ void scan_partials_total(int *part, int nparts, int *total_out) {
-    __shared__ int sm[33];
+    int *row = part + (size_t)blockIdx.x * nt;
     int carry = 0;
-    for (int base = 0; base < nparts; base += blockDim.x) {
-        int i = base + threadIdx.x;
-        int v = i < nparts ? part[i] : 0;
+    for (int base = 0; base < nt; base += 1024) {
+        const int i = base + threadIdx.x;
+        const int v = i < nt ? row[i] : 0;
         int total;
-        int ex = block_scan_excl(v, &total, sm);
-        if (i < nparts) part[i] = ex + carry;
+        const int ex = block_exclusive_scan(v, &total, sm);
+        if (i < nt) row[i] = ex + carry;
         carry += total;
     }
-    if (threadIdx.x == 0) *total_out = carry;
+    if (threadIdx.x == 0) totals[blockIdx.x] = carry;
 }
 
-__global__ void __launch_bounds__(HT) head_write(const uint32_t *__restrict__ keys, int64_t n, int shift,
-                                                const int *__restrict__ part, int *off, uint32_t *code, int nb) {
-    __shared__ int sm[33];
-    int64_t base = (int64_t)blockIdx.x * HTILE + (int64_t)threadIdx.x * HI;
-    bool h[HI];
-    int c = 0;
+struct HeadsOut {
+    int *off[HB];
+    uint32_t *code[HB];
+    int nb[HB];
+};
+
+__global__ void __launch_bounds__(HT) heads_write(const uint32_t *__restrict__ keys, int64_t n, int d, int lmax, int l_first,
+                                                 int nlev, int nt, const int *__restrict__ part, HeadsOut out) {
+    __shared__ int wtot[HB][HT / 32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int64_t base = (int64_t)blockIdx.x * HTILE + (int64_t)threadIdx.x * HI;
+    int l0[HI], c[HB];
+    load_head_levels(keys, n, base, d, lmax, l0);
 #pragma unroll
-    for (int k = 0; k < HI; k++) {
-        h[k] = (base + k < n) && is_head(keys, base + k, shift);
-        c += h[k];
-    }
-    int r = block_scan_excl(c, nullptr, sm) + part[blockIdx.x];
+    for (int v = 0; v < HB; v++) c[v] = 0;
 #pragma unroll
     for (int k = 0; k < HI; k++)
-        if (h[k]) {
-            off[r] = (int)(base + k);
-            code[r] = keys[base + k] >> shift;
-            r++;
+#pragma unroll
+        for (int v = 0; v < HB; v++) c[v] += (l0[k] <= l_first + v);
+    int ex[HB];   // boxes of the level that start before this thread's keys, inside the warp
+#pragma unroll
+    for (int v = 0; v < HB; v++) {
+        int inc = c[v];
+        if (v < nlev && __any_sync(0xffffffffu, inc > 0)) {   // warp-uniform: most warps hold no box start
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += t;
+            }
         }
-    if (blockIdx.x == 0 && threadIdx.x == 0) off[nb] = (int)n;
+        ex[v] = inc - c[v];
+        if (lane == 31) wtot[v][w] = inc;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int v = 0; v < HB; v++) {
+        if (v >= nlev || c[v] == 0) continue;
+        int r = part[(size_t)v * nt + blockIdx.x] + ex[v];
+        for (int ww = 0; ww < w; ww++) r += wtot[v][ww];
+        const int shift = d * (lmax - (l_first + v));
+#pragma unroll
+        for (int k = 0; k < HI; k++)
+            if (l0[k] <= l_first + v) {
+                out.off[v][r] = (int)(base + k);
+                out.code[v][r] = keys[base + k] >> shift;
+                r++;
+            }
+        if (blockIdx.x == 0 && threadIdx.x == 0) out.off[v][out.nb[v]] = (int)n;
+    }
 }
 
 template <int D>
@@ -158,49 +207,61 @@ void build_root(Tree &t, cudaStream_t s) {
     F3M_CUDA(cudaStreamSynchronize(s));   // host arrays above go out of scope
 }
 
-void build_next_level(Tree &t, f3m_plan *pl, cudaStream_t s) {
-    const int lvl = (int)t.levels.size();
-    F3M_REQUIRE(lvl <= t.lmax, F3M_ERR_DEPTH,
-                "tree needs level %d but a 30-bit cell index holds %d levels in %d dimensions", lvl, t.lmax, t.d);
-    const int shift = t.d * (t.lmax - lvl);
+// Appends the levels after the last one built, up to l_last, in batches of HB levels: two host synchronisations
+// per batch (box counts before the arrays are sized, largest boxes after the links).
+void build_levels(Tree &t, int l_last, f3m_plan *pl, cudaStream_t s) {
+    F3M_REQUIRE(l_last <= t.sorted_depth, F3M_ERR_INTERNAL, "level %d requested, keys are sorted to level %d", l_last, t.sorted_depth);
     const int64_t n = t.n;
-    int nt = (int)((n + HTILE - 1) / HTILE);
-    DevBuf<int> part;
-    part.alloc(nt, s);
-    int *d_total = pl->d_flags + 1, *d_max = pl->d_flags + 2, *d_err = pl->d_flags + 0;
-    head_count<<<nt, HT, 0, s>>>(t.keys.p, n, shift, part.p);
-    F3M_LAUNCH_CHECK();
-    scan_partials_total<<<1, 1024, 0, s>>>(part.p, nt, d_total);
-    F3M_LAUNCH_CHECK();
-    F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, d_total, sizeof(int), cudaMemcpyDeviceToHost, s));
-    F3M_CUDA(cudaStreamSynchronize(s));
-    const int nb = pl->h_pinned[0];
-    t.levels.emplace_back();
-    Level &L = t.levels[lvl];
-    Level &P = t.levels[lvl - 1];
-    L.nb = nb;
-    L.edge = P.edge * 0.5f;
-    L.off.alloc((size_t)nb + 1, s); L.code.alloc(nb, s); L.parent.alloc(nb, s); L.ctr.alloc((size_t)nb * t.d, s);
-    head_write<<<nt, HT, 0, s>>>(t.keys.p, n, shift, part.p, L.off.p, L.code.p, nb);
-    F3M_LAUNCH_CHECK();
-    F3M_CUDA(cudaMemsetAsync(d_max, 0, sizeof(int), s));
-    const float q = 0.25f * P.edge;
-    unsigned g = (unsigned)((nb + 255) / 256);
-    switch (t.d) {
-        case 1: level_links<1><<<g, 256, 0, s>>>(nb, L.code.p, L.off.p, P.nb, P.code.p, P.ctr.p, q, L.parent.p, L.ctr.p, d_max, d_err); break;
-        case 2: level_links<2><<<g, 256, 0, s>>>(nb, L.code.p, L.off.p, P.nb, P.code.p, P.ctr.p, q, L.parent.p, L.ctr.p, d_max, d_err); break;
-        case 3: level_links<3><<<g, 256, 0, s>>>(nb, L.code.p, L.off.p, P.nb, P.code.p, P.ctr.p, q, L.parent.p, L.ctr.p, d_max, d_err); break;
-        case 4: level_links<4><<<g, 256, 0, s>>>(nb, L.code.p, L.off.p, P.nb, P.code.p, P.ctr.p, q, L.parent.p, L.ctr.p, d_max, d_err); break;
-        default: level_links<5><<<g, 256, 0, s>>>(nb, L.code.p, L.off.p, P.nb, P.code.p, P.ctr.p, q, L.parent.p, L.ctr.p, d_max, d_err); break;
+    const int nt = (int)((n + HTILE - 1) / HTILE);
+    int *d_err = pl->d_flags + FL_ERR, *d_tot = pl->d_flags + FL_LVTOT, *d_max = pl->d_flags + FL_LVMAX;
+    while ((int)t.levels.size() <= l_last) {
+        const int l_first = (int)t.levels.size();
+        const int nlev = std::min(HB, l_last - l_first + 1);
+        DevBuf<int> part;
+        part.alloc((size_t)nlev * nt, s);
+        heads_count<<<nt, HT, 0, s>>>(t.keys.p, n, t.d, t.lmax, l_first, nlev, nt, part.p);
+        F3M_LAUNCH_CHECK();
+        heads_scan<<<nlev, 1024, 0, s>>>(part.p, nt, d_tot);
+        F3M_LAUNCH_CHECK();
+        F3M_CUDA(cudaMemcpyAsync(pl->h_pinned + FL_LVTOT, d_tot, nlev * sizeof(int), cudaMemcpyDeviceToHost, s));
+        F3M_CUDA(cudaStreamSynchronize(s));
+        HeadsOut ho{};
+        for (int v = 0; v < nlev; v++) {
+            const int nb = pl->h_pinned[FL_LVTOT + v];
+            t.levels.emplace_back();
+            Level &L = t.levels.back();
+            L.nb = nb;
+            L.edge = t.levels[l_first + v - 1].edge * 0.5f;
+            L.off.alloc((size_t)nb + 1, s); L.code.alloc(nb, s); L.parent.alloc(nb, s); L.ctr.alloc((size_t)nb * t.d, s);
+            ho.off[v] = L.off.p; ho.code[v] = L.code.p; ho.nb[v] = nb;
+        }
+        heads_write<<<nt, HT, 0, s>>>(t.keys.p, n, t.d, t.lmax, l_first, nlev, nt, part.p, ho);
+        F3M_LAUNCH_CHECK();
+        F3M_CUDA(cudaMemsetAsync(d_max, 0, nlev * sizeof(int), s));
+        for (int v = 0; v < nlev; v++) {
+            Level &L = t.levels[l_first + v], &P = t.levels[l_first + v - 1];
+            const int nb = L.nb;
+            const float q = 0.25f * P.edge;
+            const unsigned g = (unsigned)((nb + 255) / 256);
+            switch (t.d) {
+                case 1: level_links<1><<<g, 256, 0, s>>>(nb, L.code.p, L.off.p, P.nb, P.code.p, P.ctr.p, q, L.parent.p, L.ctr.p, d_max + v, d_err); break;
+                case 2: level_links<2><<<g, 256, 0, s>>>(nb, L.code.p, L.off.p, P.nb, P.code.p, P.ctr.p, q, L.parent.p, L.ctr.p, d_max + v, d_err); break;
+                case 3: level_links<3><<<g, 256, 0, s>>>(nb, L.code.p, L.off.p, P.nb, P.code.p, P.ctr.p, q, L.parent.p, L.ctr.p, d_max + v, d_err); break;
+                case 4: level_links<4><<<g, 256, 0, s>>>(nb, L.code.p, L.off.p, P.nb, P.code.p, P.ctr.p, q, L.parent.p, L.ctr.p, d_max + v, d_err); break;
+                default: level_links<5><<<g, 256, 0, s>>>(nb, L.code.p, L.off.p, P.nb, P.code.p, P.ctr.p, q, L.parent.p, L.ctr.p, d_max + v, d_err); break;
+            }
+            F3M_LAUNCH_CHECK();
+            P.child_start.alloc((size_t)P.nb + 1, s);
+            child_starts<<<(unsigned)((P.nb + 1 + 255) / 256), 256, 0, s>>>(P.nb, P.off.p, nb, L.off.p, P.child_start.p);
+            F3M_LAUNCH_CHECK();
+        }
+        F3M_CUDA(cudaMemcpyAsync(pl->h_pinned + FL_LVMAX, d_max, nlev * sizeof(int), cudaMemcpyDeviceToHost, s));
+        F3M_CUDA(cudaMemcpyAsync(pl->h_pinned + FL_ERR, d_err, sizeof(int), cudaMemcpyDeviceToHost, s));
+        F3M_CUDA(cudaStreamSynchronize(s));
+        F3M_REQUIRE(pl->h_pinned[FL_ERR] == 0, F3M_ERR_INTERNAL, "a box of levels %d..%d has no parent one level up", l_first,
+                    l_first + nlev - 1);
+        for (int v = 0; v < nlev; v++) t.levels[l_first + v].max_count = pl->h_pinned[FL_LVMAX + v];
     }
-    F3M_LAUNCH_CHECK();
-    P.child_start.alloc((size_t)P.nb + 1, s);
-    child_starts<<<(unsigned)((P.nb + 1 + 255) / 256), 256, 0, s>>>(P.nb, P.off.p, nb, L.off.p, P.child_start.p);
-    F3M_LAUNCH_CHECK();
-    F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, pl->d_flags, 4 * sizeof(int), cudaMemcpyDeviceToHost, s));
-    F3M_CUDA(cudaStreamSynchronize(s));
-    F3M_REQUIRE(pl->h_pinned[0] == 0, F3M_ERR_INTERNAL, "box of level %d has no parent at level %d", lvl, lvl - 1);
-    L.max_count = pl->h_pinned[2];
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -305,17 +366,14 @@ __global__ void __launch_bounds__(256) pair_work_kernel(int nbx, const int *__re
     if (lane == 0 && s) atomicAdd(total, (unsigned long long)(s * (long long)(off_x[box + 1] - off_x[box])));
 }
 
-void accumulate_pair_work(f3m_plan *pl, int level, const PairCSR &csr, int64_t *h_pairs, cudaStream_t s) {
+// adds the list's pair work to the plan's device-side total, which the host reads once when the plan is complete
+void accumulate_pair_work(f3m_plan *pl, int level, const PairCSR &csr, cudaStream_t s) {
     if (csr.count == 0) return;
     Level &lx = pl->tx.levels[level], &ly = pl->ty->levels[level];
-    unsigned long long *d_tot = reinterpret_cast<unsigned long long *>(pl->d_flags + 8);
-    F3M_CUDA(cudaMemsetAsync(d_tot, 0, 8, s));
+    unsigned long long *d_tot = reinterpret_cast<unsigned long long *>(pl->d_flags + FL_PAIRWORK);
     pair_work_kernel<<<(unsigned)(((int64_t)lx.nb * 32 + 255) / 256), 256, 0, s>>>(lx.nb, csr.ptr.p, csr.idx.p, lx.off.p,
                                                                                    ly.off.p, d_tot);
     F3M_LAUNCH_CHECK();
-    F3M_CUDA(cudaMemcpyAsync(pl->h_pinned, d_tot, 8, cudaMemcpyDeviceToHost, s));
-    F3M_CUDA(cudaStreamSynchronize(s));
-    *h_pairs += *reinterpret_cast<long long *>(pl->h_pinned);
 }
 
 void build_level_lists(f3m_plan *pl, int level, cudaStream_t s) {
@@ -355,15 +413,14 @@ void build_level_lists(f3m_plan *pl, int level, cudaStream_t s) {
     }                                                                                                                \
     F3M_LAUNCH_CHECK();
     F3M_LISTS(0)
-    exclusive_scan_i32(cur.far.ptr.p, cur.far.ptr.p, (int64_t)nbx + 1, s);
-    exclusive_scan_i32(cur.small.ptr.p, cur.small.ptr.p, (int64_t)nbx + 1, s);
-    exclusive_scan_i32(cur.keep.ptr.p, cur.keep.ptr.p, (int64_t)nbx + 1, s);
-    int *h = pl->h_pinned;
-    F3M_CUDA(cudaMemcpyAsync(h + 0, cur.far.ptr.p + nbx, 4, cudaMemcpyDeviceToHost, s));
-    F3M_CUDA(cudaMemcpyAsync(h + 1, cur.small.ptr.p + nbx, 4, cudaMemcpyDeviceToHost, s));
-    F3M_CUDA(cudaMemcpyAsync(h + 2, cur.keep.ptr.p + nbx, 4, cudaMemcpyDeviceToHost, s));
+    int *ptrs[3] = {cur.far.ptr.p, cur.small.ptr.p, cur.keep.ptr.p};
+    long long *d_tot = reinterpret_cast<long long *>(pl->d_flags + FL_LISTTOT);
+    exclusive_scan_multi(ptrs, 3, (int64_t)nbx + 1, d_tot, s);
+    long long *h = reinterpret_cast<long long *>(pl->h_pinned + FL_LISTTOT);
+    F3M_CUDA(cudaMemcpyAsync(h, d_tot, 3 * sizeof(long long), cudaMemcpyDeviceToHost, s));
     F3M_CUDA(cudaStreamSynchronize(s));
-    F3M_REQUIRE(h[0] >= 0 && h[1] >= 0 && h[2] >= 0, F3M_ERR_OVERFLOW, "interaction list of level %d exceeds 2^31 pairs", level);
+    F3M_REQUIRE(h[0] <= 0x7fffffffLL && h[1] <= 0x7fffffffLL && h[2] <= 0x7fffffffLL, F3M_ERR_OVERFLOW,
+                "interaction list of level %d exceeds 2^31 pairs (far %lld, small %lld, kept %lld)", level, h[0], h[1], h[2]);
     cur.far.count = h[0]; cur.small.count = h[1]; cur.keep.count = h[2];
     cur.far.idx.alloc((size_t)h[0], s); cur.small.idx.alloc((size_t)h[1], s); cur.keep.idx.alloc((size_t)h[2], s);
     F3M_LISTS(1)

@@ -107,6 +107,59 @@ class Plan:
         check(st, "f3m_plan_apply")
         return out
 
+    # ---- one product shared by several GPUs, in phases (see include/f3m.h) --------------------
+    def partition_rows(self, R: int, nparts: int):
+        """Cuts of the sorted target rows into nparts slices of equal estimated work (list of nparts + 1 ints)."""
+        bounds = (C.c_int64 * (nparts + 1))()
+        with torch.cuda.device(self.device):
+            check(_lib.lib().f3m_plan_partition_rows(self._h, int(R), int(nparts), bounds, _stream_ptr(self.device)),
+                  "f3m_plan_partition_rows")
+        return [int(v) for v in bounds]
+
+    def shard_begin(self, b: torch.Tensor, row_range, box_range=None, mom_slice: Optional[torch.Tensor] = None):
+        b = _as_f32(b)
+        if b.dim() == 1:
+            b = b[:, None]
+        if b.shape[0] != self.M or not b.is_cuda:
+            raise AssertionError(f"b must be a CUDA tensor with {self.M} rows")
+        self._shard_b = b      # kept alive until shard_end
+        box_range = (0, 0) if box_range is None else box_range
+        with torch.cuda.device(self.device):
+            st = _lib.lib().f3m_plan_shard_begin(self._h, b.data_ptr(), b.shape[1], int(row_range[0]), int(row_range[1]),
+                                                 int(box_range[0]), int(box_range[1]),
+                                                 None if mom_slice is None else mom_slice.data_ptr(), _stream_ptr(self.device))
+        check(st, "f3m_plan_shard_begin")
+
+    def shard_near(self, acc_sorted: torch.Tensor):
+        with torch.cuda.device(self.device):
+            check(_lib.lib().f3m_plan_shard_near(self._h, acc_sorted.data_ptr(), _stream_ptr(self.device)), "f3m_plan_shard_near")
+
+    def shard_far(self, mom: Optional[torch.Tensor], acc_sorted: torch.Tensor):
+        with torch.cuda.device(self.device):
+            check(_lib.lib().f3m_plan_shard_far(self._h, None if mom is None else mom.data_ptr(), acc_sorted.data_ptr(),
+                                                _stream_ptr(self.device)), "f3m_plan_shard_far")
+
+    def shard_end(self):
+        check(_lib.lib().f3m_plan_shard_end(self._h), "f3m_plan_shard_end")
+        self._shard_b = None
+
+    def rows_to_input_order(self, acc_sorted: torch.Tensor, in_lo: int, in_hi: int) -> torch.Tensor:
+        """Rows in_lo..in_hi of the product in input order, taken from the sorted result acc_sorted (N, R)."""
+        R = acc_sorted.shape[1]
+        out = torch.empty(in_hi - in_lo, R, device=self.device, dtype=torch.float32)
+        with torch.cuda.device(self.device):
+            check(_lib.lib().f3m_plan_rows_to_input_order(self._h, acc_sorted.data_ptr(), R, int(in_lo), int(in_hi), out.data_ptr(),
+                                                          _stream_ptr(self.device)), "f3m_plan_rows_to_input_order")
+        return out
+
+    def finest_boxes(self):
+        """(target boxes, source boxes) at the finest level (1, 1 when no level was built)."""
+        L = self.stats()["levels"]
+        if L == 0:
+            return 1, 1
+        info = self.level(L)
+        return info["boxes_x"], info["boxes_y"]
+
     # ---- introspection ---------------------------------------------------------------------
     def stats(self) -> Dict:
         s = PlanStats()

@@ -121,6 +121,35 @@ int f3m_plan_moments_range(f3m_plan *plan, const float *b, int32_t R, int64_t sr
                            float *mom_out, void *stream);
 int f3m_plan_apply_range_moments(f3m_plan *plan, const float *b, int32_t R, float *out, int64_t row_begin,
                                  int64_t row_end, const float *mom, void *stream);
+
+/* One product shared by several GPUs in phases, so that the exchange of the moments over NVLink runs while the
+ * direct sums are computed (no counterpart in the reference: par_FFM_block runs independent block products,
+ * experiments/FFM_classes.py:128-211).  Every rank holds the same plan (built from all points) and owns one slice
+ * [row_begin, row_end) of the SORTED target rows; slices are cut at finest-level box starts.
+ *
+ *   f3m_plan_partition_rows  cuts the sorted rows into nparts slices of equal estimated work (direct pairs, far
+ *                            pairs, finest-level interpolation); bounds is a HOST array of nparts + 1 entries.
+ *   f3m_plan_shard_begin     marks the source boxes the slice's direct lists name, brings the rows of b of those
+ *                            boxes and of the source boxes [box_begin, box_end) into sorted order, and writes the
+ *                            finest-level moments of the boxes [box_begin, box_end) to mom_slice
+ *                            ((box_end - box_begin) * nfloats / boxes floats, nfloats from f3m_plan_moments_size).
+ *                            mom_slice == NULL or nfloats == 0: no exchange, the rank reads all sources itself.
+ *   (the caller gathers the moment slices of all ranks into one array, boxes in order)
+ *   f3m_plan_shard_near      direct sums of the slice into acc_sorted (N x R, sorted row order; only the rows of
+ *                            the slice are written, and they are overwritten).
+ *   f3m_plan_shard_far       adds the far field of the slice, taking the finest-level moments from mom (all boxes).
+ *   f3m_plan_shard_end       releases what the phases kept in the plan.
+ *   f3m_plan_rows_to_input_order  out[(r - in_lo)] = acc_sorted[position of input row r] for in_lo <= r < in_hi:
+ *                            the rows of the (gathered) sorted result that belong to one range of input rows.
+ * A plan runs one sharded product at a time and must not be used from two host threads at once. */
+int f3m_plan_partition_rows(f3m_plan *plan, int32_t R, int32_t nparts, int64_t *bounds, void *stream);
+int f3m_plan_shard_begin(f3m_plan *plan, const float *b, int32_t R, int64_t row_begin, int64_t row_end, int64_t box_begin,
+                         int64_t box_end, float *mom_slice, void *stream);
+int f3m_plan_shard_near(f3m_plan *plan, float *acc_sorted, void *stream);
+int f3m_plan_shard_far(f3m_plan *plan, const float *mom, float *acc_sorted, void *stream);
+int f3m_plan_shard_end(f3m_plan *plan);
+int f3m_plan_rows_to_input_order(const f3m_plan *plan, const float *acc_sorted, int32_t R, int64_t in_lo, int64_t in_hi,
+                                 float *out, void *stream);
 int f3m_plan_destroy(f3m_plan *plan);
 
 /* -------- introspection (parity checks and work accounting) ------------------------------ */

@@ -16,6 +16,34 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def load_reference(d=3):
+    path = os.path.join(ROOT, "oracle", "_ref", f"f3m_ref_d{d}.so")
+    spec = importlib.util.spec_from_file_location(f"f3m_ref_d{d}", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    return ref
+
+
+def time_reference(n, nodes=216, min_points=1000., ls=1.0, reps=3, dev="cuda:0"):
+    """Median seconds of FFM_XY<float,3> (F3M_src/n_tree.cu:1056-1125) on n points of the benchmark's distribution."""
+    ref = load_reference(3)
+    n = int(n)
+    g = torch.Generator(device=dev).manual_seed(1)
+    X = torch.empty(n, 3, device=dev).uniform_(0, 12 ** 0.5, generator=g)
+    b = torch.randn(n, 1, device=dev, generator=g)
+    times = []
+    for it in range(reps + 1):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = ref.FFM_XY_FLOAT(X, X, b, dev, ls, min_points, nodes, False, 0.15, nodes)
+        torch.cuda.synchronize()
+        if it:
+            times.append(time.perf_counter() - t0)
+    t = sorted(times)[len(times) // 2]
+    return {"impl": "reference build for sm_100a (GPU)", "N": n, "nodes": nodes, "min_points": min_points, "ls": ls,
+            "s_per_kmvm": t, "interactions_per_s": float(n) * n / t, "checksum": float(out.double().sum())}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("n", nargs="*", type=float, default=[1e6])
@@ -24,29 +52,8 @@ def main():
     ap.add_argument("--ls", type=float, default=1.0)
     ap.add_argument("--reps", type=int, default=3)
     a = ap.parse_args()
-    path = os.path.join(ROOT, "oracle", "_ref", "f3m_ref_d3.so")
-    spec = importlib.util.spec_from_file_location("f3m_ref_d3", path)
-    ref = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(ref)
-    dev = "cuda:0"
     for n in a.n:
-        n = int(n)
-        g = torch.Generator(device=dev).manual_seed(1)
-        X = torch.empty(n, 3, device=dev).uniform_(0, 12 ** 0.5, generator=g)
-        b = torch.randn(n, 1, device=dev, generator=g)
-        times = []
-        for it in range(a.reps + 1):
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            out = ref.FFM_XY_FLOAT(X, X, b, dev, a.ls, a.min_points, a.nodes, False, 0.15, a.nodes)
-            torch.cuda.synchronize()
-            if it:
-                times.append(time.perf_counter() - t0)
-        t = sorted(times)[len(times) // 2]
-        print(json.dumps({"impl": "reference build for sm_100a (GPU)", "N": n, "nodes": a.nodes, "min_points": a.min_points,
-                          "ls": a.ls, "s_per_kmvm": t, "interactions_per_s": float(n) * n / t,
-                          "checksum": float(out.double().sum())}), flush=True)
-        del X, b, out
+        print(json.dumps(time_reference(n, a.nodes, a.min_points, a.ls, a.reps)), flush=True)
         torch.cuda.empty_cache()
 
 

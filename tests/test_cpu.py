@@ -153,6 +153,66 @@ def test_oracle_against_reference_golden(path):
 # ---------------------------------------------------------------------------------------------
 # multi-rank host logic on CPU (gloo, world size 2)
 # ---------------------------------------------------------------------------------------------
+class _FakePlan:
+    """Stand-in for engine.Plan in the multi-rank host logic: same phase methods, dense float64 arithmetic on the CPU.
+    "Sorted order" is a fixed permutation, "boxes" are runs of 37 sorted rows, the near part of the product is the
+    dense kernel product and the far part is a made-up term that needs every box's moment in the right order, so that
+    a moment slice that is lost, misplaced or taken from the wrong rank changes the result."""
+    BOX = 37
+
+    def __init__(self, X, ls):
+        from oracle.f3m_oracle import dense_kmvm_f64
+        self._dense = dense_kmvm_f64
+        self.X, self.ls = X, ls
+        self.N = X.shape[0]
+        g = torch.Generator().manual_seed(99)
+        self.perm = torch.randperm(self.N, generator=g)            # sorted position -> input row
+        self.nb = -(-self.N // self.BOX)
+
+    def partition_rows(self, R, nparts):
+        cuts = [0] + [min(self.N, self.BOX * ((self.nb * k) // nparts + (k % 2))) for k in range(1, nparts)] + [self.N]
+        return cuts                                                 # uneven on purpose, at box starts
+
+    def moments_size(self, R):
+        return self.nb * R
+
+    def finest_boxes(self):
+        return self.nb, self.nb
+
+    def shard_begin(self, b, row_range, box_range, mom_slice):
+        self.b, self.rows, self.R = b, row_range, b.shape[1]
+        bs = b[self.perm]
+        for j in range(box_range[0], box_range[1]):                # "moment" of a box: the sum of its rows of b
+            mom_slice.view(-1, self.R)[j - box_range[0]] = bs[j * self.BOX:(j + 1) * self.BOX].sum(0)
+
+    def shard_near(self, acc):
+        rb, re = self.rows
+        rows = self.perm[rb:re]
+        acc[rb:re] = self._dense(self.X[rows], self.X, self.b, self.ls).float()
+
+    def shard_far(self, mom, acc):
+        rb, re = self.rows
+        m = mom.view(-1, self.R)[:self.nb]
+        w = torch.arange(1, self.nb + 1, dtype=torch.float32)[:, None]
+        acc[rb:re] += 1e-3 * (w * m).sum(0)
+
+    def shard_end(self):
+        pass
+
+    def rows_to_input_order(self, acc, lo, hi):
+        out = torch.empty(self.N, acc.shape[1])
+        out[self.perm] = acc
+        return out[lo:hi].clone()
+
+    def close(self):
+        pass
+
+
+class _FakeBackend:
+    def plan(self, X, params):
+        return _FakePlan(X, params)
+
+
 def _rank_main(rank, world, port, q):
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
@@ -162,29 +222,34 @@ def _rank_main(rank, world, port, q):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     g = torch.Generator().manual_seed(3)
     X, b = torch.rand(1001, 3, generator=g), torch.randn(1001, 2, generator=g)
-    lo, hi = [0, 377, 1001][rank], [0, 377, 1001][rank + 1]          # uneven shards
-
-    def compute(Xg, bg, r0, r1):                                      # stand-in for the CUDA engine
-        out = torch.zeros(Xg.shape[0], bg.shape[1])
-        out[r0:r1] = dense_kmvm_f64(Xg[r0:r1], Xg, bg, 0.5).float()
-        return out
-
-    out = distributed_kmvm(X[lo:hi], b[lo:hi], None, compute=compute)
-    exact = dense_kmvm_f64(X, X, b, 0.5)
-    q.put((rank, rel_l2(out, exact)))
+    cuts = [0, 377, 1001] if world == 2 else [0, 200, 377, 1001]    # uneven shards
+    lo, hi = cuts[rank], cuts[rank + 1]
+    out = distributed_kmvm(X[lo:hi], b[lo:hi], 0.5, backend=_FakeBackend())
+    plan = _FakePlan(X, 0.5)
+    bs = b[plan.perm]
+    mom = torch.stack([bs[j * plan.BOX:(j + 1) * plan.BOX].sum(0) for j in range(plan.nb)])
+    far = 1e-3 * (torch.arange(1, plan.nb + 1, dtype=torch.float32)[:, None] * mom).sum(0)
+    exact = dense_kmvm_f64(X, X, b, 0.5).float() + far
+    q.put((rank, tuple(out.shape), rel_l2(out, exact[lo:hi])))
     dist.destroy_process_group()
 
 
-def test_distributed_host_logic_gloo():
+@pytest.mark.parametrize("world", [2, 3])
+def test_distributed_host_logic_gloo(world):
+    """The phases of f3m_b200.parallel.distributed_kmvm on CPU ranks (gloo): shards of unequal size, slices of unequal
+    size, moment slices gathered in box order, every rank gets exactly the rows of its own shard."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + os.getpid() % 2000
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    port = 29500 + (os.getpid() + 7 * world) % 2000
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=120) for _ in procs]
     for p in procs:
         p.join(30)
         assert p.exitcode == 0
-    assert all(err <= 1e-6 for _, err in res), res
+    sizes = {2: [377, 624], 3: [200, 177, 624]}[world]
+    for rank, shape, err in res:
+        assert shape == (sizes[rank], 2)
+        assert err <= 1e-6, res

@@ -511,3 +511,50 @@ def test_leading_slice_is_not_the_shared_tree(cuda):
     assert rel_l2(chunked.cpu(), full.cpu()) <= 1e-4
     plan = engine.Plan(X, X[:k], prm)
     assert not plan.same and plan.M == k
+
+
+@pytest.mark.parametrize("name,world", [("u3_shared", 3), ("clustered3", 4), ("n4_r8", 2), ("u3_xy", 2), ("u3_varcomp", 3), ("tiny", 2)])
+def test_sharded_phases_equal_full_product(name, world, cuda):
+    """The phases a multi-GPU product runs (slices of equal estimated work, moments of a share of the source boxes,
+    direct sums that pack only the sources the slice's lists name, far field from the gathered moments), carried out
+    for every "rank" in turn on one GPU: the assembled sorted result, put back into input order, must equal the
+    single-call product."""
+    from f3m_b200 import engine
+    c = make_case(name)
+    prm = engine.make_params(c["ls"], c["min_points"], c["P"], c["var_comp"], c["eff"], c["small"])
+    X = c["X"].to(cuda)
+    Y = None if c["Y"] is None else c["Y"].to(cuda)
+    plan = engine.Plan(X, Y, prm)
+    b = c["b"].to(cuda)
+    R = b.shape[1]
+    full = plan.apply(b)
+    bounds = plan.partition_rows(R, world)
+    assert bounds[0] == 0 and bounds[-1] == plan.N and all(a <= b_ for a, b_ in zip(bounds, bounds[1:]))
+    L = plan.stats()["levels"]
+    if L > 0:   # cuts lie on finest-level box starts
+        starts = set(plan.array(L, 0, 1).tolist())      # F3M_ARR_BOX_OFFSETS of the target tree
+        assert all(v in starts for v in bounds)
+    msize = plan.moments_size(R)
+    _, nby = plan.finest_boxes()
+    mom_full, per_box, cb = None, 0, 0
+    if msize > 0:
+        per_box, cb = msize // nby, -(-nby // world)
+        mom_full = torch.full((world * cb * per_box,), float("nan"), device=cuda)
+        for r in range(world):      # what the all-gather delivers: every rank's slice at its place
+            box_range = (min(nby, r * cb), min(nby, (r + 1) * cb))
+            plan.shard_begin(b, (bounds[r], bounds[r + 1]), box_range, mom_full[r * cb * per_box:(r + 1) * cb * per_box])
+            plan.shard_end()
+        assert torch.isfinite(mom_full[:nby * per_box]).all()
+        assert rel_l2(mom_full[:nby * per_box].cpu(), plan.moments(b, (0, plan.M)).cpu()) <= 1e-6
+    acc = torch.full((plan.N, R), float("nan"), device=cuda)
+    for r in range(world):
+        box_range = (min(nby, r * cb), min(nby, (r + 1) * cb)) if msize > 0 else (0, 0)
+        scratch = None if msize == 0 else torch.empty(cb * per_box, device=cuda)
+        plan.shard_begin(b, (bounds[r], bounds[r + 1]), box_range, scratch)
+        plan.shard_near(acc)
+        plan.shard_far(mom_full, acc)
+        plan.shard_end()
+    assert torch.isfinite(acc).all()
+    cut = plan.N // 3
+    out = torch.cat([plan.rows_to_input_order(acc, 0, cut), plan.rows_to_input_order(acc, cut, plan.N)])
+    assert rel_l2(out.cpu(), full.cpu()) <= 2e-6

@@ -16,8 +16,8 @@ Prints ONE JSON line.  `value` = N*M / seconds with inputs resident in HBM; `e2e
 host-buffer path (host->device copies of X and b, device->host copy of the result inside the timed region).
 N > 1 GPUs (torchrun): every rank starts with its 1/N shard of X and b and ends with the rows of the
 product that belong to its shard (f3m_b200/parallel.py: all-gather of the points, tree on every rank,
-slices of equal estimated work, moment exchange overlapped with the direct sums, all-gather of the sorted
-slices); the time is the max over ranks.
+slices of equal estimated work, moment exchange overlapped with the direct sums, all-to-all of the computed
+rows to their owners); the time is the max over ranks.
 
 --impl reference: the reference has no CPU implementation (its operator calls CUDA unconditionally,
 experiments/FFM_classes.py:98-126); this arm times the CPU restatement of the reference algorithm
@@ -299,7 +299,7 @@ def main():
         # ---- one more product outside the timed region: phase times (max over ranks), balance, error on sampled rows ----
         stats = {}
         step(stats)
-        names = ["gather_points", "tree_lists", "partition", "sources_moments", "direct_sums", "far_field", "gather_result", "own_rows"]
+        names = ["gather_points", "tree_lists", "partition", "sources_moments", "direct_sums", "far_field", "pack_rows", "exchange_rows", "own_rows"]
         t = torch.tensor([stats.get(k, 0.0) for k in names], device=dev, dtype=torch.float64)
         tm = t.clone()
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)

@@ -63,12 +63,22 @@ SIGNATURES = {
     "f3m_plan_moments_size": (C.c_int, [_P, _I32, C.POINTER(_I64)]),
     "f3m_plan_moments_range": (C.c_int, [_P, _P, _I32, _I64, _I64, _P, _P]),
     "f3m_plan_apply_range_moments": (C.c_int, [_P, _P, _I32, _P, _I64, _I64, _P, _P]),
+    "f3m_sort_depth": (C.c_int, [_I64, _I32, _F32]),
+    "f3m_record_words": (C.c_int, [_I32]),
+    "f3m_bounding_box_f32": (C.c_int, [_P, _I64, _I32, C.POINTER(_F32), C.POINTER(_F32), _P]),
+    "f3m_sort_shard_f32": (C.c_int, [_P, _I64, _I64, _I32, C.POINTER(_F32), _F32, _I32, _I32, _P, _P, _P]),
+    "f3m_plan_create_from_runs": (C.c_int, [C.POINTER(_P), _P, _P, C.POINTER(_I64), _I32, _I64, _I32, C.POINTER(_F32), _F32, _I32,
+                                            C.POINTER(Params), _P]),
     "f3m_plan_partition_rows": (C.c_int, [_P, _I32, _I32, C.POINTER(_I64), _P]),
     "f3m_plan_shard_begin": (C.c_int, [_P, _P, _I32, _I64, _I64, _I64, _I64, _P, _P]),
     "f3m_plan_shard_near": (C.c_int, [_P, _P, _P]),
     "f3m_plan_shard_far": (C.c_int, [_P, _P, _P, _P]),
     "f3m_plan_shard_end": (C.c_int, [_P]),
     "f3m_plan_rows_to_input_order": (C.c_int, [_P, _P, _I32, _I64, _I64, _P, _P]),
+    "f3m_plan_gathered_rows_to_input_order": (C.c_int, [_P, _P, _I32, C.POINTER(_I64), _I32, _I64, _I64, _I64, _P, _P]),
+    "f3m_plan_count_rows_by_owner": (C.c_int, [_P, _I64, _I64, C.POINTER(_I64), _I32, C.POINTER(_I64), _P]),
+    "f3m_plan_pack_rows_by_owner": (C.c_int, [_P, _P, _I32, _I64, _I64, C.POINTER(_I64), _I32, C.POINTER(_I64), _P, _P]),
+    "f3m_plan_place_rows": (C.c_int, [_P, _P, _I64, _I32, _I64, _I64, _P, _P]),
     "f3m_plan_destroy": (C.c_int, [_P]),
     "f3m_plan_get_stats": (C.c_int, [_P, C.POINTER(PlanStats)]),
     "f3m_plan_get_level": (C.c_int, [_P, _I32, C.POINTER(LevelInfo)]),

@@ -144,14 +144,26 @@ static void check_common(const void *X, int64_t N, const void *Y, int64_t M, int
     F3M_REQUIRE(prm->nr_interpolation >= 1, F3M_ERR_ARG, "nr_interpolation must be >= 1");
 }
 
-static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, int64_t M, int d, const f3m_params *prm,
-                       cudaStream_t s) {
+static void plan_build_levels(f3m_plan *pl, const float *X, int64_t N, const float *Y, int64_t M, const float *xmin, const float *ymin,
+                              float edge0, cudaStream_t s);
+
+// levels the sort covers: the level loop stops at the first level whose largest box holds at most min_points points;
+// for evenly spread points that is the level where the mean occupancy falls below min_points (one more when the mean
+// is within a factor two of it)
+static int estimate_depth(int64_t n, int d, float min_points) {
+    const int lmax = std::min(30 / d, 20);
+    int L = 1;
+    auto mean = [&](int l) { return (double)n / pow(2.0, (double)d * l); };
+    while (L < lmax && mean(L) > (double)min_points) L++;
+    if (L < lmax && mean(L) > 0.5 * (double)min_points) L++;
+    return L;
+}
+
+static void plan_begin(f3m_plan *pl, int d, const f3m_params *prm, bool same, cudaStream_t s) {
     F3M_CUDA(cudaGetDevice(&pl->device));
     pl->d = d;
     pl->prm = *prm;
-    // n_tree.cu:1072 tests the address only; a leading slice of X starts at the same address but is another
-    // (smaller) point set, so the sizes must agree too
-    pl->same = (X == Y && N == M);
+    pl->same = same;
     pl->lcs = 1 / (2 * prm->ls * prm->ls);                // n_tree.cu:1060
     {
         ScratchSlot sl = take_slot(pl->device);
@@ -160,6 +172,13 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
     }
     F3M_CUDA(cudaMemsetAsync(pl->d_flags, 0, FLAG_WORDS * sizeof(int), s));
     pl->last.begin(ST_BUILD, s);
+}
+
+static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, int64_t M, int d, const f3m_params *prm,
+                       cudaStream_t s) {
+    // n_tree.cu:1072 tests the address only; a leading slice of X starts at the same address but is another
+    // (smaller) point set, so the sizes must agree too
+    plan_begin(pl, d, prm, X == Y && N == M, s);
 
     // bounding cube: calculate_edge_X / calculate_edge (n_tree.cu:25-46), float32 throughout
     float xmin[MAXD], xmax[MAXD], ymin[MAXD], ymax[MAXD];
@@ -183,20 +202,10 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
     float edge0 = range * 1.01f;
     F3M_REQUIRE(edge0 > 0.f && std::isfinite(edge0), F3M_ERR_ARG, "degenerate or non-finite bounding cube (edge %g)", edge0);
 
-    // Only the key bits of the levels the loop below will visit are sorted.  The loop stops at the first level whose
-    // largest box holds at most min_points points; for evenly spread points that is the level where the mean
-    // occupancy falls below min_points (one more when the mean is within a factor two of it).  If the loop does
-    // go deeper (clustered points), the trees are sorted again to the full key depth.
-    auto estimate_depth = [&](int64_t n) {
-        const int lmax = std::min(30 / d, 20);
-        int L = 1;
-        auto mean = [&](int l) { return (double)n / pow(2.0, (double)d * l); };
-        while (L < lmax && mean(L) > (double)prm->min_points) L++;
-        if (L < lmax && mean(L) > 0.5 * (double)prm->min_points) L++;
-        return L;
-    };
-    int depth = estimate_depth(N);
-    if (!pl->same) depth = std::min(depth, estimate_depth(M));
+    // Only the key bits of the levels the loop below will visit are sorted.  If the loop does go deeper than estimated
+    // (clustered points), the trees are sorted again to the full key depth.
+    int depth = estimate_depth(N, d, prm->min_points);
+    if (!pl->same) depth = std::min(depth, estimate_depth(M, d, prm->min_points));
     build_sorted_tree(pl->tx, X, N, d, xmin, edge0, prm->math_mode, depth, s);
     build_root(pl->tx, s);
     if (pl->same) pl->ty = &pl->tx;
@@ -205,6 +214,14 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
         build_root(pl->ty_store, s);
         pl->ty = &pl->ty_store;
     }
+    plan_build_levels(pl, X, N, Y, M, xmin, ymin, edge0, s);
+}
+
+// second half of the plan: levels, interaction lists, work accounting (the trees hold sorted points)
+static void plan_build_levels(f3m_plan *pl, const float *X, int64_t N, const float *Y, int64_t M, const float *xmin, const float *ymin,
+                              float edge0, cudaStream_t s) {
+    const f3m_params *prm = &pl->prm;
+    const int d = pl->d;
     Tree &tx = pl->tx, &ty = *pl->ty;
 
     // root pair list (n_tree.cu:1071)
@@ -234,6 +251,9 @@ static void plan_build(f3m_plan *pl, const float *X, int64_t N, const float *Y, 
         F3M_REQUIRE(need <= tx.lmax, F3M_ERR_DEPTH,
                     "tree needs level %d but a 30-bit cell index holds %d levels in %d dimensions", need, tx.lmax, d);
         if (need > tx.sorted_depth) {
+            F3M_REQUIRE(X != nullptr, F3M_ERR_UNSUPPORTED,
+                        "the tree needs level %d but the runs it was merged from are sorted to level %d: build the plan from the points",
+                        need, tx.sorted_depth);
             // deeper than estimated: sort to the full key depth (levels already built keep their boxes)
             build_sorted_tree(tx, X, N, d, xmin, edge0, prm->math_mode, tx.lmax, s);
             if (!pl->same) build_sorted_tree(ty, Y, M, d, ymin, edge0, prm->math_mode, ty.lmax, s);
@@ -298,6 +318,8 @@ static void plan_apply(f3m_plan *pl, const float *b, int R, float *out, int64_t 
     pl->last.direct_launches = 0;
     for (int &v : pl->last.direct_variants) v = 0;
     pl->last.begin(ST_TOTAL, s);
+    pl->pack_cache.reset();
+    struct DropPacked { f3m_plan *p; ~DropPacked() { p->pack_cache.reset(); } } drop_packed{pl};
 
     pl->last.begin(ST_PERMUTE, s);
     DevBuf<float> bs, outs;
@@ -420,6 +442,65 @@ int f3m_plan_apply_range_moments(f3m_plan *plan, const float *b, int32_t R, floa
     return st;
 }
 
+/* ---- a plan from runs sorted on several GPUs ----------------------------------------------------------------- */
+
+int f3m_sort_depth(int64_t n, int32_t d, float min_points) {
+    if (n < 1 || d < 1 || d > F3M_MAX_DIM) return 0;
+    return estimate_depth(n, d, min_points);
+}
+
+int f3m_record_words(int32_t d) { return (d < 1 || d > F3M_MAX_DIM) ? 0 : record_words(d); }
+
+int f3m_bounding_box_f32(const float *X, int64_t n, int32_t d, float *min_out, float *max_out, void *stream) {
+    if (!X || !min_out || !max_out || n < 1 || d < 1 || d > F3M_MAX_DIM) return F3M_ERR_ARG;
+    return guarded([&] {
+        f3m_plan tmp;   // only its scratch words are used
+        F3M_CUDA(cudaGetDevice(&tmp.device));
+        ScratchSlot sl = take_slot(tmp.device);
+        tmp.h_pinned = sl.h_pinned;
+        tmp.d_flags = sl.d_flags;
+        bounding_box(X, n, d, min_out, max_out, &tmp, (cudaStream_t)stream);
+    });
+}
+
+int f3m_sort_shard_f32(const float *X, int64_t n, int64_t row_offset, int32_t d, const float *origin, float edge0, int32_t math_mode,
+                       int32_t depth, uint32_t *keys_out, void *records_out, void *stream) {
+    if (!X || !origin || !keys_out || !records_out || n < 1 || row_offset < 0 || d < 1 || d > F3M_MAX_DIM) return F3M_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    return guarded([&] {
+        F3M_REQUIRE(edge0 > 0.f && std::isfinite(edge0), F3M_ERR_ARG, "degenerate or non-finite bounding cube (edge %g)", edge0);
+        sort_shard(X, n, row_offset, d, origin, edge0, math_mode, depth, keys_out, static_cast<uint32_t *>(records_out), s);
+        F3M_CUDA(cudaStreamSynchronize(s));
+    });
+}
+
+int f3m_plan_create_from_runs(f3m_plan **plan, const uint32_t *keys, const void *records, const int64_t *run_counts, int32_t nruns,
+                              int64_t run_stride, int32_t d, const float *origin, float edge0, int32_t depth, const f3m_params *prm,
+                              void *stream) {
+    if (!plan) return F3M_ERR_ARG;
+    *plan = nullptr;
+    f3m_plan *pl = nullptr;
+    cudaStream_t s = (cudaStream_t)stream;
+    int st = guarded([&] {
+        F3M_REQUIRE(keys && records && run_counts && origin && prm && nruns >= 1, F3M_ERR_ARG, "null pointer argument");
+        F3M_REQUIRE(d >= 1 && d <= F3M_MAX_DIM, F3M_ERR_ARG, "dimension %d outside 1..%d", d, F3M_MAX_DIM);
+        F3M_REQUIRE(prm->ls > 0.f && prm->nr_interpolation >= 1, F3M_ERR_ARG, "bad parameters");
+        F3M_REQUIRE(edge0 > 0.f && std::isfinite(edge0), F3M_ERR_ARG, "degenerate or non-finite bounding cube (edge %g)", edge0);
+        pl = new f3m_plan();
+        plan_begin(pl, d, prm, true, s);
+        build_tree_from_runs(pl->tx, keys, static_cast<const uint32_t *>(records), run_counts, nruns, run_stride, d, origin, edge0, depth, s);
+        build_root(pl->tx, s);
+        pl->ty = &pl->tx;
+        plan_build_levels(pl, nullptr, pl->tx.n, nullptr, pl->tx.n, origin, origin, edge0, s);
+    });
+    if (st != F3M_OK) {
+        if (pl) { cudaStreamSynchronize(s); delete pl; }
+        return st;
+    }
+    *plan = pl;
+    return F3M_OK;
+}
+
 /* ---- one product shared by several GPUs, in phases ------------------------------------------------------------ */
 
 int f3m_plan_partition_rows(f3m_plan *plan, int32_t R, int32_t nparts, int64_t *bounds, void *stream) {
@@ -493,6 +574,8 @@ int f3m_plan_shard_near(f3m_plan *plan, float *acc_sorted, void *stream) {
         F3M_REQUIRE(sh.active, F3M_ERR_ARG, "f3m_plan_shard_near without f3m_plan_shard_begin");
         const int L = plan->levels, R = sh.R;
         const int64_t rb = sh.row_begin, re = sh.row_end;
+        plan->pack_cache.reset();
+        struct DropPacked { f3m_plan *p; ~DropPacked() { p->pack_cache.reset(); } } drop_packed{plan};
         if (re > rb) F3M_CUDA(cudaMemsetAsync(acc_sorted + rb * R, 0, (size_t)(re - rb) * R * sizeof(float), s));
         if (L == 0) direct_sums(plan, 0, plan->lists[0].keep, sh.bs.p, R, acc_sorted, rb, re, s);
         for (int level = 1; level <= L; level++) direct_sums(plan, level, plan->lists[level].small, sh.bs.p, R, acc_sorted, rb, re, s);
@@ -529,6 +612,43 @@ int f3m_plan_shard_end(f3m_plan *plan) {
     plan->shard.bs.release();
     plan->shard.need.clear();
     return F3M_OK;
+}
+
+int f3m_plan_gathered_rows_to_input_order(const f3m_plan *plan, const float *gathered, int32_t R, const int64_t *slice_bounds,
+                                          int32_t nslices, int64_t stride, int64_t in_lo, int64_t in_hi, float *out, void *stream) {
+    if (!plan || !gathered || !slice_bounds || !out || R < 1 || in_lo < 0 || in_hi < in_lo || in_hi > plan->tx.n) return F3M_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    return guarded([&] {
+        shard_gathered_rows_to_input_order(plan, gathered, R, slice_bounds, nslices, stride, in_lo, in_hi, out, s);
+        F3M_CUDA(cudaStreamSynchronize(s));
+    });
+}
+
+int f3m_plan_count_rows_by_owner(const f3m_plan *plan, int64_t row_begin, int64_t row_end, const int64_t *in_bounds, int32_t nranks,
+                                 int64_t *counts, void *stream) {
+    if (!plan || !in_bounds || !counts || row_begin < 0 || row_end < row_begin || row_end > plan->tx.n) return F3M_ERR_ARG;
+    return guarded([&] { shard_count_rows_by_owner(plan, row_begin, row_end, in_bounds, nranks, counts, (cudaStream_t)stream); });
+}
+
+int f3m_plan_pack_rows_by_owner(const f3m_plan *plan, const float *acc_sorted, int32_t R, int64_t row_begin, int64_t row_end,
+                                const int64_t *in_bounds, int32_t nranks, const int64_t *counts, float *send, void *stream) {
+    if (!plan || !acc_sorted || !in_bounds || !counts || !send || R < 1 || row_begin < 0 || row_end < row_begin || row_end > plan->tx.n)
+        return F3M_ERR_ARG;
+    return guarded([&] {
+        shard_pack_rows_by_owner(plan, acc_sorted, R, row_begin, row_end, in_bounds, nranks, counts, send, (cudaStream_t)stream);
+    });
+}
+
+int f3m_plan_place_rows(f3m_plan *plan, const float *records, int64_t n, int32_t R, int64_t in_lo, int64_t in_hi, float *out,
+                        void *stream) {
+    if (!plan || !records || !out || n < 0 || R < 1 || in_hi < in_lo) return F3M_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    return guarded([&] {
+        shard_place_rows(records, n, R, in_lo, in_hi, out, plan->d_flags + FL_ERR, s);
+        F3M_CUDA(cudaMemcpyAsync(plan->h_pinned, plan->d_flags + FL_ERR, sizeof(int), cudaMemcpyDeviceToHost, s));
+        F3M_CUDA(cudaStreamSynchronize(s));
+        F3M_REQUIRE(plan->h_pinned[0] == 0, F3M_ERR_INTERNAL, "a received row lies outside this rank's input rows (code %d)", plan->h_pinned[0]);
+    });
 }
 
 int f3m_plan_rows_to_input_order(const f3m_plan *plan, const float *acc_sorted, int32_t R, int64_t in_lo, int64_t in_hi, float *out,

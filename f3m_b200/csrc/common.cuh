@@ -257,6 +257,15 @@ struct f3m_plan {
     int64_t mom_begin = 0, mom_end = 0;
     int64_t mom_box_begin = -1, mom_box_end = -1;   // >= 0: moments_out covers these source boxes only
     const float *ext_mom = nullptr;
+    // source boxes named by the direct lists of a level over ALL targets (a constant of the plan, built on first use)
+    std::vector<f3m::DevBuf<unsigned char>> src_need;
+    // packed sources of the last direct list (valid inside one product)
+    struct PackCache {
+        int level = -1, r0 = 0, rb = 0;
+        bool expanded = false;
+        f3m::DevBuf<float> buf;
+        void reset() { level = -1; buf.release(); }
+    } pack_cache;
     // a product shared by several GPUs, in phases (f3m_plan_shard_begin / _near / _far): state kept between the calls
     struct Shard {
         bool active = false;
@@ -277,6 +286,11 @@ namespace f3m {
 void bounding_box(const float *X, int64_t n, int d, float *h_min, float *h_max, f3m_plan *pl, cudaStream_t s);
 void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *origin, float edge0,
                        int math_mode, int depth, cudaStream_t s);
+int record_words(int d);   // 32-bit words of the record [input row, coordinates] that travels with a key in the sort
+void sort_shard(const float *X, int64_t n, int64_t row0, int d, const float *origin, float edge0, int math_mode, int depth,
+                uint32_t *keys_out, uint32_t *recs_out, cudaStream_t s);
+void build_tree_from_runs(Tree &t, const uint32_t *keys, const uint32_t *recs, const int64_t *h_run_counts, int nruns, int64_t stride,
+                          int d, const float *origin, float edge0, int depth, cudaStream_t s);
 void exclusive_scan_i32(const int *in, int *out, int64_t n, cudaStream_t s);  // n values; out may alias in
 // up to four arrays of n values scanned in place by one set of launches; their sums as 64-bit numbers -> totals64 (device)
 void exclusive_scan_multi(int *const *arrays, int narr, int64_t n, long long *totals64, cudaStream_t s);
@@ -299,9 +313,17 @@ void far_field(f3m_plan *pl, const float *b_sorted, int R, float *out_sorted, in
 int64_t far_moments_size(const f3m_plan *pl, int R);
 
 // ---- shard.cu --------------------------------------------------------------------------------
+const unsigned char *level_source_flags(f3m_plan *pl, int level, cudaStream_t s);   // per source box of the level: named by a direct list?
 void shard_partition(f3m_plan *pl, int R, int nparts, int64_t *h_bounds, cudaStream_t s);
 void shard_mark_and_gather(f3m_plan *pl, const float *b, int R, int row_begin, int row_end, int box_begin, int box_end,
                            bool everything, cudaStream_t s);
+void shard_count_rows_by_owner(const f3m_plan *pl, int64_t row_begin, int64_t row_end, const int64_t *h_bounds, int nranks,
+                               int64_t *h_counts, cudaStream_t s);
+void shard_pack_rows_by_owner(const f3m_plan *pl, const float *acc_sorted, int R, int64_t row_begin, int64_t row_end,
+                              const int64_t *h_bounds, int nranks, const int64_t *h_counts, float *send, cudaStream_t s);
+void shard_gathered_rows_to_input_order(const f3m_plan *pl, const float *gathered, int R, const int64_t *h_slice_bounds, int nslices,
+                                        int64_t stride, int64_t in_lo, int64_t in_hi, float *out, cudaStream_t s);
+void shard_place_rows(const float *recs, int64_t n, int R, int64_t in_lo, int64_t in_hi, float *out, int *d_err, cudaStream_t s);
 void shard_rows_to_input_order(const f3m_plan *pl, const float *acc_sorted, int R, int64_t in_lo, int64_t in_hi, float *out,
                                cudaStream_t s);
 

@@ -227,6 +227,48 @@ __global__ void __launch_bounds__(256) pack_pairs_rel(const float *__restrict__ 
     }
 }
 
+// The same packing with one warp per source box (and per part of a long box): boxes no list of this product names
+// are skipped without touching their points, and no point searches for its box.
+template <int D, int RB>
+__global__ void __launch_bounds__(256) pack_pairs_box(const float *__restrict__ pts, int n, const float *__restrict__ bs, int R,
+                                                     int r0, float scale, const int *__restrict__ off_y, int nby,
+                                                     const float *__restrict__ ctr_y, const unsigned char *__restrict__ need,
+                                                     int nsplit, float *packed) {
+    constexpr int W = row_width(D, RB);
+    const int lane = threadIdx.x & 31;
+    const int by = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (by >= nby || (need && !need[by])) return;
+    const int s0 = off_y[by], s1 = off_y[by + 1], len = s1 - s0;
+    const int c0 = s0 + (int)(((long long)len * blockIdx.y) / nsplit), c1 = s0 + (int)(((long long)len * (blockIdx.y + 1)) / nsplit);
+    float ctr[D];
+#pragma unroll
+    for (int k = 0; k < D; k++) ctr[k] = ctr_y[by * D + k];
+    const int prow = pair_row_start(s0, by);
+    for (int j = c0 + lane; j < c1; j += 32) {
+        float row[W];
+        float ny = 0.f;
+#pragma unroll
+        for (int k = 0; k < D; k++) {
+            float yr = scale * (pts[(size_t)k * n + j] - ctr[k]);
+            ny = fmaf(-yr, yr, ny);
+            row[k] = 2.f * yr;
+        }
+        const float wy = ex2_approx(ny);
+#pragma unroll
+        for (int r = 0; r < RB; r++) row[D + r] = (r0 + r < R) ? bs[(size_t)j * R + r0 + r] * wy : 0.f;
+#pragma unroll
+        for (int c = D + RB; c < W; c++) row[c] = 0.f;
+        const int pos = prow + (j - s0);
+        float *dst = packed + (size_t)(pos >> 1) * (2 * W) + (pos & 1);
+#pragma unroll
+        for (int c = 0; c < W; c++) dst[2 * c] = row[c];
+        if (j == s1 - 1 && !(pos & 1)) {   // last source of an odd box: its partner weighs nothing
+#pragma unroll
+            for (int c = 0; c < W; c++) dst[2 * c + 1] = 0.f;
+        }
+    }
+}
+
 constexpr int SP2 = 192;   // source pairs per shared-memory tile
 
 // POLY = 0: every exponential on the MUFU pipe.  POLY = 2 or 3: PNUM of every PDEN source pairs use the
@@ -595,9 +637,16 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
     const int items = pl->h_pinned[0];
     const bool small_tiles = pl->h_pinned[1] > 0;   // some tiles hold at most 32 targets: use the kernel that halves their work
     if (items <= 0) return;
-    DevBuf<float> packed;
-    // the pair layout of the expanded form starts every box on an even row
-    if (!use_mma) packed.alloc((size_t)(ty.n + (expanded ? ly.nb + 2 : 0)) * row_width(D, RB), s);
+    // Packed sources are kept for the lists of one level that share (column block, form): the "small" list of the last
+    // level and the final near list read the same boxes' rows.
+    f3m_plan::PackCache &pc = pl->pack_cache;
+    const bool cached = !use_mma && pc.level == level && pc.r0 == r0 && pc.rb == RB && pc.expanded == expanded;
+    if (!use_mma && !cached) {
+        // the pair layout of the expanded form starts every box on an even row
+        pc.buf.alloc((size_t)(ty.n + (expanded ? ly.nb + 2 : 0)) * row_width(D, RB), s);
+        pc.level = level; pc.r0 = r0; pc.rb = RB; pc.expanded = expanded;
+    }
+    DevBuf<float> &packed = pc.buf;
     const unsigned g = (unsigned)((ty.n + 255) / 256);
     if (use_mma) {
         using S = MmaShape<D>;
@@ -642,14 +691,20 @@ static void direct_impl(f3m_plan *pl, int level, const PairCSR &csr, const float
         F3M_LAUNCH_CHECK();
         return;
     }
-    pl->last.begin(ST_PERMUTE, s);
-    if (expanded) {
-        pack_pairs_rel<D, RB><<<g, 256, 0, s>>>(ty.pts.p, (int)ty.n, bs, R, r0, scale, ly.off.p, ly.nb, ly.ctr.p,
-                                                (pl->shard.active && !pl->shard.all_sources) ? pl->shard.need[level].p : nullptr, packed.p);
-    } else
-        pack_sources<D, RB><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
-    pl->last.end(s);
-    F3M_LAUNCH_CHECK();
+    if (!cached) {
+        pl->last.begin(ST_PERMUTE, s);
+        if (expanded) {
+            // only the boxes that a direct list of this level names (for this slice of the targets, when the product is
+            // shared by several GPUs) are packed
+            const unsigned char *need = level_source_flags(pl, level, s);
+            const int nsplit = std::max(1, std::min(65535, (ly.max_count + 2047) / 2048));
+            pack_pairs_box<D, RB><<<dim3((unsigned)(((int64_t)ly.nb * 32 + 255) / 256), nsplit), 256, 0, s>>>(
+                ty.pts.p, (int)ty.n, bs, R, r0, scale, ly.off.p, ly.nb, ly.ctr.p, need, nsplit, packed.p);
+        } else
+            pack_sources<D, RB><<<g, 256, 0, s>>>(ty.pts.p, ty.n, bs, R, r0, scale, packed.p);
+        pl->last.end(s);
+        F3M_LAUNCH_CHECK();
+    }
     pl->last.begin(ST_DIRECT, s);
     if (expanded) {
         const int poly = exp2_poly_degree(tmax);

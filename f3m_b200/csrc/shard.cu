@@ -61,6 +61,29 @@ __global__ void __launch_bounds__(256) gather_rows_of_boxes(int nb, const int *_
     }
 }
 
+// Source boxes of `level` that a direct list of the level names: for the slice of the running sharded product, else for
+// all targets (kept in the plan: the lists do not change).
+const unsigned char *level_source_flags(f3m_plan *pl, int level, cudaStream_t s) {
+    if (pl->shard.active) return pl->shard.all_sources ? nullptr : pl->shard.need[level].p;
+    if (level < 1) return nullptr;
+    if ((int)pl->src_need.size() <= pl->levels) pl->src_need.resize(pl->levels + 1);
+    DevBuf<unsigned char> &f = pl->src_need[level];
+    if (!f.p) {
+        Level &lx = pl->tx.levels[level];
+        f.alloc((size_t)pl->ty->levels[level].nb, s);
+        f.zero();
+        auto mark = [&](const PairCSR &csr) {
+            if (csr.count == 0) return;
+            mark_list_sources<<<(unsigned)(((int64_t)lx.nb * 32 + 255) / 256), 256, 0, s>>>(lx.nb, lx.off.p, csr.ptr.p, csr.idx.p, 0,
+                                                                                            (int)pl->tx.n, f.p);
+            F3M_LAUNCH_CHECK();
+        };
+        mark(pl->lists[level].small);
+        if (level == pl->levels) mark(pl->lists[level].keep);
+    }
+    return f.p;
+}
+
 void shard_mark_and_gather(f3m_plan *pl, const float *b, int R, int row_begin, int row_end, int box_begin, int box_end,
                            bool everything, cudaStream_t s) {
     Tree &tx = pl->tx, &ty = *pl->ty;
@@ -130,6 +153,141 @@ void shard_rows_to_input_order(const f3m_plan *pl, const float *acc_sorted, int 
 }
 
 // ---------------------------------------------------------------------------------------------
+// rows of a slice of the sorted result, grouped by the rank that owns the INPUT row (for an all-to-all)
+// ---------------------------------------------------------------------------------------------
+constexpr int OWN_T = 256, OWN_I = 8, OWN_MAXR = 64;   // at most 64 ranks
+
+struct OwnerBounds { long long lo[OWN_MAXR + 1]; };   // rank g owns the input rows [lo[g], lo[g+1])
+
+__device__ __forceinline__ int owner_of(const OwnerBounds &ob, int nranks, long long row) {
+    int a = 0, b = nranks;   // largest g with lo[g] <= row
+    while (b - a > 1) {
+        const int mid = (a + b) >> 1;
+        if (ob.lo[mid] <= row) a = mid; else b = mid;
+    }
+    return a;
+}
+
+// pass 0: counts[g] += rows of the slice owned by rank g.  pass 1: cursor[g] holds the start of g's group in the
+// send buffer; every block reserves its share and writes [values of the row, input row] records (cols + 1 words)
+__global__ void __launch_bounds__(OWN_T) rows_by_owner_kernel(int pass, const float *__restrict__ acc, const int *__restrict__ perm,
+                                                             int64_t row_begin, int64_t row_end, int cols, OwnerBounds ob, int nranks,
+                                                             unsigned long long *cursor, float *send) {
+    __shared__ int cnt[OWN_MAXR];
+    __shared__ unsigned long long base[OWN_MAXR];
+    if (threadIdx.x < OWN_MAXR) cnt[threadIdx.x] = 0;
+    __syncthreads();
+    const int64_t i0 = row_begin + (int64_t)blockIdx.x * (OWN_T * OWN_I) + threadIdx.x;
+    int own[OWN_I], slot[OWN_I];
+#pragma unroll
+    for (int k = 0; k < OWN_I; k++) {
+        const int64_t i = i0 + (int64_t)k * OWN_T;
+        own[k] = -1;
+        if (i < row_end) {
+            own[k] = owner_of(ob, nranks, perm[i]);
+            slot[k] = atomicAdd(&cnt[own[k]], 1);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < nranks && cnt[threadIdx.x] > 0)
+        base[threadIdx.x] = atomicAdd(&cursor[threadIdx.x], (unsigned long long)cnt[threadIdx.x]);
+    if (pass == 0) return;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < OWN_I; k++) {
+        if (own[k] < 0) continue;
+        const int64_t i = i0 + (int64_t)k * OWN_T;
+        float *dst = send + (base[own[k]] + (unsigned long long)slot[k]) * (unsigned long long)(cols + 1);
+        for (int c = 0; c < cols; c++) dst[c] = acc[i * cols + c];
+        dst[cols] = __int_as_float(perm[i]);
+    }
+}
+
+// h_counts[g] = rows of [row_begin, row_end) whose input row belongs to rank g (h_bounds: nranks + 1 input-row cuts)
+void shard_count_rows_by_owner(const f3m_plan *pl, int64_t row_begin, int64_t row_end, const int64_t *h_bounds, int nranks,
+                               int64_t *h_counts, cudaStream_t s) {
+    F3M_REQUIRE(nranks >= 1 && nranks <= OWN_MAXR, F3M_ERR_ARG, "1..%d ranks", OWN_MAXR);
+    OwnerBounds ob{};
+    for (int g = 0; g <= nranks; g++) ob.lo[g] = h_bounds[g];
+    DevBuf<unsigned long long> cur;
+    cur.alloc(OWN_MAXR, s);
+    cur.zero();
+    const int64_t rows = row_end - row_begin;
+    if (rows > 0) {
+        rows_by_owner_kernel<<<(unsigned)((rows + OWN_T * OWN_I - 1) / (OWN_T * OWN_I)), OWN_T, 0, s>>>(
+            0, nullptr, pl->tx.perm.p, row_begin, row_end, 1, ob, nranks, cur.p, nullptr);
+        F3M_LAUNCH_CHECK();
+    }
+    unsigned long long h[OWN_MAXR];
+    F3M_CUDA(cudaMemcpyAsync(h, cur.p, sizeof(h), cudaMemcpyDeviceToHost, s));
+    F3M_CUDA(cudaStreamSynchronize(s));
+    for (int g = 0; g < nranks; g++) h_counts[g] = (int64_t)h[g];
+}
+
+// send: (rows, cols + 1) floats, the rows of rank 0 first, then rank 1, ...; h_counts from the call above
+void shard_pack_rows_by_owner(const f3m_plan *pl, const float *acc_sorted, int R, int64_t row_begin, int64_t row_end,
+                              const int64_t *h_bounds, int nranks, const int64_t *h_counts, float *send, cudaStream_t s) {
+    F3M_REQUIRE(nranks >= 1 && nranks <= OWN_MAXR, F3M_ERR_ARG, "1..%d ranks", OWN_MAXR);
+    OwnerBounds ob{};
+    for (int g = 0; g <= nranks; g++) ob.lo[g] = h_bounds[g];
+    unsigned long long h[OWN_MAXR] = {0};
+    unsigned long long run = 0;
+    for (int g = 0; g < nranks; g++) { h[g] = run; run += (unsigned long long)h_counts[g]; }
+    DevBuf<unsigned long long> cur;
+    cur.alloc(OWN_MAXR, s);
+    F3M_CUDA(cudaMemcpyAsync(cur.p, h, sizeof(h), cudaMemcpyHostToDevice, s));
+    const int64_t rows = row_end - row_begin;
+    if (rows > 0) {
+        rows_by_owner_kernel<<<(unsigned)((rows + OWN_T * OWN_I - 1) / (OWN_T * OWN_I)), OWN_T, 0, s>>>(
+            1, acc_sorted, pl->tx.perm.p, row_begin, row_end, R, ob, nranks, cur.p, send);
+        F3M_LAUNCH_CHECK();
+    }
+    F3M_CUDA(cudaStreamSynchronize(s));   // h lives on this frame
+}
+
+// The sorted result as an all-gather of the ranks' slices leaves it: slice g (sorted rows [lo[g], lo[g+1])) starts at row
+// g * stride of `gathered`.  Rows of the input range [in_lo, in_hi) go to out in input order.
+__global__ void __launch_bounds__(256) gathered_rows_to_input_order(const float *__restrict__ gathered, const int *__restrict__ perm,
+                                                                   int64_t n, int cols, OwnerBounds slices, int nslices, int64_t stride,
+                                                                   int64_t in_lo, int64_t in_hi, float *out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t r = perm[i];
+    if (r < in_lo || r >= in_hi) return;
+    const int g = owner_of(slices, nslices, i);
+    const float *src = gathered + ((int64_t)g * stride + (i - slices.lo[g])) * cols;
+    for (int c = 0; c < cols; c++) out[(r - in_lo) * cols + c] = src[c];
+}
+
+void shard_gathered_rows_to_input_order(const f3m_plan *pl, const float *gathered, int R, const int64_t *h_slice_bounds, int nslices,
+                                        int64_t stride, int64_t in_lo, int64_t in_hi, float *out, cudaStream_t s) {
+    F3M_REQUIRE(nslices >= 1 && nslices <= OWN_MAXR, F3M_ERR_ARG, "1..%d slices", OWN_MAXR);
+    OwnerBounds ob{};
+    for (int g = 0; g <= nslices; g++) ob.lo[g] = h_slice_bounds[g];
+    const Tree &tx = pl->tx;
+    gathered_rows_to_input_order<<<(unsigned)((tx.n + 255) / 256), 256, 0, s>>>(gathered, tx.perm.p, tx.n, R, ob, nslices, stride, in_lo,
+                                                                                in_hi, out);
+    F3M_LAUNCH_CHECK();
+}
+
+// records [values, input row] -> out[(input row - in_lo)] (the receiving side of the all-to-all)
+__global__ void __launch_bounds__(256) place_rows_kernel(const float *__restrict__ recs, int64_t n, int cols, int64_t in_lo,
+                                                        int64_t in_hi, float *out, int *err) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float *src = recs + i * (cols + 1);
+    const int64_t r = __float_as_int(src[cols]);
+    if (r < in_lo || r >= in_hi) { atomicExch(err, 3); return; }
+    for (int c = 0; c < cols; c++) out[(r - in_lo) * cols + c] = src[c];
+}
+
+void shard_place_rows(const float *recs, int64_t n, int R, int64_t in_lo, int64_t in_hi, float *out, int *d_err, cudaStream_t s) {
+    if (n <= 0) return;
+    place_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(recs, n, R, in_lo, in_hi, out, d_err);
+    F3M_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------------------
 // slices of equal estimated work
 // ---------------------------------------------------------------------------------------------
 // one warp per target box of a level: estimated cost of its direct lists and of its far row, added to the
@@ -139,7 +297,7 @@ __global__ void __launch_bounds__(256) box_work_kernel(int nbx, const int *__res
                                                       const int *__restrict__ ptr_a, const int *__restrict__ idx_a,
                                                       const int *__restrict__ ptr_b, const int *__restrict__ idx_b,
                                                       const int *__restrict__ far_ptr, double w_pair, double w_far, double w_point,
-                                                      int nb_fine, const int *__restrict__ off_fine, double *work) {
+                                                      int nb_fine, const int *__restrict__ off_fine, unsigned long long *work) {
     const int lane = threadIdx.x & 31;
     const int box = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (box >= nbx) return;
@@ -154,31 +312,32 @@ __global__ void __launch_bounds__(256) box_work_kernel(int nbx, const int *__res
     const double nx = (double)(off_x[box + 1] - off_x[box]);
     double w = w_pair * nx * (double)ny + w_point * nx;
     if (far_ptr) w += w_far * (double)(far_ptr[box + 1] - far_ptr[box]);
-    if (w > 0.0) atomicAdd(&work[lower_bound_i32(off_fine, nb_fine, off_x[box])], w);
+    // integer units: the sums must come out identical on every rank, whatever order the atomics run in
+    if (w > 0.0) atomicAdd(&work[lower_bound_i32(off_fine, nb_fine, off_x[box])], (unsigned long long)llrint(w) + 1ull);
 }
 
 // one block: running sum of the work over the finest-level boxes, cuts where it passes k / nparts of the total
-__global__ void __launch_bounds__(1024) partition_kernel(int nb, const double *__restrict__ work, const int *__restrict__ off,
-                                                        int nparts, long long *bounds) {
-    __shared__ double part[1024];
-    __shared__ double total_s;
+__global__ void __launch_bounds__(1024) partition_kernel(int nb, const unsigned long long *__restrict__ work,
+                                                        const int *__restrict__ off, int nparts, long long *bounds) {
+    __shared__ unsigned long long part[1024];
+    __shared__ unsigned long long total_s;
     const int per = (nb + 1023) / 1024;
     const int j0 = min(nb, (int)threadIdx.x * per), j1 = min(nb, j0 + per);
-    double s = 0.0;
+    unsigned long long s = 0;
     for (int j = j0; j < j1; j++) s += work[j];
     part[threadIdx.x] = s;
     __syncthreads();
     if (threadIdx.x == 0) {
-        double run = 0.0;
-        for (int t = 0; t < 1024; t++) { const double v = part[t]; part[t] = run; run += v; }
+        unsigned long long run = 0;
+        for (int t = 0; t < 1024; t++) { const unsigned long long v = part[t]; part[t] = run; run += v; }
         total_s = run;
         bounds[0] = 0;
         bounds[nparts] = off[nb];
         for (int k = 1; k < nparts; k++) bounds[k] = -1;
     }
     __syncthreads();
-    const double total = total_s;
-    if (total <= 0.0) {   // no work estimate (no lists): even row counts
+    const unsigned long long total = total_s;
+    if (total == 0) {   // no work estimate (no lists): even row counts
         if (threadIdx.x == 0)
             for (int k = 1; k < nparts; k++) {
                 const int target = (int)(((long long)off[nb] * k) / nparts);
@@ -186,15 +345,13 @@ __global__ void __launch_bounds__(1024) partition_kernel(int nb, const double *_
             }
         return;
     }
-    // the same additions as above, so that the sum at the end of a thread's boxes equals the next thread's start
-    const double base = part[threadIdx.x];
-    double loc = 0.0;
+    unsigned long long run = part[threadIdx.x];
     for (int j = j0; j < j1; j++) {
-        const double before = base + loc;
-        loc += work[j];
-        const double after = base + loc;
-        // cut k lies after box j when the running sum passes k * total / nparts inside this box
-        const int k0 = (int)floor(before * nparts / total), k1 = (int)floor(after * nparts / total);
+        const unsigned long long before = run;
+        run += work[j];
+        // cut k lies after box j when the running sum passes k * total / nparts inside this box (the sums are integers,
+        // so every rank computes the same cuts from the same plan)
+        const int k0 = (int)((double)before * nparts / (double)total), k1 = (int)((double)run * nparts / (double)total);
         for (int k = k0 + 1; k <= k1 && k < nparts; k++) bounds[k] = off[j + 1];
     }
 }
@@ -207,7 +364,7 @@ void shard_partition(f3m_plan *pl, int R, int nparts, int64_t *h_bounds, cudaStr
         return;
     }
     Level &lf = tx.levels[L];
-    DevBuf<double> work;
+    DevBuf<unsigned long long> work;
     work.alloc((size_t)lf.nb, s);
     work.zero();
     // cost per unit, relative to one direct pair of one column in three dimensions (measured on the N = 1e8 uniform

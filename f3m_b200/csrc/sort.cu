@@ -306,6 +306,7 @@ template <> struct VecOf<4> { typedef uint4 type; };
 struct SortIO {
     const uint32_t *kin;       // keys of this pass's input order
     const float *X;            // first pass: the caller's row-major points (the record is built from them)
+    int row0;                  // first pass: the record's row is row0 + position
     const void *rin;           // later passes: records of the input order
     uint32_t *kout;
     void *rout;                // records of the output order
@@ -317,9 +318,9 @@ __host__ __device__ constexpr size_t rs_smem_bytes(int nbins, int rec_words) {
     return (size_t)RS_W * nbins * 2 + (size_t)2 * nbins * 4 + (size_t)RS_TILE * 4 + (size_t)RS_TILE * rec_words * 4;
 }
 
-// STABLE = false: the rank of a key among the tile's keys of its digit is whatever order the shared-memory atomics
-// grant.  That is enough for the FIRST pass (nothing is ordered yet: points that agree in every sorted bit lie in
-// one finest-level box, where their order does not matter); every later pass must keep the order of its input.
+// STABLE = false ranks a key among the tile's keys of its digit in whatever order the shared-memory atomics grant.
+// That would do for a first pass on one GPU (points that agree in every sorted bit lie in one finest-level box), but
+// the order then differs from run to run, so the host uses the stable form for every pass.
 template <int D, bool STABLE>
 __global__ void __launch_bounds__(RS_T, 3) rs_scatter(SortIO io, int64_t n, int shift, int dbits, int64_t chunk,
                                                   const int *__restrict__ rowex, const int *__restrict__ tot, int G) {
@@ -378,7 +379,7 @@ __global__ void __launch_bounds__(RS_T, 3) rs_scatter(SortIO io, int64_t n, int 
 #pragma unroll
                 for (int q = 0; q < RW; q++) wds[q] = 0u;
                 if (j < tile_cnt) {
-                    wds[0] = (uint32_t)(tile + j);
+                    wds[0] = (uint32_t)(io.row0 + tile + j);
 #pragma unroll
                     for (int k = 0; k < D; k++) wds[1 + k] = __float_as_uint(xin[j * D + k]);
                 }
@@ -573,10 +574,11 @@ __global__ void __launch_bounds__(256) unpack_records(const void *__restrict__ r
     for (int c = 0; c < D; c++) pts[(size_t)c * n + i] = __uint_as_float(wds[1 + c]);
 }
 
+// keys and records [row0 + position, coordinates] of n points, sorted by the key bits [shift0, shift0 + bits)
 template <int D>
-static void sort_passes(Tree &t, const float *X, const MortonCfg &cfg, int shift0, int bits, cudaStream_t s) {
+static void sort_records(const float *X, int64_t n, int row0, const MortonCfg &cfg, int shift0, int bits, DevBuf<uint32_t> &keys_out,
+                         DevBuf<uint32_t> &recs_out, cudaStream_t s) {
     constexpr int RW = Rec<D>::VW * Rec<D>::RV;
-    const int64_t n = t.n;
     const int passes = (bits + RS_MAXBITS - 1) / RS_MAXBITS;
     const int dbits_all = (bits + passes - 1) / passes;
     const size_t smem = rs_smem_bytes(1 << dbits_all, RW);
@@ -585,7 +587,6 @@ static void sort_passes(Tree &t, const float *X, const MortonCfg &cfg, int shift
     F3M_CUDA(cudaGetDevice(&dev));
     F3M_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     F3M_CUDA(cudaFuncSetAttribute(rs_scatter<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    F3M_CUDA(cudaFuncSetAttribute(rs_scatter<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     F3M_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, rs_scatter<D, true>, RS_T, smem));
     const int64_t ntiles = (n + RS_TILE - 1) / RS_TILE;
     const int64_t wave = (int64_t)sms * std::max(1, occ);
@@ -598,8 +599,6 @@ static void sort_passes(Tree &t, const float *X, const MortonCfg &cfg, int shift
     kA.alloc(n, s); kB.alloc(n, s);
     rB.alloc((size_t)n * RW, s);
     if (passes > 1) rA.alloc((size_t)n * RW, s);
-    t.perm.alloc(n, s);
-    t.pts.alloc((size_t)n * D, s);
     counts.alloc((size_t)RS_MAXBINS * G, s);
     tot.alloc(RS_MAXBINS, s);
 
@@ -614,18 +613,181 @@ static void sort_passes(Tree &t, const float *X, const MortonCfg &cfg, int shift
         F3M_LAUNCH_CHECK();
         SortIO io{};
         io.first = pass == 0;
+        io.row0 = row0;
         io.kin = to_b ? kA.p : kB.p;
         io.kout = to_b ? kB.p : kA.p;
         io.X = X;
         io.rin = to_b ? rA.p : rB.p;
         io.rout = to_b ? rB.p : rA.p;
-        if (pass == 0) rs_scatter<D, false><<<G, RS_T, rs_smem_bytes(1 << dbits, RW), s>>>(io, n, shift, dbits, chunk, counts.p, tot.p, G);
-        else rs_scatter<D, true><<<G, RS_T, rs_smem_bytes(1 << dbits, RW), s>>>(io, n, shift, dbits, chunk, counts.p, tot.p, G);
+        // every pass stable, the first one too: ranks that build the same plan on different GPUs must end with the same
+        // permutation (their sorted slices are exchanged), and the form ranked by atomics measured no faster
+        rs_scatter<D, true><<<G, RS_T, rs_smem_bytes(1 << dbits, RW), s>>>(io, n, shift, dbits, chunk, counts.p, tot.p, G);
         F3M_LAUNCH_CHECK();
     }
-    unpack_records<D><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(passes % 2 == 1 ? rB.p : rA.p, n, t.perm.p, t.pts.p);
+    keys_out = std::move(passes % 2 == 1 ? kB : kA);
+    recs_out = std::move(passes % 2 == 1 ? rB : rA);
+}
+
+template <int D>
+static void sort_passes(Tree &t, const float *X, const MortonCfg &cfg, int shift0, int bits, cudaStream_t s) {
+    const int64_t n = t.n;
+    DevBuf<uint32_t> recs;
+    sort_records<D>(X, n, 0, cfg, shift0, bits, t.keys, recs, s);
+    t.perm.alloc(n, s);
+    t.pts.alloc((size_t)n * D, s);
+    unpack_records<D><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(recs.p, n, t.perm.p, t.pts.p);
     F3M_LAUNCH_CHECK();
-    t.keys = std::move(passes % 2 == 1 ? kB : kA);
+}
+
+static MortonCfg morton_cfg(int d, const float *origin, float edge0, int math_mode) {
+    MortonCfg cfg{};
+    for (int k = 0; k < d; k++) cfg.org[k] = origin[k];
+    cfg.L = std::min(30 / d, 20);
+    cfg.side = (float)(1u << cfg.L);
+    cfg.edge0 = edge0;
+    cfg.ieee = math_mode == F3M_MATH_IEEE;
+    return cfg;
+}
+
+int record_words(int d) {
+    switch (d) {
+        case 1: return Rec<1>::VW * Rec<1>::RV;
+        case 2: return Rec<2>::VW * Rec<2>::RV;
+        case 3: return Rec<3>::VW * Rec<3>::RV;
+        case 4: return Rec<4>::VW * Rec<4>::RV;
+        default: return Rec<5>::VW * Rec<5>::RV;
+    }
+}
+
+// One rank's share of a sort that several GPUs do together: keys and records of the n points of X (rows row0 ...
+// of the whole set), sorted by the first `depth` levels, into the caller's arrays.
+void sort_shard(const float *X, int64_t n, int64_t row0, int d, const float *origin, float edge0, int math_mode, int depth,
+                uint32_t *keys_out, uint32_t *recs_out, cudaStream_t s) {
+    F3M_REQUIRE(row0 + n < (int64_t)0x7fffffff, F3M_ERR_OVERFLOW, "row %lld does not fit a 31-bit index", (long long)(row0 + n));
+    const MortonCfg cfg = morton_cfg(d, origin, edge0, math_mode);
+    depth = std::max(1, std::min(depth, cfg.L));
+    const int shift0 = d * (cfg.L - depth), bits = d * depth;
+    DevBuf<uint32_t> keys, recs;
+    switch (d) {
+        case 1: sort_records<1>(X, n, (int)row0, cfg, shift0, bits, keys, recs, s); break;
+        case 2: sort_records<2>(X, n, (int)row0, cfg, shift0, bits, keys, recs, s); break;
+        case 3: sort_records<3>(X, n, (int)row0, cfg, shift0, bits, keys, recs, s); break;
+        case 4: sort_records<4>(X, n, (int)row0, cfg, shift0, bits, keys, recs, s); break;
+        default: sort_records<5>(X, n, (int)row0, cfg, shift0, bits, keys, recs, s); break;
+    }
+    F3M_CUDA(cudaMemcpyAsync(keys_out, keys.p, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
+    F3M_CUDA(cudaMemcpyAsync(recs_out, recs.p, (size_t)n * record_words(d) * 4, cudaMemcpyDeviceToDevice, s));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Merge of sorted runs (one per rank, all-gathered) into the tree's sorted arrays.  Every run is sorted by the same
+// key bits, so the points of one finest-sorted cell form one segment per run; the merged order is cell by cell,
+// run by run -- the same on every rank.  One pass marks the segment ends of every run in a dense (run, cell) table,
+// a scan over the cells gives the merged offsets, and one warp per cell copies its segments (records taken apart
+// into permutation and coordinate planes on the way).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) run_segments_kernel(const uint32_t *__restrict__ keys, int64_t stride, int nruns,
+                                                          const int64_t *__restrict__ run_counts, int shift0, int ncells,
+                                                          int *seg_start, int *seg_end) {
+    const int r = blockIdx.y;
+    const int64_t cnt = run_counts[r];
+    const uint32_t *k = keys + (size_t)r * stride;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < cnt; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t c = k[i] >> shift0;
+        if (i == 0 || (k[i - 1] >> shift0) != c) seg_start[(size_t)r * ncells + c] = (int)i;
+        if (i == cnt - 1 || (k[i + 1] >> shift0) != c) seg_end[(size_t)r * ncells + c] = (int)i + 1;
+    }
+}
+
+__global__ void __launch_bounds__(256) cell_totals_kernel(int ncells, int nruns, const int *__restrict__ seg_start,
+                                                         const int *__restrict__ seg_end, int *total) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c > ncells) return;
+    int t = 0;
+    if (c < ncells)
+        for (int r = 0; r < nruns; r++) t += seg_end[(size_t)r * ncells + c] - seg_start[(size_t)r * ncells + c];
+    total[c] = t;   // entry ncells = 0: the scan turns it into the grand total
+}
+
+template <int D>
+__global__ void __launch_bounds__(256) merge_runs_kernel(const uint32_t *__restrict__ keys, const void *__restrict__ recs,
+                                                        int64_t stride, int nruns, int ncells, const int *__restrict__ seg_start,
+                                                        const int *__restrict__ seg_end, const int *__restrict__ cell_off, int64_t n,
+                                                        uint32_t *keys_out, int *perm, float *pts) {
+    constexpr int VW = Rec<D>::VW, RV = Rec<D>::RV, RW = VW * RV;
+    typedef typename VecOf<VW>::type vec_t;
+    const int lane = threadIdx.x & 31;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (c >= ncells) return;
+    int dst = cell_off[c];
+    if (cell_off[c + 1] == dst) return;
+    for (int r = 0; r < nruns; r++) {
+        const int a = seg_start[(size_t)r * ncells + c], b = seg_end[(size_t)r * ncells + c];
+        const uint32_t *k = keys + (size_t)r * stride;
+        const vec_t *rc = reinterpret_cast<const vec_t *>(recs) + (size_t)r * stride * RV;
+        for (int i = a + lane; i < b; i += 32) {
+            const int o = dst + (i - a);
+            uint32_t wds[RW];
+#pragma unroll
+            for (int v = 0; v < RV; v++) {
+                const vec_t t = rc[(size_t)i * RV + v];
+                const uint32_t *tw = reinterpret_cast<const uint32_t *>(&t);
+#pragma unroll
+                for (int q = 0; q < VW; q++) wds[VW * v + q] = tw[q];
+            }
+            keys_out[o] = k[i];
+            perm[o] = (int)wds[0];
+#pragma unroll
+            for (int q = 0; q < D; q++) pts[(size_t)q * n + o] = __uint_as_float(wds[1 + q]);
+        }
+        dst += b - a;
+    }
+}
+
+void build_tree_from_runs(Tree &t, const uint32_t *keys, const uint32_t *recs, const int64_t *h_run_counts, int nruns, int64_t stride,
+                          int d, const float *origin, float edge0, int depth, cudaStream_t s) {
+    int64_t n = 0;
+    for (int r = 0; r < nruns; r++) {
+        F3M_REQUIRE(h_run_counts[r] >= 0 && h_run_counts[r] <= stride, F3M_ERR_ARG, "run %d holds %lld points, runs lie %lld apart", r,
+                    (long long)h_run_counts[r], (long long)stride);
+        n += h_run_counts[r];
+    }
+    F3M_REQUIRE(n > 0 && n < (int64_t)0x7fffffff, F3M_ERR_OVERFLOW, "point count %lld does not fit a 31-bit index", (long long)n);
+    t.n = n;
+    t.d = d;
+    t.data = nullptr;   // the points exist as runs only: this tree cannot be sorted again to a greater depth
+    t.edge0 = edge0;
+    for (int k = 0; k < d; k++) t.origin[k] = origin[k];
+    t.lmax = std::min(30 / d, 20);
+    depth = std::max(1, std::min(depth, t.lmax));
+    F3M_REQUIRE(d * depth <= 22, F3M_ERR_UNSUPPORTED, "runs sorted by %d key bits: the merge tabulates at most 22", d * depth);
+    t.sorted_depth = depth;
+    const int shift0 = d * (t.lmax - depth), ncells = 1 << (d * depth);
+    DevBuf<int> seg_start, seg_end, cell_off;
+    DevBuf<int64_t> counts;
+    seg_start.alloc((size_t)nruns * ncells, s); seg_end.alloc((size_t)nruns * ncells, s); cell_off.alloc((size_t)ncells + 1, s);
+    seg_start.zero(); seg_end.zero();
+    counts.alloc(nruns, s);
+    F3M_CUDA(cudaMemcpyAsync(counts.p, h_run_counts, nruns * sizeof(int64_t), cudaMemcpyHostToDevice, s));
+    int64_t longest = 0;
+    for (int r = 0; r < nruns; r++) longest = std::max(longest, h_run_counts[r]);
+    const unsigned gx = (unsigned)std::max<int64_t>(1, std::min<int64_t>((longest + 255) / 256, NUM_SMS_HINT * 16));
+    run_segments_kernel<<<dim3(gx, nruns), 256, 0, s>>>(keys, stride, nruns, counts.p, shift0, ncells, seg_start.p, seg_end.p);
+    F3M_LAUNCH_CHECK();
+    cell_totals_kernel<<<(unsigned)((ncells + 1 + 255) / 256), 256, 0, s>>>(ncells, nruns, seg_start.p, seg_end.p, cell_off.p);
+    F3M_LAUNCH_CHECK();
+    exclusive_scan_i32(cell_off.p, cell_off.p, (int64_t)ncells + 1, s);
+    t.keys.alloc(n, s); t.perm.alloc(n, s); t.pts.alloc((size_t)n * d, s);
+    const unsigned gm = (unsigned)(((int64_t)ncells * 32 + 255) / 256);
+    switch (d) {
+        case 1: merge_runs_kernel<1><<<gm, 256, 0, s>>>(keys, recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, t.keys.p, t.perm.p, t.pts.p); break;
+        case 2: merge_runs_kernel<2><<<gm, 256, 0, s>>>(keys, recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, t.keys.p, t.perm.p, t.pts.p); break;
+        case 3: merge_runs_kernel<3><<<gm, 256, 0, s>>>(keys, recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, t.keys.p, t.perm.p, t.pts.p); break;
+        case 4: merge_runs_kernel<4><<<gm, 256, 0, s>>>(keys, recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, t.keys.p, t.perm.p, t.pts.p); break;
+        default: merge_runs_kernel<5><<<gm, 256, 0, s>>>(keys, recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, t.keys.p, t.perm.p, t.pts.p); break;
+    }
+    F3M_LAUNCH_CHECK();
+    F3M_CUDA(cudaStreamSynchronize(s));   // h_run_counts is the caller's host array
 }
 
 // Sorts the points of one tree by the first `depth` levels of their Morton key (all later levels are read off the
@@ -643,12 +805,7 @@ void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *o
     depth = std::max(1, std::min(depth, t.lmax));
     t.sorted_depth = depth;
     t.keys.release(); t.perm.release(); t.pts.release();   // a second sort (deeper) replaces the first
-    MortonCfg cfg{};
-    for (int k = 0; k < d; k++) cfg.org[k] = origin[k];
-    cfg.side = (float)(1u << t.lmax);
-    cfg.edge0 = edge0;
-    cfg.L = t.lmax;
-    cfg.ieee = math_mode == F3M_MATH_IEEE;
+    const MortonCfg cfg = morton_cfg(d, origin, edge0, math_mode);
     const int shift0 = d * (t.lmax - depth), bits = d * depth;
     switch (d) {
         case 1: sort_passes<1>(t, X, cfg, shift0, bits, s); break;

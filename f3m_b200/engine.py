@@ -41,8 +41,59 @@ def make_params(ls, min_points, nr_of_interpolation, var_compression, eff_var_li
                   float(eff_var_limit), int(small_field_points), int(math_mode), int(flags))
 
 
+def bounding_box(X: torch.Tensor):
+    """Per-dimension minimum and maximum of the points (two lists of d floats; f3m_bounding_box_f32)."""
+    X = _as_f32(X)
+    d = X.shape[1]
+    lo, hi = (C.c_float * d)(), (C.c_float * d)()
+    with torch.cuda.device(X.device):
+        check(_lib.lib().f3m_bounding_box_f32(X.data_ptr(), X.shape[0], d, lo, hi, _stream_ptr(X.device)), "f3m_bounding_box_f32")
+    return list(lo), list(hi)
+
+
+def sort_depth(n_total: int, d: int, min_points: float) -> int:
+    return int(_lib.lib().f3m_sort_depth(int(n_total), int(d), float(min_points)))
+
+
+def sort_shard(X: torch.Tensor, row_offset: int, origin, edge0: float, math_mode: int, depth: int):
+    """One rank's share of a sort done by several GPUs (f3m_sort_shard_f32): (keys (n,) int32 bits, records (n, words))."""
+    X = _as_f32(X)
+    n, d = X.shape
+    words = int(_lib.lib().f3m_record_words(d))
+    keys = torch.empty(n, device=X.device, dtype=torch.int32)
+    recs = torch.empty(n, words, device=X.device, dtype=torch.int32)
+    org = (C.c_float * d)(*[float(v) for v in origin])
+    with torch.cuda.device(X.device):
+        check(_lib.lib().f3m_sort_shard_f32(X.data_ptr(), n, int(row_offset), d, org, C.c_float(edge0), int(math_mode), int(depth),
+                                            keys.data_ptr(), recs.data_ptr(), _stream_ptr(X.device)), "f3m_sort_shard_f32")
+    return keys, recs
+
+
 class Plan:
     """Tree and interaction lists of one (X, Y) pair (f3m_plan); apply() multiplies by any b."""
+
+    @classmethod
+    def from_runs(cls, keys: torch.Tensor, recs: torch.Tensor, run_counts, run_stride: int, d: int, origin, edge0: float,
+                  depth: int, params: Params) -> "Plan":
+        """The plan of all points (Y = X) from runs that several GPUs sorted (f3m_plan_create_from_runs)."""
+        self = cls.__new__(cls)
+        self.X = self.Y = None
+        self.same = True
+        self.params = params
+        self.device = keys.device
+        self.N = self.M = int(sum(run_counts))
+        self.d = d
+        self._h = C.c_void_p()
+        self._runs = (keys, recs)
+        counts = (C.c_int64 * len(run_counts))(*[int(c) for c in run_counts])
+        org = (C.c_float * d)(*[float(v) for v in origin])
+        with torch.cuda.device(self.device):
+            st = _lib.lib().f3m_plan_create_from_runs(C.byref(self._h), keys.data_ptr(), recs.data_ptr(), counts, len(run_counts),
+                                                      int(run_stride), d, org, C.c_float(edge0), int(depth), C.byref(params),
+                                                      _stream_ptr(self.device))
+        self._runs = None    # the plan holds its own sorted copy
+        check(st, "f3m_plan_create_from_runs")
+        return self
 
     def __init__(self, X: torch.Tensor, Y: Optional[torch.Tensor], params: Params):
         if not X.is_cuda:
@@ -150,6 +201,46 @@ class Plan:
         with torch.cuda.device(self.device):
             check(_lib.lib().f3m_plan_rows_to_input_order(self._h, acc_sorted.data_ptr(), R, int(in_lo), int(in_hi), out.data_ptr(),
                                                           _stream_ptr(self.device)), "f3m_plan_rows_to_input_order")
+        return out
+
+    def gathered_rows_to_input_order(self, gathered: torch.Tensor, slice_bounds, stride: int, in_lo: int, in_hi: int) -> torch.Tensor:
+        """Rows in_lo..in_hi of the product in input order from the all-gathered slices (slice g at row g * stride)."""
+        R = gathered.shape[1]
+        nr = len(slice_bounds) - 1
+        cuts = (C.c_int64 * (nr + 1))(*[int(v) for v in slice_bounds])
+        out = torch.empty(in_hi - in_lo, R, device=self.device, dtype=torch.float32)
+        with torch.cuda.device(self.device):
+            check(_lib.lib().f3m_plan_gathered_rows_to_input_order(self._h, gathered.data_ptr(), R, cuts, nr, int(stride), int(in_lo),
+                                                                   int(in_hi), out.data_ptr(), _stream_ptr(self.device)),
+                  "f3m_plan_gathered_rows_to_input_order")
+        return out
+
+    def rows_by_owner(self, acc_sorted: torch.Tensor, row_range, in_bounds):
+        """The rows [row_range) of the sorted result as records [values, input row] grouped by the rank that owns the
+        input row (rank g owns input rows in_bounds[g]..in_bounds[g+1]): (send buffer (rows, R + 1), counts per rank)."""
+        nr = len(in_bounds) - 1
+        R = acc_sorted.shape[1]
+        cuts = (C.c_int64 * (nr + 1))(*[int(v) for v in in_bounds])
+        counts = (C.c_int64 * nr)()
+        rb, re = int(row_range[0]), int(row_range[1])
+        with torch.cuda.device(self.device):
+            check(_lib.lib().f3m_plan_count_rows_by_owner(self._h, rb, re, cuts, nr, counts, _stream_ptr(self.device)),
+                  "f3m_plan_count_rows_by_owner")
+            send = torch.empty(re - rb, R + 1, device=self.device, dtype=torch.float32)
+            if re > rb:
+                check(_lib.lib().f3m_plan_pack_rows_by_owner(self._h, acc_sorted.data_ptr(), R, rb, re, cuts, nr, counts, send.data_ptr(),
+                                                             _stream_ptr(self.device)), "f3m_plan_pack_rows_by_owner")
+        return send, [int(v) for v in counts]
+
+    def place_rows(self, records: torch.Tensor, in_lo: int, in_hi: int) -> torch.Tensor:
+        """Received records [values, input row] -> the rows in_lo..in_hi of the product in input order."""
+        R = records.shape[1] - 1
+        out = torch.empty(in_hi - in_lo, R, device=self.device, dtype=torch.float32)
+        if records.shape[0] == 0:
+            return out
+        with torch.cuda.device(self.device):
+            check(_lib.lib().f3m_plan_place_rows(self._h, records.data_ptr(), records.shape[0], R, int(in_lo), int(in_hi), out.data_ptr(),
+                                                 _stream_ptr(self.device)), "f3m_plan_place_rows")
         return out
 
     def finest_boxes(self):

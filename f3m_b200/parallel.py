@@ -4,14 +4,17 @@ The reference's multi-GPU mode is one independent process per block of K with no
 (par_FFM_block, experiments/FFM_classes.py:128-211; experiment_utils/scalability_analysis.sh).  Here every rank
 holds a shard of the points and of b and gets back the rows of the product that belong to its shard:
 
-  1. all-gather the shards of X (NCCL over NVLink); the all-gather of b runs while the tree is built;
-  2. every rank builds the same tree and interaction lists (a few milliseconds next to the sums);
+  1. every rank sorts its own shard of the points inside the global bounding cube; the sorted runs are all-gathered
+     (NCCL over NVLink) and merged, cell by cell, into the same sorted arrays on every rank; the all-gather of b runs
+     meanwhile (strongly clustered sets, whose tree goes deeper than the shards are sorted: all-gather of the points
+     and a sort on every rank);
+  2. every rank builds the same levels and interaction lists (about two milliseconds);
   3. the sorted target rows are cut into one slice per rank of equal estimated work (f3m_plan_partition_rows);
   4. each rank interpolates an equal share of the source boxes onto the finest-level nodes; the moment slices are
      all-gathered while the rank computes the direct sums of its slice (it packs only the source boxes its own
      lists name: its slice plus a halo);
   5. far field of the slice from the gathered moments; nothing but the rank's own rows is written;
-  6. the sorted slices are all-gathered and each rank takes the rows of its own shard, in input order.
+  6. all-to-all: every computed row goes to the rank that owns its input row, which puts it in input order.
 
 No kernel reads another GPU's memory: remote data always lands in local HBM through NCCL first.
 """
@@ -62,12 +65,82 @@ def gather_shards(x_shard: torch.Tensor, counts: List[int], group=None, async_op
     return finish if async_op else finish()
 
 
+_UNEVEN_ALL_GATHER = {"ok": None}   # does this backend's all_gather take pieces of different lengths?
+
+
+def _gather_slices_in_place(acc: torch.Tensor, bounds: List[int], rank: int, group):
+    """Every rank's slice acc[bounds[r]:bounds[r+1]] to every rank.  On CUDA tensors the list form of all_gather takes
+    the slices as they lie in acc (NCCL: one grouped broadcast per rank, no staging copy); backends that want equal
+    pieces get the padded form."""
+    world = len(bounds) - 1
+    mine = acc[bounds[rank]:bounds[rank + 1]]
+    if acc.is_cuda and _UNEVEN_ALL_GATHER["ok"] is not False:
+        try:
+            dist.all_gather([acc[bounds[r]:bounds[r + 1]] for r in range(world)], mine, group=group)
+            _UNEVEN_ALL_GATHER["ok"] = True
+            return acc
+        except (RuntimeError, ValueError):   # raised at argument checking, on every rank alike
+            if _UNEVEN_ALL_GATHER["ok"]:
+                raise
+            _UNEVEN_ALL_GATHER["ok"] = False
+    return gather_shards(mine, [bounds[r + 1] - bounds[r] for r in range(world)], group)
+
+
+def gather_runs(t_shard: torch.Tensor, counts: List[int], group=None, async_op: bool = False):
+    """All-gather row shards WITHOUT closing the gaps: rank r's rows start at row r * max(counts) of the result.
+    Returns (buffer, stride) -- with async_op a function that waits and returns them."""
+    mx = max(counts)
+    t_shard = t_shard.contiguous()
+    if t_shard.shape[0] != mx:
+        padded = torch.zeros(mx, *t_shard.shape[1:], dtype=t_shard.dtype, device=t_shard.device)
+        padded[:t_shard.shape[0]] = t_shard
+        t_shard = padded
+    buf = torch.empty(len(counts) * mx, *t_shard.shape[1:], dtype=t_shard.dtype, device=t_shard.device)
+    work = _all_gather_equal(buf, t_shard, group, async_op)
+
+    def finish():
+        work.wait()
+        return buf, mx
+    return finish if async_op else (buf, mx)
+
+
 class EngineBackend:
     """The CUDA engine behind the phases of distributed_kmvm (a test may pass a stand-in with the same methods)."""
 
     def plan(self, X: torch.Tensor, params):
         from . import engine
         return engine.Plan(X, None, params)
+
+    def plan_from_shards(self, x_shard: torch.Tensor, counts: List[int], rank: int, params, group):
+        """The plan of all points with the sort shared by the ranks: global bounding cube (two tiny all-reduces), every
+        rank sorts its shard, the sorted runs are all-gathered and merged.  None when that form does not apply (the
+        level loop would need more levels than the shards were sorted to): the caller gathers the points instead."""
+        import numpy as np
+        from . import engine
+        from ._lib import F3MError
+        dev, d, N = x_shard.device, x_shard.shape[1], sum(counts)
+        if min(counts) < 1:
+            return None
+        lo, hi = engine.bounding_box(x_shard)
+        box = torch.tensor([lo, [-v for v in hi]], device=dev, dtype=torch.float32)
+        dist.all_reduce(box, op=dist.ReduceOp.MIN, group=group)
+        box = box.cpu().numpy()
+        origin, top = box[0], -box[1]
+        edge0 = float(np.float32((top - origin).max()) * np.float32(1.01))     # calculate_edge_X, float32
+        if not (np.isfinite(edge0) and edge0 > 0):
+            return None    # the single-GPU path reports degenerate or non-finite point sets
+        depth = engine.sort_depth(N, d, params.min_points)
+        if d * depth > 22:
+            return None
+        keys, recs = engine.sort_shard(x_shard, sum(counts[:rank]), origin, edge0, params.math_mode, depth)
+        keys_all, stride = gather_runs(keys, counts, group)
+        recs_all, _ = gather_runs(recs, counts, group)
+        try:
+            return engine.Plan.from_runs(keys_all, recs_all, counts, stride, d, origin, edge0, depth, params)
+        except F3MError as e:
+            if e.status == 5:     # F3M_ERR_UNSUPPORTED: deeper than the shards were sorted (the same on every rank)
+                return None
+            raise
 
 
 class _Clock:
@@ -112,12 +185,22 @@ def distributed_kmvm(x_shard: torch.Tensor, b_shard: torch.Tensor, params, group
     in_hi = in_lo + counts[rank]
     R = b_shard.shape[1]
 
-    X = gather_shards(x_shard, counts, group)
     b_wait = gather_shards(b_shard, counts, group, async_op=True)    # lands while the tree is built
-    clock.mark("gather_points")
-    plan = backend.plan(X, params)
+    plan = None
+    if world > 1 and hasattr(backend, "plan_from_shards"):
+        plan = backend.plan_from_shards(x_shard, counts, rank, params, group)
+    if plan is None:
+        X = gather_shards(x_shard, counts, group)
+        clock.mark("gather_points")
+        plan = backend.plan(X, params)
     clock.mark("tree_lists")
     bounds = plan.partition_rows(R, world)
+    if world > 1:
+        # every rank computes the same cuts from the same plan; rank 0's copy is the one used, so that a difference
+        # between the ranks could never leave a row without an owner
+        cuts = torch.tensor(bounds, device=dev, dtype=torch.int64)
+        dist.broadcast(cuts, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        bounds = [int(v) for v in cuts.tolist()]
     rb, re = bounds[rank], bounds[rank + 1]
     msize = plan.moments_size(R)
     _, nby = plan.finest_boxes()
@@ -146,10 +229,30 @@ def distributed_kmvm(x_shard: torch.Tensor, b_shard: torch.Tensor, params, group
     plan.shard_far(mom_full, acc)
     plan.shard_end()
     clock.mark("far_field")
-    if world > 1:
-        acc = gather_shards(acc[rb:re], [bounds[r + 1] - bounds[r] for r in range(world)], group)
-    clock.mark("gather_result")
-    out = plan.rows_to_input_order(acc, in_lo, in_hi)
+    if world > 1 and R <= 2 and hasattr(plan, "gathered_rows_to_input_order"):
+        # few columns: one all-gather of the slices (padded to the longest, left where they land), then every rank
+        # picks the rows of its own shard -- NCCL's all-gather moves these few hundred megabytes faster than an
+        # all-to-all moves an eighth of them
+        gathered, stride = gather_runs(acc[rb:re], [bounds[r + 1] - bounds[r] for r in range(world)], group)
+        clock.mark("exchange_rows")
+        out = plan.gathered_rows_to_input_order(gathered, bounds, stride, in_lo, in_hi)
+    elif world > 1:
+        # all-to-all: every row of the slice goes to the rank that owns its input row, with the row number beside it
+        in_bounds = [sum(counts[:r]) for r in range(world + 1)]
+        send, send_counts = plan.rows_by_owner(acc, (rb, re), in_bounds)
+        clock.mark("pack_rows")
+        mine = torch.tensor(send_counts, device=dev, dtype=torch.int64)
+        table = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(table, mine, group=group)
+        recv_counts = torch.stack(table)[:, rank].tolist()
+        assert sum(recv_counts) == in_hi - in_lo, "rows received do not add up to this rank's shard"
+        recv = torch.empty(in_hi - in_lo, R + 1, device=dev, dtype=torch.float32)
+        dist.all_to_all_single(recv, send, output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
+        clock.mark("exchange_rows")
+        out = plan.place_rows(recv, in_lo, in_hi)
+    else:
+        clock.mark("exchange_rows")
+        out = plan.rows_to_input_order(acc, in_lo, in_hi)
     clock.mark("own_rows")
     if stats is not None:
         stats["slice_rows"] = re - rb

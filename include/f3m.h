@@ -122,6 +122,28 @@ int f3m_plan_moments_range(f3m_plan *plan, const float *b, int32_t R, int64_t sr
 int f3m_plan_apply_range_moments(f3m_plan *plan, const float *b, int32_t R, float *out, int64_t row_begin,
                                  int64_t row_end, const float *mom, void *stream);
 
+/* A plan whose sort is shared by several GPUs (no counterpart in the reference).  Each rank sorts its own shard of
+ * the points inside the GLOBAL bounding cube (origin = per-dimension minimum over all ranks, edge0 = 1.01f * largest
+ * extent, both float32 as in calculate_edge_X, n_tree.cu:39-46) to the depth f3m_sort_depth gives for the TOTAL
+ * point count; the sorted runs (keys: uint32 per point; records: f3m_record_words(d) 32-bit words per point,
+ * [input row, coordinates]) are all-gathered, and every rank merges them into the same plan.
+ *   f3m_bounding_box_f32       per-dimension minimum and maximum of a shard (HOST arrays of d floats).
+ *   f3m_sort_shard_f32         keys_out (n), records_out (n records): the shard sorted; row_offset = input row of the
+ *                              shard's first point in the whole set.
+ *   f3m_plan_create_from_runs  keys / records hold nruns runs, run r at element r * run_stride with run_counts[r]
+ *                              points (HOST array).  The plan is that of f3m_plan_create on the whole set with Y = X,
+ *                              except for the order of the points inside a finest sorted cell.  If the level loop
+ *                              needs more levels than `depth` (strongly clustered points): F3M_ERR_UNSUPPORTED --
+ *                              build the plan from the gathered points instead. */
+int f3m_sort_depth(int64_t n_total, int32_t d, float min_points);
+int f3m_record_words(int32_t d);
+int f3m_bounding_box_f32(const float *X, int64_t n, int32_t d, float *min_out, float *max_out, void *stream);
+int f3m_sort_shard_f32(const float *X, int64_t n, int64_t row_offset, int32_t d, const float *origin, float edge0,
+                       int32_t math_mode, int32_t depth, uint32_t *keys_out, void *records_out, void *stream);
+int f3m_plan_create_from_runs(f3m_plan **plan, const uint32_t *keys, const void *records, const int64_t *run_counts,
+                              int32_t nruns, int64_t run_stride, int32_t d, const float *origin, float edge0, int32_t depth,
+                              const f3m_params *prm, void *stream);
+
 /* One product shared by several GPUs in phases, so that the exchange of the moments over NVLink runs while the
  * direct sums are computed (no counterpart in the reference: par_FFM_block runs independent block products,
  * experiments/FFM_classes.py:128-211).  Every rank holds the same plan (built from all points) and owns one slice
@@ -141,6 +163,14 @@ int f3m_plan_apply_range_moments(f3m_plan *plan, const float *b, int32_t R, floa
  *   f3m_plan_shard_end       releases what the phases kept in the plan.
  *   f3m_plan_rows_to_input_order  out[(r - in_lo)] = acc_sorted[position of input row r] for in_lo <= r < in_hi:
  *                            the rows of the (gathered) sorted result that belong to one range of input rows.
+ *   f3m_plan_gathered_rows_to_input_order  the same from the buffer an all-gather of the ranks' slices leaves: slice g
+ *                            (sorted rows slice_bounds[g] .. slice_bounds[g+1], HOST array) starts at row g * stride.
+ *   f3m_plan_count_rows_by_owner / f3m_plan_pack_rows_by_owner / f3m_plan_place_rows   the same without gathering
+ *                            the whole result: rank g owns the input rows [in_bounds[g], in_bounds[g+1]) (HOST array of
+ *                            nranks + 1 cuts).  count: how many rows of the slice [row_begin, row_end) belong to each
+ *                            rank (HOST array counts).  pack: those rows as records of R + 1 floats [values, input row
+ *                            as an integer's bits], grouped by owner in rank order -- the send buffer of an
+ *                            all-to-all.  place: received records into out[(input row - in_lo)].
  * A plan runs one sharded product at a time and must not be used from two host threads at once. */
 int f3m_plan_partition_rows(f3m_plan *plan, int32_t R, int32_t nparts, int64_t *bounds, void *stream);
 int f3m_plan_shard_begin(f3m_plan *plan, const float *b, int32_t R, int64_t row_begin, int64_t row_end, int64_t box_begin,
@@ -150,6 +180,14 @@ int f3m_plan_shard_far(f3m_plan *plan, const float *mom, float *acc_sorted, void
 int f3m_plan_shard_end(f3m_plan *plan);
 int f3m_plan_rows_to_input_order(const f3m_plan *plan, const float *acc_sorted, int32_t R, int64_t in_lo, int64_t in_hi,
                                  float *out, void *stream);
+int f3m_plan_gathered_rows_to_input_order(const f3m_plan *plan, const float *gathered, int32_t R, const int64_t *slice_bounds,
+                                          int32_t nslices, int64_t stride, int64_t in_lo, int64_t in_hi, float *out, void *stream);
+int f3m_plan_count_rows_by_owner(const f3m_plan *plan, int64_t row_begin, int64_t row_end, const int64_t *in_bounds,
+                                 int32_t nranks, int64_t *counts, void *stream);
+int f3m_plan_pack_rows_by_owner(const f3m_plan *plan, const float *acc_sorted, int32_t R, int64_t row_begin, int64_t row_end,
+                                const int64_t *in_bounds, int32_t nranks, const int64_t *counts, float *send, void *stream);
+int f3m_plan_place_rows(f3m_plan *plan, const float *records, int64_t n, int32_t R, int64_t in_lo, int64_t in_hi, float *out,
+                        void *stream);
 int f3m_plan_destroy(f3m_plan *plan);
 
 /* -------- introspection (parity checks and work accounting) ------------------------------ */

@@ -199,6 +199,19 @@ class _FakePlan:
     def shard_end(self):
         pass
 
+    def rows_by_owner(self, acc, row_range, in_bounds):
+        rb, re = row_range
+        rows = self.perm[rb:re]
+        owner = torch.bucketize(rows, torch.tensor(in_bounds[1:-1]), right=True)
+        order = torch.argsort(owner, stable=True)
+        send = torch.cat([acc[rb:re][order], rows[order, None].int().view(torch.float32)], 1)
+        return send.contiguous(), torch.bincount(owner, minlength=len(in_bounds) - 1).tolist()
+
+    def place_rows(self, recs, lo, hi):
+        out = torch.full((hi - lo, recs.shape[1] - 1), float("nan"))
+        out[recs[:, -1].contiguous().view(torch.int32).long() - lo] = recs[:, :-1]
+        return out
+
     def rows_to_input_order(self, acc, lo, hi):
         out = torch.empty(self.N, acc.shape[1])
         out[self.perm] = acc
@@ -208,9 +221,20 @@ class _FakePlan:
         pass
 
 
+class _FakePlanGather(_FakePlan):
+    """With the all-gather form of the result exchange (what the engine's plan offers for one or two columns)."""
+
+    def gathered_rows_to_input_order(self, gathered, slice_bounds, stride, lo, hi):
+        acc = torch.cat([gathered[g * stride:g * stride + slice_bounds[g + 1] - slice_bounds[g]] for g in range(len(slice_bounds) - 1)])
+        return self.rows_to_input_order(acc, lo, hi)
+
+
 class _FakeBackend:
+    def __init__(self, gather_form):
+        self.cls = _FakePlanGather if gather_form else _FakePlan
+
     def plan(self, X, params):
-        return _FakePlan(X, params)
+        return self.cls(X, params)
 
 
 def _rank_main(rank, world, port, q):
@@ -224,7 +248,7 @@ def _rank_main(rank, world, port, q):
     X, b = torch.rand(1001, 3, generator=g), torch.randn(1001, 2, generator=g)
     cuts = [0, 377, 1001] if world == 2 else [0, 200, 377, 1001]    # uneven shards
     lo, hi = cuts[rank], cuts[rank + 1]
-    out = distributed_kmvm(X[lo:hi], b[lo:hi], 0.5, backend=_FakeBackend())
+    out = distributed_kmvm(X[lo:hi], b[lo:hi], 0.5, backend=_FakeBackend(gather_form=(world == 2)))
     plan = _FakePlan(X, 0.5)
     bs = b[plan.perm]
     mom = torch.stack([bs[j * plan.BOX:(j + 1) * plan.BOX].sum(0) for j in range(plan.nb)])

@@ -558,3 +558,89 @@ def test_sharded_phases_equal_full_product(name, world, cuda):
     cut = plan.N // 3
     out = torch.cat([plan.rows_to_input_order(acc, 0, cut), plan.rows_to_input_order(acc, cut, plan.N)])
     assert rel_l2(out.cpu(), full.cpu()) <= 2e-6
+    # the all-gather form: slices at a fixed stride, as the collective leaves them
+    stride = max(bounds[r + 1] - bounds[r] for r in range(world))
+    gathered = torch.full((world * stride, R), float("nan"), device=cuda)
+    for r in range(world):
+        gathered[r * stride:r * stride + bounds[r + 1] - bounds[r]] = acc[bounds[r]:bounds[r + 1]]
+    assert torch.equal(plan.gathered_rows_to_input_order(gathered, bounds, stride, cut, plan.N), out[cut:])
+    # the all-to-all form of the same step: every slice's rows grouped by the owner of the input row, then placed
+    in_bounds = [0, plan.N // 5, plan.N // 2, plan.N][:world + 1] if world >= 3 else [0, plan.N // 3, plan.N]
+    owners = len(in_bounds) - 1
+    chunks = [[] for _ in range(owners)]
+    for r in range(world):
+        send, counts = plan.rows_by_owner(acc, (bounds[r], bounds[r + 1]), in_bounds)
+        assert sum(counts) == bounds[r + 1] - bounds[r] == send.shape[0]
+        pos = 0
+        for q, c_ in enumerate(counts):
+            chunks[q].append(send[pos:pos + c_])
+            pos += c_
+    for q in range(owners):
+        recv = torch.cat(chunks[q]).contiguous()
+        assert recv.shape[0] == in_bounds[q + 1] - in_bounds[q]
+        placed = plan.place_rows(recv, in_bounds[q], in_bounds[q + 1])
+        assert torch.equal(placed, out[in_bounds[q]:in_bounds[q + 1]])
+
+
+def test_plan_is_deterministic(cuda):
+    """Two plans of the same points hold the same permutation, bit for bit: ranks that build the plan on different GPUs
+    exchange slices of the SORTED result, so the order inside a box must not depend on the run."""
+    from f3m_b200 import engine, _lib
+    g = torch.Generator().manual_seed(61)
+    X = (torch.rand(400000, 3, generator=g) * 3).to(cuda)
+    prm = engine.make_params(1.0, 200.0, 64, False, 0.15, 64)
+    perms = []
+    for _ in range(3):
+        plan = engine.Plan(X, None, prm)
+        perms.append(plan.array(0, 0, _lib.ARR_SORTED_INDEX))
+        plan.close()
+    assert np.array_equal(perms[0], perms[1]) and np.array_equal(perms[0], perms[2])
+    assert np.array_equal(np.sort(perms[0]), np.arange(X.shape[0]))
+
+
+@pytest.mark.parametrize("name", ["u3_shared", "n4_r8", "u2_shared", "clustered3"])
+def test_plan_from_sorted_runs(name, cuda):
+    """The sort shared by several ranks, carried out on one GPU: three uneven shards are sorted separately inside the
+    global bounding cube, laid out as an all-gather would leave them (runs at a fixed stride, the short ones padded) and
+    merged.  Boxes, centres and interaction lists must equal those of the plan built from all points at once, and so
+    must the product (the two plans order the points inside a box differently)."""
+    import numpy as np
+    from f3m_b200 import engine, _lib
+    c = make_case(name)
+    prm = engine.make_params(c["ls"], c["min_points"], c["P"], c["var_comp"], c["eff"], c["small"])
+    X = c["X"].to(cuda)
+    b = c["b"].to(cuda)
+    N, d = X.shape
+    ref = engine.Plan(X, None, prm)
+    full = ref.apply(b)
+    cuts = [0, N // 5, N // 5 + N // 2, N]
+    counts = [cuts[i + 1] - cuts[i] for i in range(3)]
+    los, his = zip(*[engine.bounding_box(X[cuts[i]:cuts[i + 1]]) for i in range(3)])
+    origin = np.min(np.array(los, dtype=np.float32), 0)
+    top = np.max(np.array(his, dtype=np.float32), 0)
+    edge0 = float(np.float32((top - origin).max()) * np.float32(1.01))
+    assert abs(edge0 - ref.stats()["edge0"]) == 0.0
+    depth = engine.sort_depth(N, d, c["min_points"])
+    stride = max(counts)
+    words = _lib.lib().f3m_record_words(d)
+    keys_all = torch.zeros(3 * stride, device=cuda, dtype=torch.int32)
+    recs_all = torch.zeros(3 * stride, words, device=cuda, dtype=torch.int32)
+    for i in range(3):
+        k, r = engine.sort_shard(X[cuts[i]:cuts[i + 1]], cuts[i], origin, edge0, prm.math_mode, depth)
+        keys_all[i * stride:i * stride + counts[i]] = k
+        recs_all[i * stride:i * stride + counts[i]] = r
+    try:
+        plan = engine.Plan.from_runs(keys_all, recs_all, counts, stride, d, origin, edge0, depth, prm)
+    except _lib.F3MError as e:
+        assert e.status == 5 and ref.stats()["levels"] > depth     # deeper than the estimate: the documented refusal
+        return
+    L = ref.stats()["levels"]
+    assert plan.stats()["levels"] == L and plan.stats()["direct_pairs"] == ref.stats()["direct_pairs"]
+    for l in range(1, L + 1):
+        for what in (_lib.ARR_BOX_OFFSETS, _lib.ARR_BOX_CENTERS, _lib.ARR_BOX_CODES):
+            assert np.array_equal(plan.array(l, 0, what), ref.array(l, 0, what))
+        for cls in ("far", "small", "keep"):
+            assert np.array_equal(plan.pairs(l, cls), ref.pairs(l, cls))
+    perm = plan.array(0, 0, _lib.ARR_SORTED_INDEX)
+    assert np.array_equal(np.sort(perm), np.arange(N))
+    assert rel_l2(plan.apply(b).cpu(), full.cpu()) <= 2e-6

@@ -299,7 +299,7 @@ def main():
         # ---- one more product outside the timed region: phase times (max over ranks), balance, error on sampled rows ----
         stats = {}
         step(stats)
-        names = ["gather_points", "tree_lists", "partition", "sources_moments", "direct_sums", "far_field", "pack_rows", "exchange_rows", "own_rows"]
+        names = ["cube", "sort_shard", "gather_runs", "gather_points", "tree_lists", "partition", "sources_moments", "direct_sums", "far_field", "pack_rows", "exchange_rows", "own_rows"]
         t = torch.tensor([stats.get(k, 0.0) for k in names], device=dev, dtype=torch.float64)
         tm = t.clone()
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)

@@ -464,17 +464,17 @@ int f3m_bounding_box_f32(const float *X, int64_t n, int32_t d, float *min_out, f
 }
 
 int f3m_sort_shard_f32(const float *X, int64_t n, int64_t row_offset, int32_t d, const float *origin, float edge0, int32_t math_mode,
-                       int32_t depth, uint32_t *keys_out, void *records_out, void *stream) {
-    if (!X || !origin || !keys_out || !records_out || n < 1 || row_offset < 0 || d < 1 || d > F3M_MAX_DIM) return F3M_ERR_ARG;
+                       int32_t depth, void *records_out, void *stream) {
+    if (!X || !origin || !records_out || n < 1 || row_offset < 0 || d < 1 || d > F3M_MAX_DIM) return F3M_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     return guarded([&] {
         F3M_REQUIRE(edge0 > 0.f && std::isfinite(edge0), F3M_ERR_ARG, "degenerate or non-finite bounding cube (edge %g)", edge0);
-        sort_shard(X, n, row_offset, d, origin, edge0, math_mode, depth, keys_out, static_cast<uint32_t *>(records_out), s);
+        sort_shard(X, n, row_offset, d, origin, edge0, math_mode, depth, static_cast<uint32_t *>(records_out), s);
         F3M_CUDA(cudaStreamSynchronize(s));
     });
 }
 
-int f3m_plan_create_from_runs(f3m_plan **plan, const uint32_t *keys, const void *records, const int64_t *run_counts, int32_t nruns,
+int f3m_plan_create_from_runs(f3m_plan **plan, const void *records, const int64_t *run_counts, int32_t nruns,
                               int64_t run_stride, int32_t d, const float *origin, float edge0, int32_t depth, const f3m_params *prm,
                               void *stream) {
     if (!plan) return F3M_ERR_ARG;
@@ -482,13 +482,14 @@ int f3m_plan_create_from_runs(f3m_plan **plan, const uint32_t *keys, const void 
     f3m_plan *pl = nullptr;
     cudaStream_t s = (cudaStream_t)stream;
     int st = guarded([&] {
-        F3M_REQUIRE(keys && records && run_counts && origin && prm && nruns >= 1, F3M_ERR_ARG, "null pointer argument");
+        F3M_REQUIRE(records && run_counts && origin && prm && nruns >= 1, F3M_ERR_ARG, "null pointer argument");
         F3M_REQUIRE(d >= 1 && d <= F3M_MAX_DIM, F3M_ERR_ARG, "dimension %d outside 1..%d", d, F3M_MAX_DIM);
         F3M_REQUIRE(prm->ls > 0.f && prm->nr_interpolation >= 1, F3M_ERR_ARG, "bad parameters");
         F3M_REQUIRE(edge0 > 0.f && std::isfinite(edge0), F3M_ERR_ARG, "degenerate or non-finite bounding cube (edge %g)", edge0);
         pl = new f3m_plan();
         plan_begin(pl, d, prm, true, s);
-        build_tree_from_runs(pl->tx, keys, static_cast<const uint32_t *>(records), run_counts, nruns, run_stride, d, origin, edge0, depth, s);
+        build_tree_from_runs(pl->tx, static_cast<const uint32_t *>(records), run_counts, nruns, run_stride, d, origin, edge0,
+                             prm->math_mode, depth, s);
         build_root(pl->tx, s);
         pl->ty = &pl->tx;
         plan_build_levels(pl, nullptr, pl->tx.n, nullptr, pl->tx.n, origin, origin, edge0, s);

@@ -288,9 +288,9 @@ void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *o
                        int math_mode, int depth, cudaStream_t s);
 int record_words(int d);   // 32-bit words of the record [input row, coordinates] that travels with a key in the sort
 void sort_shard(const float *X, int64_t n, int64_t row0, int d, const float *origin, float edge0, int math_mode, int depth,
-                uint32_t *keys_out, uint32_t *recs_out, cudaStream_t s);
-void build_tree_from_runs(Tree &t, const uint32_t *keys, const uint32_t *recs, const int64_t *h_run_counts, int nruns, int64_t stride,
-                          int d, const float *origin, float edge0, int depth, cudaStream_t s);
+                uint32_t *recs_out, cudaStream_t s);
+void build_tree_from_runs(Tree &t, const uint32_t *recs, const int64_t *h_run_counts, int nruns, int64_t stride, int d,
+                          const float *origin, float edge0, int math_mode, int depth, cudaStream_t s);
 void exclusive_scan_i32(const int *in, int *out, int64_t n, cudaStream_t s);  // n values; out may alias in
 // up to four arrays of n values scanned in place by one set of launches; their sums as 64-bit numbers -> totals64 (device)
 void exclusive_scan_multi(int *const *arrays, int narr, int64_t n, long long *totals64, cudaStream_t s);

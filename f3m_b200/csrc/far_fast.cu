@@ -297,12 +297,14 @@ __global__ void __launch_bounds__(128, 5) m2l_fast(int nbx, int d, const int *__
 constexpr int ORD_WORDS = 128;   // 4096 keys
 __global__ void __launch_bounds__(128) far_order_kernel(int nbx, int d, const int *__restrict__ fptr, const int *__restrict__ fidx,
                                                        const int *__restrict__ cell_x, const int *__restrict__ cell_y,
-                                                       Geom2 geo, uint32_t *okey, int *oidx, int *err) {
+                                                       Geom2 geo, uint32_t *okey, int *oidx, int *err,
+                                                       const int *__restrict__ off_x, int row_begin, int row_end) {
     __shared__ uint32_t bits[4][ORD_WORDS];
     __shared__ int below[4][ORD_WORDS];
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bx = blockIdx.x * 4 + w;
     if (bx >= nbx) return;
+    if (off_x[bx + 1] <= row_begin || off_x[bx] >= row_end) return;   // no row of this box in the slice being computed
     const int e0 = fptr[bx], n = fptr[bx + 1] - e0;
     if (n == 0) return;
     auto key_of = [&](int by) {
@@ -1193,9 +1195,10 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
                     ll.far_okey.alloc((size_t)ll.far.count, s);
                     ll.far_oidx.alloc((size_t)ll.far.count, s);
                     far_order_kernel<<<(lx.nb + 3) / 4, 128, 0, s>>>(lx.nb, d, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, geo,
-                                                                    ll.far_okey.p, ll.far_oidx.p, pl->d_flags);
+                                                                    ll.far_okey.p, ll.far_oidx.p, pl->d_flags, lx.off.p, rb, re);
                     F3M_LAUNCH_CHECK();
-                    ll.far_ordered = true;
+                    // kept for later products of this plan only when every box was ordered
+                    ll.far_ordered = rb <= 0 && re >= n_x;
                 }
                 const size_t smem_n = tab + (size_t)4 * P * sizeof(float);   // tables + one buffer per warp
                 if (d == 3) {

@@ -215,6 +215,33 @@ struct MortonCfg {
     int L, ieee;
 };
 
+// Morton key of one point; spread[v] moves bit j of the 5-bit value v to bit D*j (a 32-entry table in shared memory)
+template <int D>
+__device__ __forceinline__ uint32_t morton_key(const float (&x)[D], const MortonCfg &cfg, const uint32_t *spread) {
+    const int qmax = (1 << cfg.L) - 1;
+    uint32_t key = 0;
+#pragma unroll
+    for (int k = 0; k < D; k++) {
+        float t = __fsub_rn(x[k], cfg.org[k]);
+        int q = (int)floorf(div_mode(__fmul_rn(cfg.side, t), cfg.edge0, cfg.ieee));
+        q = max(0, min(qmax, q));
+        uint32_t sk = 0;
+#pragma unroll
+        for (int c = 0; c < 4; c++)   // 5 bits at a time; 20 bits hold the deepest key (d = 1)
+            if (5 * c < cfg.L) sk |= spread[(q >> (5 * c)) & 31] << (5 * D * c);
+        key |= sk << k;
+    }
+    return key;
+}
+template <int D>
+__device__ __forceinline__ void fill_spread_table(uint32_t *spread) {
+    if (threadIdx.x < 32) {
+        uint32_t v = 0;
+        for (int j = 0; j < 5; j++) v |= ((threadIdx.x >> j) & 1u) << (D * j);
+        spread[threadIdx.x] = v;
+    }
+}
+
 // keys of a block's chunk and the histogram of their first digit
 template <int D>
 __global__ void __launch_bounds__(512) morton_hist_kernel(const float *__restrict__ X, int64_t n, MortonCfg cfg, int shift,
@@ -222,13 +249,8 @@ __global__ void __launch_bounds__(512) morton_hist_kernel(const float *__restric
     __shared__ int hist[RS_MAXBINS];
     __shared__ uint32_t spread[32];   // bit j of a 5-bit value -> bit D*j
     for (int q = threadIdx.x; q < RS_MAXBINS; q += blockDim.x) hist[q] = 0;
-    if (threadIdx.x < 32) {
-        uint32_t v = 0;
-        for (int j = 0; j < 5; j++) v |= ((threadIdx.x >> j) & 1u) << (D * j);
-        spread[threadIdx.x] = v;
-    }
+    fill_spread_table<D>(spread);
     __syncthreads();
-    const int qmax = (1 << cfg.L) - 1;
     const uint32_t mask = (1u << dbits) - 1u;
     const int64_t beg = (int64_t)blockIdx.x * chunk, end = min(n, beg + chunk);
     constexpr int U = 4;   // points per thread and round: all their loads are issued before the first is used
@@ -244,18 +266,7 @@ __global__ void __launch_bounds__(512) morton_hist_kernel(const float *__restric
         for (int u = 0; u < U; u++) {
             const int64_t i = i0 + (int64_t)u * blockDim.x;
             if (i >= end) break;
-            uint32_t key = 0;
-#pragma unroll
-            for (int k = 0; k < D; k++) {
-                float t = __fsub_rn(x[u][k], cfg.org[k]);
-                int q = (int)floorf(div_mode(__fmul_rn(cfg.side, t), cfg.edge0, cfg.ieee));
-                q = max(0, min(qmax, q));
-                uint32_t sk = 0;
-#pragma unroll
-                for (int c = 0; c < 4; c++)   // 5 bits at a time; 20 bits hold the deepest key (d = 1)
-                    if (5 * c < cfg.L) sk |= spread[(q >> (5 * c)) & 31] << (5 * D * c);
-                key |= sk << k;
-            }
+            const uint32_t key = morton_key<D>(x[u], cfg, spread);
             keys[i] = key;
             atomicAdd(&hist[(key >> shift) & mask], 1);
         }
@@ -659,10 +670,10 @@ int record_words(int d) {
     }
 }
 
-// One rank's share of a sort that several GPUs do together: keys and records of the n points of X (rows row0 ...
-// of the whole set), sorted by the first `depth` levels, into the caller's arrays.
+// One rank's share of a sort that several GPUs do together: the records [input row, coordinates] of the n points of
+// X (rows row0 ... of the whole set), sorted by the first `depth` levels of their keys, into the caller's array.
 void sort_shard(const float *X, int64_t n, int64_t row0, int d, const float *origin, float edge0, int math_mode, int depth,
-                uint32_t *keys_out, uint32_t *recs_out, cudaStream_t s) {
+                uint32_t *recs_out, cudaStream_t s) {
     F3M_REQUIRE(row0 + n < (int64_t)0x7fffffff, F3M_ERR_OVERFLOW, "row %lld does not fit a 31-bit index", (long long)(row0 + n));
     const MortonCfg cfg = morton_cfg(d, origin, edge0, math_mode);
     depth = std::max(1, std::min(depth, cfg.L));
@@ -675,7 +686,6 @@ void sort_shard(const float *X, int64_t n, int64_t row0, int d, const float *ori
         case 4: sort_records<4>(X, n, (int)row0, cfg, shift0, bits, keys, recs, s); break;
         default: sort_records<5>(X, n, (int)row0, cfg, shift0, bits, keys, recs, s); break;
     }
-    F3M_CUDA(cudaMemcpyAsync(keys_out, keys.p, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
     F3M_CUDA(cudaMemcpyAsync(recs_out, recs.p, (size_t)n * record_words(d) * 4, cudaMemcpyDeviceToDevice, s));
 }
 
@@ -686,16 +696,44 @@ void sort_shard(const float *X, int64_t n, int64_t row0, int d, const float *ori
 // a scan over the cells gives the merged offsets, and one warp per cell copies its segments (records taken apart
 // into permutation and coordinate planes on the way).
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) run_segments_kernel(const uint32_t *__restrict__ keys, int64_t stride, int nruns,
-                                                          const int64_t *__restrict__ run_counts, int shift0, int ncells,
+// coordinates of record i of a run
+template <int D>
+__device__ __forceinline__ void record_point(const void *__restrict__ recs, size_t i, float (&x)[D], int *row) {
+    constexpr int VW = Rec<D>::VW, RV = Rec<D>::RV, RW = VW * RV;
+    typedef typename VecOf<VW>::type vec_t;
+    uint32_t wds[RW];
+#pragma unroll
+    for (int v = 0; v < RV; v++) {
+        const vec_t t = reinterpret_cast<const vec_t *>(recs)[i * RV + v];
+        const uint32_t *tw = reinterpret_cast<const uint32_t *>(&t);
+#pragma unroll
+        for (int q = 0; q < VW; q++) wds[VW * v + q] = tw[q];
+    }
+    if (row) *row = (int)wds[0];
+#pragma unroll
+    for (int k = 0; k < D; k++) x[k] = __uint_as_float(wds[1 + k]);
+}
+
+// The keys are not gathered with the records: a key follows from the coordinates.
+template <int D>
+__global__ void __launch_bounds__(256) run_segments_kernel(const void *__restrict__ recs, int64_t stride, int nruns,
+                                                          const int64_t *__restrict__ run_counts, MortonCfg cfg, int shift0, int ncells,
                                                           int *seg_start, int *seg_end) {
+    __shared__ uint32_t spread[32];
+    fill_spread_table<D>(spread);
+    __syncthreads();
     const int r = blockIdx.y;
     const int64_t cnt = run_counts[r];
-    const uint32_t *k = keys + (size_t)r * stride;
+    const size_t base = (size_t)r * stride;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < cnt; i += (int64_t)gridDim.x * blockDim.x) {
-        const uint32_t c = k[i] >> shift0;
-        if (i == 0 || (k[i - 1] >> shift0) != c) seg_start[(size_t)r * ncells + c] = (int)i;
-        if (i == cnt - 1 || (k[i + 1] >> shift0) != c) seg_end[(size_t)r * ncells + c] = (int)i + 1;
+        float x[D];
+        record_point<D>(recs, base + i, x, nullptr);
+        const uint32_t c = morton_key<D>(x, cfg, spread) >> shift0;
+        uint32_t cp = 0xffffffffu, cn = 0xffffffffu;
+        if (i > 0) { record_point<D>(recs, base + i - 1, x, nullptr); cp = morton_key<D>(x, cfg, spread) >> shift0; }
+        if (i < cnt - 1) { record_point<D>(recs, base + i + 1, x, nullptr); cn = morton_key<D>(x, cfg, spread) >> shift0; }
+        if (cp != c) seg_start[(size_t)r * ncells + c] = (int)i;
+        if (cn != c) seg_end[(size_t)r * ncells + c] = (int)i + 1;
     }
 }
 
@@ -710,12 +748,13 @@ __global__ void __launch_bounds__(256) cell_totals_kernel(int ncells, int nruns,
 }
 
 template <int D>
-__global__ void __launch_bounds__(256) merge_runs_kernel(const uint32_t *__restrict__ keys, const void *__restrict__ recs,
-                                                        int64_t stride, int nruns, int ncells, const int *__restrict__ seg_start,
-                                                        const int *__restrict__ seg_end, const int *__restrict__ cell_off, int64_t n,
-                                                        uint32_t *keys_out, int *perm, float *pts) {
-    constexpr int VW = Rec<D>::VW, RV = Rec<D>::RV, RW = VW * RV;
-    typedef typename VecOf<VW>::type vec_t;
+__global__ void __launch_bounds__(256) merge_runs_kernel(const void *__restrict__ recs, int64_t stride, int nruns, int ncells,
+                                                        const int *__restrict__ seg_start, const int *__restrict__ seg_end,
+                                                        const int *__restrict__ cell_off, int64_t n, MortonCfg cfg, uint32_t *keys_out,
+                                                        int *perm, float *pts) {
+    __shared__ uint32_t spread[32];
+    fill_spread_table<D>(spread);
+    __syncthreads();
     const int lane = threadIdx.x & 31;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (c >= ncells) return;
@@ -723,29 +762,23 @@ __global__ void __launch_bounds__(256) merge_runs_kernel(const uint32_t *__restr
     if (cell_off[c + 1] == dst) return;
     for (int r = 0; r < nruns; r++) {
         const int a = seg_start[(size_t)r * ncells + c], b = seg_end[(size_t)r * ncells + c];
-        const uint32_t *k = keys + (size_t)r * stride;
-        const vec_t *rc = reinterpret_cast<const vec_t *>(recs) + (size_t)r * stride * RV;
+        const size_t base = (size_t)r * stride;
         for (int i = a + lane; i < b; i += 32) {
             const int o = dst + (i - a);
-            uint32_t wds[RW];
+            float x[D];
+            int row;
+            record_point<D>(recs, base + i, x, &row);
+            keys_out[o] = morton_key<D>(x, cfg, spread);
+            perm[o] = row;
 #pragma unroll
-            for (int v = 0; v < RV; v++) {
-                const vec_t t = rc[(size_t)i * RV + v];
-                const uint32_t *tw = reinterpret_cast<const uint32_t *>(&t);
-#pragma unroll
-                for (int q = 0; q < VW; q++) wds[VW * v + q] = tw[q];
-            }
-            keys_out[o] = k[i];
-            perm[o] = (int)wds[0];
-#pragma unroll
-            for (int q = 0; q < D; q++) pts[(size_t)q * n + o] = __uint_as_float(wds[1 + q]);
+            for (int q = 0; q < D; q++) pts[(size_t)q * n + o] = x[q];
         }
         dst += b - a;
     }
 }
 
-void build_tree_from_runs(Tree &t, const uint32_t *keys, const uint32_t *recs, const int64_t *h_run_counts, int nruns, int64_t stride,
-                          int d, const float *origin, float edge0, int depth, cudaStream_t s) {
+void build_tree_from_runs(Tree &t, const uint32_t *recs, const int64_t *h_run_counts, int nruns, int64_t stride, int d,
+                          const float *origin, float edge0, int math_mode, int depth, cudaStream_t s) {
     int64_t n = 0;
     for (int r = 0; r < nruns; r++) {
         F3M_REQUIRE(h_run_counts[r] >= 0 && h_run_counts[r] <= stride, F3M_ERR_ARG, "run %d holds %lld points, runs lie %lld apart", r,
@@ -772,7 +805,15 @@ void build_tree_from_runs(Tree &t, const uint32_t *keys, const uint32_t *recs, c
     int64_t longest = 0;
     for (int r = 0; r < nruns; r++) longest = std::max(longest, h_run_counts[r]);
     const unsigned gx = (unsigned)std::max<int64_t>(1, std::min<int64_t>((longest + 255) / 256, NUM_SMS_HINT * 16));
-    run_segments_kernel<<<dim3(gx, nruns), 256, 0, s>>>(keys, stride, nruns, counts.p, shift0, ncells, seg_start.p, seg_end.p);
+    const MortonCfg cfg = morton_cfg(d, origin, edge0, math_mode);
+    const dim3 gs(gx, nruns);
+    switch (d) {
+        case 1: run_segments_kernel<1><<<gs, 256, 0, s>>>(recs, stride, nruns, counts.p, cfg, shift0, ncells, seg_start.p, seg_end.p); break;
+        case 2: run_segments_kernel<2><<<gs, 256, 0, s>>>(recs, stride, nruns, counts.p, cfg, shift0, ncells, seg_start.p, seg_end.p); break;
+        case 3: run_segments_kernel<3><<<gs, 256, 0, s>>>(recs, stride, nruns, counts.p, cfg, shift0, ncells, seg_start.p, seg_end.p); break;
+        case 4: run_segments_kernel<4><<<gs, 256, 0, s>>>(recs, stride, nruns, counts.p, cfg, shift0, ncells, seg_start.p, seg_end.p); break;
+        default: run_segments_kernel<5><<<gs, 256, 0, s>>>(recs, stride, nruns, counts.p, cfg, shift0, ncells, seg_start.p, seg_end.p); break;
+    }
     F3M_LAUNCH_CHECK();
     cell_totals_kernel<<<(unsigned)((ncells + 1 + 255) / 256), 256, 0, s>>>(ncells, nruns, seg_start.p, seg_end.p, cell_off.p);
     F3M_LAUNCH_CHECK();
@@ -780,11 +821,11 @@ void build_tree_from_runs(Tree &t, const uint32_t *keys, const uint32_t *recs, c
     t.keys.alloc(n, s); t.perm.alloc(n, s); t.pts.alloc((size_t)n * d, s);
     const unsigned gm = (unsigned)(((int64_t)ncells * 32 + 255) / 256);
     switch (d) {
-        case 1: merge_runs_kernel<1><<<gm, 256, 0, s>>>(keys, recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, t.keys.p, t.perm.p, t.pts.p); break;
-        case 2: merge_runs_kernel<2><<<gm, 256, 0, s>>>(keys, recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, t.keys.p, t.perm.p, t.pts.p); break;
-        case 3: merge_runs_kernel<3><<<gm, 256, 0, s>>>(keys, recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, t.keys.p, t.perm.p, t.pts.p); break;
-        case 4: merge_runs_kernel<4><<<gm, 256, 0, s>>>(keys, recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, t.keys.p, t.perm.p, t.pts.p); break;
-        default: merge_runs_kernel<5><<<gm, 256, 0, s>>>(keys, recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, t.keys.p, t.perm.p, t.pts.p); break;
+        case 1: merge_runs_kernel<1><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, cfg, t.keys.p, t.perm.p, t.pts.p); break;
+        case 2: merge_runs_kernel<2><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, cfg, t.keys.p, t.perm.p, t.pts.p); break;
+        case 3: merge_runs_kernel<3><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, cfg, t.keys.p, t.perm.p, t.pts.p); break;
+        case 4: merge_runs_kernel<4><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, cfg, t.keys.p, t.perm.p, t.pts.p); break;
+        default: merge_runs_kernel<5><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, cfg, t.keys.p, t.perm.p, t.pts.p); break;
     }
     F3M_LAUNCH_CHECK();
     F3M_CUDA(cudaStreamSynchronize(s));   // h_run_counts is the caller's host array

@@ -56,42 +56,39 @@ def sort_depth(n_total: int, d: int, min_points: float) -> int:
 
 
 def sort_shard(X: torch.Tensor, row_offset: int, origin, edge0: float, math_mode: int, depth: int):
-    """One rank's share of a sort done by several GPUs (f3m_sort_shard_f32): (keys (n,) int32 bits, records (n, words))."""
+    """One rank's share of a sort done by several GPUs (f3m_sort_shard_f32): the sorted records (n, words)."""
     X = _as_f32(X)
     n, d = X.shape
     words = int(_lib.lib().f3m_record_words(d))
-    keys = torch.empty(n, device=X.device, dtype=torch.int32)
     recs = torch.empty(n, words, device=X.device, dtype=torch.int32)
     org = (C.c_float * d)(*[float(v) for v in origin])
     with torch.cuda.device(X.device):
         check(_lib.lib().f3m_sort_shard_f32(X.data_ptr(), n, int(row_offset), d, org, C.c_float(edge0), int(math_mode), int(depth),
-                                            keys.data_ptr(), recs.data_ptr(), _stream_ptr(X.device)), "f3m_sort_shard_f32")
-    return keys, recs
+                                            recs.data_ptr(), _stream_ptr(X.device)), "f3m_sort_shard_f32")
+    return recs
 
 
 class Plan:
     """Tree and interaction lists of one (X, Y) pair (f3m_plan); apply() multiplies by any b."""
 
     @classmethod
-    def from_runs(cls, keys: torch.Tensor, recs: torch.Tensor, run_counts, run_stride: int, d: int, origin, edge0: float,
+    def from_runs(cls, recs: torch.Tensor, run_counts, run_stride: int, d: int, origin, edge0: float,
                   depth: int, params: Params) -> "Plan":
         """The plan of all points (Y = X) from runs that several GPUs sorted (f3m_plan_create_from_runs)."""
         self = cls.__new__(cls)
         self.X = self.Y = None
         self.same = True
         self.params = params
-        self.device = keys.device
+        self.device = recs.device
         self.N = self.M = int(sum(run_counts))
         self.d = d
         self._h = C.c_void_p()
-        self._runs = (keys, recs)
         counts = (C.c_int64 * len(run_counts))(*[int(c) for c in run_counts])
         org = (C.c_float * d)(*[float(v) for v in origin])
         with torch.cuda.device(self.device):
-            st = _lib.lib().f3m_plan_create_from_runs(C.byref(self._h), keys.data_ptr(), recs.data_ptr(), counts, len(run_counts),
+            st = _lib.lib().f3m_plan_create_from_runs(C.byref(self._h), recs.data_ptr(), counts, len(run_counts),
                                                       int(run_stride), d, org, C.c_float(edge0), int(depth), C.byref(params),
                                                       _stream_ptr(self.device))
-        self._runs = None    # the plan holds its own sorted copy
         check(st, "f3m_plan_create_from_runs")
         return self
 

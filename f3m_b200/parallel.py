@@ -111,7 +111,7 @@ class EngineBackend:
         from . import engine
         return engine.Plan(X, None, params)
 
-    def plan_from_shards(self, x_shard: torch.Tensor, counts: List[int], rank: int, params, group):
+    def plan_from_shards(self, x_shard: torch.Tensor, counts: List[int], rank: int, params, group, clock=None):
         """The plan of all points with the sort shared by the ranks: global bounding cube (two tiny all-reduces), every
         rank sorts its shard, the sorted runs are all-gathered and merged.  None when that form does not apply (the
         level loop would need more levels than the shards were sorted to): the caller gathers the points instead."""
@@ -132,11 +132,16 @@ class EngineBackend:
         depth = engine.sort_depth(N, d, params.min_points)
         if d * depth > 22:
             return None
-        keys, recs = engine.sort_shard(x_shard, sum(counts[:rank]), origin, edge0, params.math_mode, depth)
-        keys_all, stride = gather_runs(keys, counts, group)
-        recs_all, _ = gather_runs(recs, counts, group)
+        if clock:
+            clock.mark("cube")
+        recs = engine.sort_shard(x_shard, sum(counts[:rank]), origin, edge0, params.math_mode, depth)
+        if clock:
+            clock.mark("sort_shard")
+        recs_all, stride = gather_runs(recs, counts, group)
+        if clock:
+            clock.mark("gather_runs")
         try:
-            return engine.Plan.from_runs(keys_all, recs_all, counts, stride, d, origin, edge0, depth, params)
+            return engine.Plan.from_runs(recs_all, counts, stride, d, origin, edge0, depth, params)
         except F3MError as e:
             if e.status == 5:     # F3M_ERR_UNSUPPORTED: deeper than the shards were sorted (the same on every rank)
                 return None
@@ -179,7 +184,7 @@ def distributed_kmvm(x_shard: torch.Tensor, b_shard: torch.Tensor, params, group
     n_local = torch.tensor([x_shard.shape[0]], device=dev, dtype=torch.int64)
     all_n = [torch.zeros_like(n_local) for _ in range(world)]
     dist.all_gather(all_n, n_local, group=group)
-    counts = [int(t.item()) for t in all_n]
+    counts = torch.stack(all_n).flatten().tolist()
     N = sum(counts)
     in_lo = sum(counts[:rank])
     in_hi = in_lo + counts[rank]
@@ -188,7 +193,7 @@ def distributed_kmvm(x_shard: torch.Tensor, b_shard: torch.Tensor, params, group
     b_wait = gather_shards(b_shard, counts, group, async_op=True)    # lands while the tree is built
     plan = None
     if world > 1 and hasattr(backend, "plan_from_shards"):
-        plan = backend.plan_from_shards(x_shard, counts, rank, params, group)
+        plan = backend.plan_from_shards(x_shard, counts, rank, params, group, clock)
     if plan is None:
         X = gather_shards(x_shard, counts, group)
         clock.mark("gather_points")

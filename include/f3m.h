@@ -125,13 +125,14 @@ int f3m_plan_apply_range_moments(f3m_plan *plan, const float *b, int32_t R, floa
 /* A plan whose sort is shared by several GPUs (no counterpart in the reference).  Each rank sorts its own shard of
  * the points inside the GLOBAL bounding cube (origin = per-dimension minimum over all ranks, edge0 = 1.01f * largest
  * extent, both float32 as in calculate_edge_X, n_tree.cu:39-46) to the depth f3m_sort_depth gives for the TOTAL
- * point count; the sorted runs (keys: uint32 per point; records: f3m_record_words(d) 32-bit words per point,
- * [input row, coordinates]) are all-gathered, and every rank merges them into the same plan.
+ * point count; the sorted runs (records of f3m_record_words(d) 32-bit words per point: [input row, coordinates];
+ * the keys follow from the coordinates and do not travel) are all-gathered, and every rank merges them into the
+ * same plan.
  *   f3m_bounding_box_f32       per-dimension minimum and maximum of a shard (HOST arrays of d floats).
- *   f3m_sort_shard_f32         keys_out (n), records_out (n records): the shard sorted; row_offset = input row of the
- *                              shard's first point in the whole set.
- *   f3m_plan_create_from_runs  keys / records hold nruns runs, run r at element r * run_stride with run_counts[r]
- *                              points (HOST array).  The plan is that of f3m_plan_create on the whole set with Y = X,
+ *   f3m_sort_shard_f32         records_out (n records): the shard sorted; row_offset = input row of the shard's
+ *                              first point in the whole set.
+ *   f3m_plan_create_from_runs  records holds nruns runs, run r at record r * run_stride with run_counts[r] points
+ *                              (HOST array); prm->math_mode must be the one the shards were sorted with.  The plan is that of f3m_plan_create on the whole set with Y = X,
  *                              except for the order of the points inside a finest sorted cell.  If the level loop
  *                              needs more levels than `depth` (strongly clustered points): F3M_ERR_UNSUPPORTED --
  *                              build the plan from the gathered points instead. */
@@ -139,8 +140,8 @@ int f3m_sort_depth(int64_t n_total, int32_t d, float min_points);
 int f3m_record_words(int32_t d);
 int f3m_bounding_box_f32(const float *X, int64_t n, int32_t d, float *min_out, float *max_out, void *stream);
 int f3m_sort_shard_f32(const float *X, int64_t n, int64_t row_offset, int32_t d, const float *origin, float edge0,
-                       int32_t math_mode, int32_t depth, uint32_t *keys_out, void *records_out, void *stream);
-int f3m_plan_create_from_runs(f3m_plan **plan, const uint32_t *keys, const void *records, const int64_t *run_counts,
+                       int32_t math_mode, int32_t depth, void *records_out, void *stream);
+int f3m_plan_create_from_runs(f3m_plan **plan, const void *records, const int64_t *run_counts,
                               int32_t nruns, int64_t run_stride, int32_t d, const float *origin, float edge0, int32_t depth,
                               const f3m_params *prm, void *stream);
 

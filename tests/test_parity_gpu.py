@@ -623,14 +623,12 @@ def test_plan_from_sorted_runs(name, cuda):
     depth = engine.sort_depth(N, d, c["min_points"])
     stride = max(counts)
     words = _lib.lib().f3m_record_words(d)
-    keys_all = torch.zeros(3 * stride, device=cuda, dtype=torch.int32)
     recs_all = torch.zeros(3 * stride, words, device=cuda, dtype=torch.int32)
     for i in range(3):
-        k, r = engine.sort_shard(X[cuts[i]:cuts[i + 1]], cuts[i], origin, edge0, prm.math_mode, depth)
-        keys_all[i * stride:i * stride + counts[i]] = k
+        r = engine.sort_shard(X[cuts[i]:cuts[i + 1]], cuts[i], origin, edge0, prm.math_mode, depth)
         recs_all[i * stride:i * stride + counts[i]] = r
     try:
-        plan = engine.Plan.from_runs(keys_all, recs_all, counts, stride, d, origin, edge0, depth, prm)
+        plan = engine.Plan.from_runs(recs_all, counts, stride, d, origin, edge0, depth, prm)
     except _lib.F3MError as e:
         assert e.status == 5 and ref.stats()["levels"] > depth     # deeper than the estimate: the documented refusal
         return

@@ -299,7 +299,7 @@ def main():
         # ---- one more product outside the timed region: phase times (max over ranks), balance, error on sampled rows ----
         stats = {}
         step(stats)
-        names = ["cube", "sort_shard", "gather_runs", "gather_points", "tree_lists", "partition", "sources_moments", "direct_sums", "far_field", "pack_rows", "exchange_rows", "own_rows"]
+        names = ["cube", "sort_shard", "levels_lists", "merge_runs", "gather_points", "tree_lists", "partition", "sources_moments", "direct_sums", "far_field", "pack_rows", "exchange_rows", "own_rows"]
         t = torch.tensor([stats.get(k, 0.0) for k in names], device=dev, dtype=torch.float64)
         tm = t.clone()
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
@@ -397,7 +397,7 @@ def main():
                         "frac": round(max(t_b, t_f) / ms_, 3) if ms_ > 0 else None}
             line["stages_roofline"] = {
                 "hbm_peak_gbs": hbm_gbs, "hbm_peak": hbm_src,
-                "tree+lists": stage_roof(tm["build"], N * (2 * 4 * d + 8), 0),   # keys + records once through the sort: 8d + 8 B/point
+                "tree+lists": stage_roof(tm["build"], N * (2 * 4 * d + 2 * 4 * R + 8), 0),   # sort traffic: 40 B/point at d=3, R=1
                 "p2m": stage_roof(tm["p2m"], N * (4 * d + 4 * R) + nb_leaf * Pn * R * 4, N * Pn * R),
                 "m2l": stage_roof(tm["m2l"], 2 * nb_leaf * Pn * R * 4, st["far_box_pairs"] * d * pd * Pn * R),
                 "l2p": stage_roof(tm["l2p"], N * (4 * d + 8 * R) + nb_leaf * Pn * R * 4, N * Pn * R),

@@ -66,9 +66,9 @@ SIGNATURES = {
     "f3m_sort_depth": (C.c_int, [_I64, _I32, _F32]),
     "f3m_record_words": (C.c_int, [_I32]),
     "f3m_bounding_box_f32": (C.c_int, [_P, _I64, _I32, C.POINTER(_F32), C.POINTER(_F32), _P]),
-    "f3m_sort_shard_f32": (C.c_int, [_P, _I64, _I64, _I32, C.POINTER(_F32), _F32, _I32, _I32, _P, _P]),
-    "f3m_plan_create_from_runs": (C.c_int, [C.POINTER(_P), _P, C.POINTER(_I64), _I32, _I64, _I32, C.POINTER(_F32), _F32, _I32,
-                                            C.POINTER(Params), _P]),
+    "f3m_sort_shard_f32": (C.c_int, [_P, _I64, _I64, _I32, C.POINTER(_F32), _F32, _I32, _I32, _P, _P, _P]),
+    "f3m_plan_create_from_cell_counts": (C.c_int, [C.POINTER(_P), _P, _I32, _I32, C.POINTER(_F32), _F32, _I32, C.POINTER(Params), _P]),
+    "f3m_plan_attach_runs": (C.c_int, [_P, _P, _I64, _P]),
     "f3m_plan_partition_rows": (C.c_int, [_P, _I32, _I32, C.POINTER(_I64), _P]),
     "f3m_plan_shard_begin": (C.c_int, [_P, _P, _I32, _I64, _I64, _I64, _I64, _P, _P]),
     "f3m_plan_shard_near": (C.c_int, [_P, _P, _P]),

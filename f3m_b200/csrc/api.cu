@@ -306,6 +306,7 @@ static void plan_build_levels(f3m_plan *pl, const float *X, int64_t N, const flo
 static void plan_apply(f3m_plan *pl, const float *b, int R, float *out, int64_t row_begin, int64_t row_end,
                        cudaStream_t s) {
     F3M_REQUIRE(b && out && R >= 1, F3M_ERR_ARG, "bad right-hand side (R=%d)", R);
+    F3M_REQUIRE(!pl->tx.runs.pending, F3M_ERR_ARG, "the plan still waits for its sorted runs (f3m_plan_attach_runs)");
     int dev;
     F3M_CUDA(cudaGetDevice(&dev));
     F3M_REQUIRE(dev == pl->device, F3M_ERR_ARG, "plan was built on device %d, current device is %d", pl->device, dev);
@@ -464,32 +465,30 @@ int f3m_bounding_box_f32(const float *X, int64_t n, int32_t d, float *min_out, f
 }
 
 int f3m_sort_shard_f32(const float *X, int64_t n, int64_t row_offset, int32_t d, const float *origin, float edge0, int32_t math_mode,
-                       int32_t depth, void *records_out, void *stream) {
-    if (!X || !origin || !records_out || n < 1 || row_offset < 0 || d < 1 || d > F3M_MAX_DIM) return F3M_ERR_ARG;
+                       int32_t depth, void *records_out, int32_t *cell_counts_out, void *stream) {
+    if (!X || !origin || !records_out || !cell_counts_out || n < 1 || row_offset < 0 || d < 1 || d > F3M_MAX_DIM) return F3M_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     return guarded([&] {
         F3M_REQUIRE(edge0 > 0.f && std::isfinite(edge0), F3M_ERR_ARG, "degenerate or non-finite bounding cube (edge %g)", edge0);
-        sort_shard(X, n, row_offset, d, origin, edge0, math_mode, depth, static_cast<uint32_t *>(records_out), s);
+        sort_shard(X, n, row_offset, d, origin, edge0, math_mode, depth, static_cast<uint32_t *>(records_out), cell_counts_out, s);
         F3M_CUDA(cudaStreamSynchronize(s));
     });
 }
 
-int f3m_plan_create_from_runs(f3m_plan **plan, const void *records, const int64_t *run_counts, int32_t nruns,
-                              int64_t run_stride, int32_t d, const float *origin, float edge0, int32_t depth, const f3m_params *prm,
-                              void *stream) {
+int f3m_plan_create_from_cell_counts(f3m_plan **plan, const int32_t *cell_counts, int32_t nruns, int32_t d, const float *origin,
+                                     float edge0, int32_t depth, const f3m_params *prm, void *stream) {
     if (!plan) return F3M_ERR_ARG;
     *plan = nullptr;
     f3m_plan *pl = nullptr;
     cudaStream_t s = (cudaStream_t)stream;
     int st = guarded([&] {
-        F3M_REQUIRE(records && run_counts && origin && prm && nruns >= 1, F3M_ERR_ARG, "null pointer argument");
+        F3M_REQUIRE(cell_counts && origin && prm && nruns >= 1, F3M_ERR_ARG, "null pointer argument");
         F3M_REQUIRE(d >= 1 && d <= F3M_MAX_DIM, F3M_ERR_ARG, "dimension %d outside 1..%d", d, F3M_MAX_DIM);
         F3M_REQUIRE(prm->ls > 0.f && prm->nr_interpolation >= 1, F3M_ERR_ARG, "bad parameters");
         F3M_REQUIRE(edge0 > 0.f && std::isfinite(edge0), F3M_ERR_ARG, "degenerate or non-finite bounding cube (edge %g)", edge0);
         pl = new f3m_plan();
         plan_begin(pl, d, prm, true, s);
-        build_tree_from_runs(pl->tx, static_cast<const uint32_t *>(records), run_counts, nruns, run_stride, d, origin, edge0,
-                             prm->math_mode, depth, s);
+        tree_from_cell_counts(pl->tx, cell_counts, nruns, d, origin, edge0, depth, pl, s);
         build_root(pl->tx, s);
         pl->ty = &pl->tx;
         plan_build_levels(pl, nullptr, pl->tx.n, nullptr, pl->tx.n, origin, origin, edge0, s);
@@ -500,6 +499,16 @@ int f3m_plan_create_from_runs(f3m_plan **plan, const void *records, const int64_
     }
     *plan = pl;
     return F3M_OK;
+}
+
+int f3m_plan_attach_runs(f3m_plan *plan, const void *records, int64_t run_stride, void *stream) {
+    if (!plan || !records || run_stride < 1) return F3M_ERR_ARG;
+    return guarded([&] {
+        int dev;
+        F3M_CUDA(cudaGetDevice(&dev));
+        F3M_REQUIRE(dev == plan->device, F3M_ERR_ARG, "plan was built on device %d, current device is %d", plan->device, dev);
+        tree_attach_runs(plan->tx, static_cast<const uint32_t *>(records), run_stride, (cudaStream_t)stream);
+    });
 }
 
 /* ---- one product shared by several GPUs, in phases ------------------------------------------------------------ */
@@ -520,6 +529,7 @@ int f3m_plan_shard_begin(f3m_plan *plan, const float *b, int32_t R, int64_t row_
     cudaStream_t s = (cudaStream_t)stream;
     int st = guarded([&] {
         F3M_REQUIRE(R >= 1, F3M_ERR_ARG, "bad right-hand side (R=%d)", R);
+        F3M_REQUIRE(!plan->tx.runs.pending, F3M_ERR_ARG, "the plan still waits for its sorted runs (f3m_plan_attach_runs)");
         int dev;
         F3M_CUDA(cudaGetDevice(&dev));
         F3M_REQUIRE(dev == plan->device, F3M_ERR_ARG, "plan was built on device %d, current device is %d", plan->device, dev);

@@ -176,6 +176,17 @@ struct Tree {
     DevBuf<int> perm;              // (n) sorted position -> input row
     DevBuf<float> pts;             // (d,n) sorted coordinates, one plane per dimension
     std::vector<Level> levels;     // levels[0] is the root
+    // A tree whose points arrive as sorted runs (one per rank): the levels are built from one pseudo key per occupied
+    // finest sorted cell (pkeys) and offsets into the merged order (fine_off) before the points are attached.
+    struct Runs {
+        bool pending = false;      // levels may be built, points not merged in yet
+        int nruns = 0, ncells = 0, nocc = 0;
+        DevBuf<int> counts;        // (nruns, ncells) points per cell and run
+        DevBuf<int> seg_start;     // (nruns, ncells + 1) position of the cell inside its run
+        DevBuf<int> cell_off;      // (ncells + 1) merged offset of the cell
+        DevBuf<uint32_t> pkeys;    // (nocc) pseudo key of every occupied cell
+        DevBuf<int> fine_off;      // (nocc + 1) merged offset of every occupied cell
+    } runs;
 };
 
 struct PairCSR {
@@ -288,9 +299,10 @@ void build_sorted_tree(Tree &t, const float *X, int64_t n, int d, const float *o
                        int math_mode, int depth, cudaStream_t s);
 int record_words(int d);   // 32-bit words of the record [input row, coordinates] that travels with a key in the sort
 void sort_shard(const float *X, int64_t n, int64_t row0, int d, const float *origin, float edge0, int math_mode, int depth,
-                uint32_t *recs_out, cudaStream_t s);
-void build_tree_from_runs(Tree &t, const uint32_t *recs, const int64_t *h_run_counts, int nruns, int64_t stride, int d,
-                          const float *origin, float edge0, int math_mode, int depth, cudaStream_t s);
+                uint32_t *recs_out, int *cell_counts_out, cudaStream_t s);
+void tree_from_cell_counts(Tree &t, const int *counts, int nruns, int d, const float *origin, float edge0, int depth, f3m_plan *pl,
+                           cudaStream_t s);
+void tree_attach_runs(Tree &t, const uint32_t *recs, int64_t stride, cudaStream_t s);
 void exclusive_scan_i32(const int *in, int *out, int64_t n, cudaStream_t s);  // n values; out may alias in
 // up to four arrays of n values scanned in place by one set of launches; their sums as 64-bit numbers -> totals64 (device)
 void exclusive_scan_multi(int *const *arrays, int narr, int64_t n, long long *totals64, cudaStream_t s);

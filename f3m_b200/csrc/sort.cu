@@ -670,14 +670,31 @@ int record_words(int d) {
     }
 }
 
+// points of one finest sorted cell in a sorted run: first and one-past-last position (0, 0 for cells the run misses)
+__global__ void __launch_bounds__(256) cell_bounds_kernel(const uint32_t *__restrict__ keys, int64_t n, int shift0, int *seg_start,
+                                                         int *seg_end) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t c = keys[i] >> shift0;
+        if (i == 0 || (keys[i - 1] >> shift0) != c) seg_start[c] = (int)i;
+        if (i == n - 1 || (keys[i + 1] >> shift0) != c) seg_end[c] = (int)i + 1;
+    }
+}
+__global__ void __launch_bounds__(256) cell_counts_kernel(int ncells, const int *__restrict__ seg_start, const int *__restrict__ seg_end,
+                                                         int *counts) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < ncells) counts[c] = seg_end[c] - seg_start[c];
+}
+
 // One rank's share of a sort that several GPUs do together: the records [input row, coordinates] of the n points of
-// X (rows row0 ... of the whole set), sorted by the first `depth` levels of their keys, into the caller's array.
+// X (rows row0 ... of the whole set), sorted by the first `depth` levels of their keys, and the number of points in
+// every cell of that depth (2^(d depth) counts), into the caller's arrays.
 void sort_shard(const float *X, int64_t n, int64_t row0, int d, const float *origin, float edge0, int math_mode, int depth,
-                uint32_t *recs_out, cudaStream_t s) {
+                uint32_t *recs_out, int *cell_counts_out, cudaStream_t s) {
     F3M_REQUIRE(row0 + n < (int64_t)0x7fffffff, F3M_ERR_OVERFLOW, "row %lld does not fit a 31-bit index", (long long)(row0 + n));
     const MortonCfg cfg = morton_cfg(d, origin, edge0, math_mode);
     depth = std::max(1, std::min(depth, cfg.L));
-    const int shift0 = d * (cfg.L - depth), bits = d * depth;
+    F3M_REQUIRE(d * depth <= 22, F3M_ERR_UNSUPPORTED, "shards sorted by %d key bits: the cell table holds at most 22", d * depth);
+    const int shift0 = d * (cfg.L - depth), bits = d * depth, ncells = 1 << bits;
     DevBuf<uint32_t> keys, recs;
     switch (d) {
         case 1: sort_records<1>(X, n, (int)row0, cfg, shift0, bits, keys, recs, s); break;
@@ -687,148 +704,149 @@ void sort_shard(const float *X, int64_t n, int64_t row0, int d, const float *ori
         default: sort_records<5>(X, n, (int)row0, cfg, shift0, bits, keys, recs, s); break;
     }
     F3M_CUDA(cudaMemcpyAsync(recs_out, recs.p, (size_t)n * record_words(d) * 4, cudaMemcpyDeviceToDevice, s));
+    DevBuf<int> a, b;
+    a.alloc(ncells, s); b.alloc(ncells, s);
+    a.zero(); b.zero();
+    const unsigned g = (unsigned)std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, NUM_SMS_HINT * 16));
+    cell_bounds_kernel<<<g, 256, 0, s>>>(keys.p, n, shift0, a.p, b.p);
+    F3M_LAUNCH_CHECK();
+    cell_counts_kernel<<<(unsigned)((ncells + 255) / 256), 256, 0, s>>>(ncells, a.p, b.p, cell_counts_out);
+    F3M_LAUNCH_CHECK();
 }
 
 // ---------------------------------------------------------------------------------------------
-// Merge of sorted runs (one per rank, all-gathered) into the tree's sorted arrays.  Every run is sorted by the same
-// key bits, so the points of one finest-sorted cell form one segment per run; the merged order is cell by cell,
-// run by run -- the same on every rank.  One pass marks the segment ends of every run in a dense (run, cell) table,
-// a scan over the cells gives the merged offsets, and one warp per cell copies its segments (records taken apart
-// into permutation and coordinate planes on the way).
+// A tree from sorted runs (one per rank).  Every run is sorted by the same key bits, so the points of one finest
+// sorted cell form one segment per run and the merged order is cell by cell, run by run -- the same on every rank.
+// The levels of the tree follow from the cell counts alone (tree.cu builds them from one pseudo key per occupied
+// cell), so they -- and the interaction lists -- can be built while the records are still on the wire; the records
+// are merged in afterwards, one warp per cell (taken apart into permutation and coordinate planes on the way).
 // ---------------------------------------------------------------------------------------------
-// coordinates of record i of a run
-template <int D>
-__device__ __forceinline__ void record_point(const void *__restrict__ recs, size_t i, float (&x)[D], int *row) {
-    constexpr int VW = Rec<D>::VW, RV = Rec<D>::RV, RW = VW * RV;
-    typedef typename VecOf<VW>::type vec_t;
-    uint32_t wds[RW];
-#pragma unroll
-    for (int v = 0; v < RV; v++) {
-        const vec_t t = reinterpret_cast<const vec_t *>(recs)[i * RV + v];
-        const uint32_t *tw = reinterpret_cast<const uint32_t *>(&t);
-#pragma unroll
-        for (int q = 0; q < VW; q++) wds[VW * v + q] = tw[q];
-    }
-    if (row) *row = (int)wds[0];
-#pragma unroll
-    for (int k = 0; k < D; k++) x[k] = __uint_as_float(wds[1 + k]);
-}
-
-// The keys are not gathered with the records: a key follows from the coordinates.
-template <int D>
-__global__ void __launch_bounds__(256) run_segments_kernel(const void *__restrict__ recs, int64_t stride, int nruns,
-                                                          const int64_t *__restrict__ run_counts, MortonCfg cfg, int shift0, int ncells,
-                                                          int *seg_start, int *seg_end) {
-    __shared__ uint32_t spread[32];
-    fill_spread_table<D>(spread);
-    __syncthreads();
-    const int r = blockIdx.y;
-    const int64_t cnt = run_counts[r];
-    const size_t base = (size_t)r * stride;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < cnt; i += (int64_t)gridDim.x * blockDim.x) {
-        float x[D];
-        record_point<D>(recs, base + i, x, nullptr);
-        const uint32_t c = morton_key<D>(x, cfg, spread) >> shift0;
-        uint32_t cp = 0xffffffffu, cn = 0xffffffffu;
-        if (i > 0) { record_point<D>(recs, base + i - 1, x, nullptr); cp = morton_key<D>(x, cfg, spread) >> shift0; }
-        if (i < cnt - 1) { record_point<D>(recs, base + i + 1, x, nullptr); cn = morton_key<D>(x, cfg, spread) >> shift0; }
-        if (cp != c) seg_start[(size_t)r * ncells + c] = (int)i;
-        if (cn != c) seg_end[(size_t)r * ncells + c] = (int)i + 1;
-    }
-}
-
-__global__ void __launch_bounds__(256) cell_totals_kernel(int ncells, int nruns, const int *__restrict__ seg_start,
-                                                         const int *__restrict__ seg_end, int *total) {
+__global__ void __launch_bounds__(256) cell_totals_kernel(int ncells, int nruns, const int *__restrict__ counts, int *total,
+                                                         int *occupied) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c > ncells) return;
     int t = 0;
     if (c < ncells)
-        for (int r = 0; r < nruns; r++) t += seg_end[(size_t)r * ncells + c] - seg_start[(size_t)r * ncells + c];
-    total[c] = t;   // entry ncells = 0: the scan turns it into the grand total
+        for (int r = 0; r < nruns; r++) t += counts[(size_t)r * ncells + c];
+    total[c] = t;   // entry ncells = 0: the scans turn it into the grand totals
+    occupied[c] = t > 0;
+}
+
+// occupied cell number rank[c]: its pseudo key (cell id at the key's position) and the merged offset of its points
+__global__ void __launch_bounds__(256) occupied_cells_kernel(int ncells, const int *__restrict__ total_before,
+                                                            const int *__restrict__ rank, int shift0, uint32_t *pkeys, int *fine_off) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c > ncells) return;
+    if (c == ncells) { fine_off[rank[c]] = total_before[c]; return; }
+    if (rank[c + 1] != rank[c]) {
+        pkeys[rank[c]] = (uint32_t)c << shift0;
+        fine_off[rank[c]] = total_before[c];
+    }
 }
 
 template <int D>
 __global__ void __launch_bounds__(256) merge_runs_kernel(const void *__restrict__ recs, int64_t stride, int nruns, int ncells,
-                                                        const int *__restrict__ seg_start, const int *__restrict__ seg_end,
-                                                        const int *__restrict__ cell_off, int64_t n, MortonCfg cfg, uint32_t *keys_out,
-                                                        int *perm, float *pts) {
-    __shared__ uint32_t spread[32];
-    fill_spread_table<D>(spread);
-    __syncthreads();
+                                                        const int *__restrict__ counts, const int *__restrict__ seg_start,
+                                                        const int *__restrict__ cell_off, int64_t n, int *perm, float *pts) {
+    constexpr int VW = Rec<D>::VW, RV = Rec<D>::RV, RW = VW * RV;
+    typedef typename VecOf<VW>::type vec_t;
     const int lane = threadIdx.x & 31;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (c >= ncells) return;
     int dst = cell_off[c];
     if (cell_off[c + 1] == dst) return;
     for (int r = 0; r < nruns; r++) {
-        const int a = seg_start[(size_t)r * ncells + c], b = seg_end[(size_t)r * ncells + c];
-        const size_t base = (size_t)r * stride;
-        for (int i = a + lane; i < b; i += 32) {
+        const int a = seg_start[(size_t)r * (ncells + 1) + c], len = counts[(size_t)r * ncells + c];
+        const vec_t *rc = reinterpret_cast<const vec_t *>(recs) + (size_t)r * stride * RV;
+        for (int i = a + lane; i < a + len; i += 32) {
             const int o = dst + (i - a);
-            float x[D];
-            int row;
-            record_point<D>(recs, base + i, x, &row);
-            keys_out[o] = morton_key<D>(x, cfg, spread);
-            perm[o] = row;
+            uint32_t wds[RW];
 #pragma unroll
-            for (int q = 0; q < D; q++) pts[(size_t)q * n + o] = x[q];
+            for (int v = 0; v < RV; v++) {
+                const vec_t t = rc[(size_t)i * RV + v];
+                const uint32_t *tw = reinterpret_cast<const uint32_t *>(&t);
+#pragma unroll
+                for (int q = 0; q < VW; q++) wds[VW * v + q] = tw[q];
+            }
+            perm[o] = (int)wds[0];
+#pragma unroll
+            for (int q = 0; q < D; q++) pts[(size_t)q * n + o] = __uint_as_float(wds[1 + q]);
         }
-        dst += b - a;
+        dst += len;
     }
 }
 
-void build_tree_from_runs(Tree &t, const uint32_t *recs, const int64_t *h_run_counts, int nruns, int64_t stride, int d,
-                          const float *origin, float edge0, int math_mode, int depth, cudaStream_t s) {
-    int64_t n = 0;
-    for (int r = 0; r < nruns; r++) {
-        F3M_REQUIRE(h_run_counts[r] >= 0 && h_run_counts[r] <= stride, F3M_ERR_ARG, "run %d holds %lld points, runs lie %lld apart", r,
-                    (long long)h_run_counts[r], (long long)stride);
-        n += h_run_counts[r];
-    }
-    F3M_REQUIRE(n > 0 && n < (int64_t)0x7fffffff, F3M_ERR_OVERFLOW, "point count %lld does not fit a 31-bit index", (long long)n);
-    t.n = n;
+// counts: (nruns, ncells) device array, the cell counts of every run.  Prepares the tree's size, the tables the
+// merge needs and the pseudo keys the levels are built from; the points themselves come with attach_runs.
+void tree_from_cell_counts(Tree &t, const int *counts, int nruns, int d, const float *origin, float edge0, int depth, f3m_plan *pl,
+                           cudaStream_t s) {
     t.d = d;
     t.data = nullptr;   // the points exist as runs only: this tree cannot be sorted again to a greater depth
     t.edge0 = edge0;
     for (int k = 0; k < d; k++) t.origin[k] = origin[k];
     t.lmax = std::min(30 / d, 20);
     depth = std::max(1, std::min(depth, t.lmax));
-    F3M_REQUIRE(d * depth <= 22, F3M_ERR_UNSUPPORTED, "runs sorted by %d key bits: the merge tabulates at most 22", d * depth);
+    F3M_REQUIRE(d * depth <= 22, F3M_ERR_UNSUPPORTED, "runs sorted by %d key bits: the cell table holds at most 22", d * depth);
     t.sorted_depth = depth;
     const int shift0 = d * (t.lmax - depth), ncells = 1 << (d * depth);
-    DevBuf<int> seg_start, seg_end, cell_off;
-    DevBuf<int64_t> counts;
-    seg_start.alloc((size_t)nruns * ncells, s); seg_end.alloc((size_t)nruns * ncells, s); cell_off.alloc((size_t)ncells + 1, s);
-    seg_start.zero(); seg_end.zero();
-    counts.alloc(nruns, s);
-    F3M_CUDA(cudaMemcpyAsync(counts.p, h_run_counts, nruns * sizeof(int64_t), cudaMemcpyHostToDevice, s));
-    int64_t longest = 0;
-    for (int r = 0; r < nruns; r++) longest = std::max(longest, h_run_counts[r]);
-    const unsigned gx = (unsigned)std::max<int64_t>(1, std::min<int64_t>((longest + 255) / 256, NUM_SMS_HINT * 16));
-    const MortonCfg cfg = morton_cfg(d, origin, edge0, math_mode);
-    const dim3 gs(gx, nruns);
-    switch (d) {
-        case 1: run_segments_kernel<1><<<gs, 256, 0, s>>>(recs, stride, nruns, counts.p, cfg, shift0, ncells, seg_start.p, seg_end.p); break;
-        case 2: run_segments_kernel<2><<<gs, 256, 0, s>>>(recs, stride, nruns, counts.p, cfg, shift0, ncells, seg_start.p, seg_end.p); break;
-        case 3: run_segments_kernel<3><<<gs, 256, 0, s>>>(recs, stride, nruns, counts.p, cfg, shift0, ncells, seg_start.p, seg_end.p); break;
-        case 4: run_segments_kernel<4><<<gs, 256, 0, s>>>(recs, stride, nruns, counts.p, cfg, shift0, ncells, seg_start.p, seg_end.p); break;
-        default: run_segments_kernel<5><<<gs, 256, 0, s>>>(recs, stride, nruns, counts.p, cfg, shift0, ncells, seg_start.p, seg_end.p); break;
+    Tree::Runs &ru = t.runs;
+    ru.nruns = nruns; ru.ncells = ncells;
+    ru.counts.alloc((size_t)nruns * ncells, s);
+    F3M_CUDA(cudaMemcpyAsync(ru.counts.p, counts, (size_t)nruns * ncells * sizeof(int), cudaMemcpyDeviceToDevice, s));
+    ru.cell_off.alloc((size_t)ncells + 1, s);
+    DevBuf<int> rank;
+    rank.alloc((size_t)ncells + 1, s);
+    cell_totals_kernel<<<(unsigned)((ncells + 1 + 255) / 256), 256, 0, s>>>(ncells, nruns, ru.counts.p, ru.cell_off.p, rank.p);
+    F3M_LAUNCH_CHECK();
+    int *both[2] = {ru.cell_off.p, rank.p};
+    long long *d_tot = reinterpret_cast<long long *>(pl->d_flags + FL_LISTTOT);
+    exclusive_scan_multi(both, 2, (int64_t)ncells + 1, d_tot, s);
+    // position of every cell inside its run: one scan per run (rows of ncells + 1, the last entry closes the row)
+    ru.seg_start.alloc((size_t)nruns * (ncells + 1), s);
+    for (int r = 0; r < nruns; r++) {
+        int *row = ru.seg_start.p + (size_t)r * (ncells + 1);
+        F3M_CUDA(cudaMemcpyAsync(row, ru.counts.p + (size_t)r * ncells, (size_t)ncells * sizeof(int), cudaMemcpyDeviceToDevice, s));
+        F3M_CUDA(cudaMemsetAsync(row + ncells, 0, sizeof(int), s));
     }
+    for (int r0 = 0; r0 < nruns; r0 += 4) {
+        int *rows[4];
+        const int nr = std::min(4, nruns - r0);
+        for (int q = 0; q < nr; q++) rows[q] = ru.seg_start.p + (size_t)(r0 + q) * (ncells + 1);
+        exclusive_scan_multi(rows, nr, (int64_t)ncells + 1, nullptr, s);
+    }
+    long long *h = reinterpret_cast<long long *>(pl->h_pinned + FL_LISTTOT);
+    F3M_CUDA(cudaMemcpyAsync(h, d_tot, 2 * sizeof(long long), cudaMemcpyDeviceToHost, s));
+    F3M_CUDA(cudaStreamSynchronize(s));
+    const long long n = h[0], nocc = h[1];
+    F3M_REQUIRE(n > 0 && n < 0x7fffffffLL, F3M_ERR_OVERFLOW, "point count %lld does not fit a 31-bit index", n);
+    t.n = n;
+    ru.pkeys.alloc((size_t)nocc, s);
+    ru.fine_off.alloc((size_t)nocc + 1, s);
+    occupied_cells_kernel<<<(unsigned)((ncells + 1 + 255) / 256), 256, 0, s>>>(ncells, ru.cell_off.p, rank.p, shift0, ru.pkeys.p,
+                                                                               ru.fine_off.p);
     F3M_LAUNCH_CHECK();
-    cell_totals_kernel<<<(unsigned)((ncells + 1 + 255) / 256), 256, 0, s>>>(ncells, nruns, seg_start.p, seg_end.p, cell_off.p);
-    F3M_LAUNCH_CHECK();
-    exclusive_scan_i32(cell_off.p, cell_off.p, (int64_t)ncells + 1, s);
-    t.keys.alloc(n, s); t.perm.alloc(n, s); t.pts.alloc((size_t)n * d, s);
+    ru.nocc = (int)nocc;
+    ru.pending = true;
+}
+
+// records: the all-gathered sorted runs, run r at record r * stride
+void tree_attach_runs(Tree &t, const uint32_t *recs, int64_t stride, cudaStream_t s) {
+    Tree::Runs &ru = t.runs;
+    F3M_REQUIRE(ru.pending, F3M_ERR_ARG, "this plan does not wait for sorted runs");
+    const int64_t n = t.n;
+    const int d = t.d, nruns = ru.nruns, ncells = ru.ncells;
+    t.perm.alloc(n, s); t.pts.alloc((size_t)n * d, s);
     const unsigned gm = (unsigned)(((int64_t)ncells * 32 + 255) / 256);
     switch (d) {
-        case 1: merge_runs_kernel<1><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, cfg, t.keys.p, t.perm.p, t.pts.p); break;
-        case 2: merge_runs_kernel<2><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, cfg, t.keys.p, t.perm.p, t.pts.p); break;
-        case 3: merge_runs_kernel<3><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, cfg, t.keys.p, t.perm.p, t.pts.p); break;
-        case 4: merge_runs_kernel<4><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, cfg, t.keys.p, t.perm.p, t.pts.p); break;
-        default: merge_runs_kernel<5><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, seg_start.p, seg_end.p, cell_off.p, n, cfg, t.keys.p, t.perm.p, t.pts.p); break;
+        case 1: merge_runs_kernel<1><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, ru.counts.p, ru.seg_start.p, ru.cell_off.p, n, t.perm.p, t.pts.p); break;
+        case 2: merge_runs_kernel<2><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, ru.counts.p, ru.seg_start.p, ru.cell_off.p, n, t.perm.p, t.pts.p); break;
+        case 3: merge_runs_kernel<3><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, ru.counts.p, ru.seg_start.p, ru.cell_off.p, n, t.perm.p, t.pts.p); break;
+        case 4: merge_runs_kernel<4><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, ru.counts.p, ru.seg_start.p, ru.cell_off.p, n, t.perm.p, t.pts.p); break;
+        default: merge_runs_kernel<5><<<gm, 256, 0, s>>>(recs, stride, nruns, ncells, ru.counts.p, ru.seg_start.p, ru.cell_off.p, n, t.perm.p, t.pts.p); break;
     }
     F3M_LAUNCH_CHECK();
-    F3M_CUDA(cudaStreamSynchronize(s));   // h_run_counts is the caller's host array
+    F3M_CUDA(cudaStreamSynchronize(s));
+    ru = Tree::Runs{};   // the tables are no longer needed
 }
 
 // Sorts the points of one tree by the first `depth` levels of their Morton key (all later levels are read off the

@@ -209,9 +209,18 @@ void build_root(Tree &t, cudaStream_t s) {
 
 // Appends the levels after the last one built, up to l_last, in batches of HB levels: two host synchronisations
 // per batch (box counts before the arrays are sized, largest boxes after the links).
+__global__ void __launch_bounds__(256) remap_offsets_kernel(int count, int *off, const int *__restrict__ fine_off) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) off[i] = fine_off[off[i]];
+}
+
 void build_levels(Tree &t, int l_last, f3m_plan *pl, cudaStream_t s) {
     F3M_REQUIRE(l_last <= t.sorted_depth, F3M_ERR_INTERNAL, "level %d requested, keys are sorted to level %d", l_last, t.sorted_depth);
-    const int64_t n = t.n;
+    // a tree that waits for its sorted runs: one pseudo key per occupied finest cell stands for the cell's points, and
+    // the box starts found among them are translated into offsets of the merged order
+    const bool from_cells = t.runs.pending;
+    const uint32_t *keys = from_cells ? t.runs.pkeys.p : t.keys.p;
+    const int64_t n = from_cells ? t.runs.nocc : t.n;
     const int nt = (int)((n + HTILE - 1) / HTILE);
     int *d_err = pl->d_flags + FL_ERR, *d_tot = pl->d_flags + FL_LVTOT, *d_max = pl->d_flags + FL_LVMAX;
     while ((int)t.levels.size() <= l_last) {
@@ -219,7 +228,7 @@ void build_levels(Tree &t, int l_last, f3m_plan *pl, cudaStream_t s) {
         const int nlev = std::min(HB, l_last - l_first + 1);
         DevBuf<int> part;
         part.alloc((size_t)nlev * nt, s);
-        heads_count<<<nt, HT, 0, s>>>(t.keys.p, n, t.d, t.lmax, l_first, nlev, nt, part.p);
+        heads_count<<<nt, HT, 0, s>>>(keys, n, t.d, t.lmax, l_first, nlev, nt, part.p);
         F3M_LAUNCH_CHECK();
         heads_scan<<<nlev, 1024, 0, s>>>(part.p, nt, d_tot);
         F3M_LAUNCH_CHECK();
@@ -235,8 +244,13 @@ void build_levels(Tree &t, int l_last, f3m_plan *pl, cudaStream_t s) {
             L.off.alloc((size_t)nb + 1, s); L.code.alloc(nb, s); L.parent.alloc(nb, s); L.ctr.alloc((size_t)nb * t.d, s);
             ho.off[v] = L.off.p; ho.code[v] = L.code.p; ho.nb[v] = nb;
         }
-        heads_write<<<nt, HT, 0, s>>>(t.keys.p, n, t.d, t.lmax, l_first, nlev, nt, part.p, ho);
+        heads_write<<<nt, HT, 0, s>>>(keys, n, t.d, t.lmax, l_first, nlev, nt, part.p, ho);
         F3M_LAUNCH_CHECK();
+        if (from_cells)
+            for (int v = 0; v < nlev; v++) {
+                remap_offsets_kernel<<<(unsigned)((ho.nb[v] + 1 + 255) / 256), 256, 0, s>>>(ho.nb[v] + 1, ho.off[v], t.runs.fine_off.p);
+                F3M_LAUNCH_CHECK();
+            }
         F3M_CUDA(cudaMemsetAsync(d_max, 0, nlev * sizeof(int), s));
         for (int v = 0; v < nlev; v++) {
             Level &L = t.levels[l_first + v], &P = t.levels[l_first + v - 1];

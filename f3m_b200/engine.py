@@ -56,41 +56,48 @@ def sort_depth(n_total: int, d: int, min_points: float) -> int:
 
 
 def sort_shard(X: torch.Tensor, row_offset: int, origin, edge0: float, math_mode: int, depth: int):
-    """One rank's share of a sort done by several GPUs (f3m_sort_shard_f32): the sorted records (n, words)."""
+    """One rank's share of a sort done by several GPUs (f3m_sort_shard_f32): the sorted records (n, words) and the
+    number of points in every cell of the sorted depth (2^(d depth) int32)."""
     X = _as_f32(X)
     n, d = X.shape
     words = int(_lib.lib().f3m_record_words(d))
     recs = torch.empty(n, words, device=X.device, dtype=torch.int32)
+    cells = torch.empty(1 << (d * depth), device=X.device, dtype=torch.int32)
     org = (C.c_float * d)(*[float(v) for v in origin])
     with torch.cuda.device(X.device):
         check(_lib.lib().f3m_sort_shard_f32(X.data_ptr(), n, int(row_offset), d, org, C.c_float(edge0), int(math_mode), int(depth),
-                                            recs.data_ptr(), _stream_ptr(X.device)), "f3m_sort_shard_f32")
-    return recs
+                                            recs.data_ptr(), cells.data_ptr(), _stream_ptr(X.device)), "f3m_sort_shard_f32")
+    return recs, cells
 
 
 class Plan:
     """Tree and interaction lists of one (X, Y) pair (f3m_plan); apply() multiplies by any b."""
 
     @classmethod
-    def from_runs(cls, recs: torch.Tensor, run_counts, run_stride: int, d: int, origin, edge0: float,
-                  depth: int, params: Params) -> "Plan":
-        """The plan of all points (Y = X) from runs that several GPUs sorted (f3m_plan_create_from_runs)."""
+    def from_cell_counts(cls, cell_counts: torch.Tensor, d: int, origin, edge0: float, depth: int, params: Params) -> "Plan":
+        """Levels and lists of all points (Y = X) from the cell counts of runs sorted on several GPUs, row r = run r
+        (f3m_plan_create_from_cell_counts).  attach_runs() must follow before any product."""
         self = cls.__new__(cls)
         self.X = self.Y = None
         self.same = True
         self.params = params
-        self.device = recs.device
-        self.N = self.M = int(sum(run_counts))
+        self.device = cell_counts.device
         self.d = d
         self._h = C.c_void_p()
-        counts = (C.c_int64 * len(run_counts))(*[int(c) for c in run_counts])
+        cell_counts = cell_counts.contiguous()
         org = (C.c_float * d)(*[float(v) for v in origin])
         with torch.cuda.device(self.device):
-            st = _lib.lib().f3m_plan_create_from_runs(C.byref(self._h), recs.data_ptr(), counts, len(run_counts),
-                                                      int(run_stride), d, org, C.c_float(edge0), int(depth), C.byref(params),
-                                                      _stream_ptr(self.device))
-        check(st, "f3m_plan_create_from_runs")
+            st = _lib.lib().f3m_plan_create_from_cell_counts(C.byref(self._h), cell_counts.data_ptr(), cell_counts.shape[0], d, org,
+                                                             C.c_float(edge0), int(depth), C.byref(params), _stream_ptr(self.device))
+        check(st, "f3m_plan_create_from_cell_counts")
+        self.N = self.M = int(cell_counts.sum().item())
         return self
+
+    def attach_runs(self, recs: torch.Tensor, run_stride: int):
+        """The gathered sorted runs (run r at record r * run_stride) are merged into the plan (f3m_plan_attach_runs)."""
+        with torch.cuda.device(self.device):
+            check(_lib.lib().f3m_plan_attach_runs(self._h, recs.data_ptr(), int(run_stride), _stream_ptr(self.device)),
+                  "f3m_plan_attach_runs")
 
     def __init__(self, X: torch.Tensor, Y: Optional[torch.Tensor], params: Params):
         if not X.is_cuda:

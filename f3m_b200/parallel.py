@@ -134,15 +134,23 @@ class EngineBackend:
             return None
         if clock:
             clock.mark("cube")
-        recs = engine.sort_shard(x_shard, sum(counts[:rank]), origin, edge0, params.math_mode, depth)
+        recs, cells = engine.sort_shard(x_shard, sum(counts[:rank]), origin, edge0, params.math_mode, depth)
         if clock:
             clock.mark("sort_shard")
-        recs_all, stride = gather_runs(recs, counts, group)
-        if clock:
-            clock.mark("gather_runs")
+        cells_all = torch.empty(len(counts) * cells.shape[0], device=dev, dtype=torch.int32)
+        _all_gather_equal(cells_all, cells, group, False)
+        recs_wait = gather_runs(recs, counts, group, async_op=True)      # the records travel while the lists are built
         try:
-            return engine.Plan.from_runs(recs_all, counts, stride, d, origin, edge0, depth, params)
+            plan = engine.Plan.from_cell_counts(cells_all.view(len(counts), -1), d, origin, edge0, depth, params)
+            if clock:
+                clock.mark("levels_lists")
+            recs_all, stride = recs_wait()
+            plan.attach_runs(recs_all, stride)
+            if clock:
+                clock.mark("merge_runs")
+            return plan
         except F3MError as e:
+            recs_wait()
             if e.status == 5:     # F3M_ERR_UNSUPPORTED: deeper than the shards were sorted (the same on every rank)
                 return None
             raise

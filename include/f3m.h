@@ -125,25 +125,28 @@ int f3m_plan_apply_range_moments(f3m_plan *plan, const float *b, int32_t R, floa
 /* A plan whose sort is shared by several GPUs (no counterpart in the reference).  Each rank sorts its own shard of
  * the points inside the GLOBAL bounding cube (origin = per-dimension minimum over all ranks, edge0 = 1.01f * largest
  * extent, both float32 as in calculate_edge_X, n_tree.cu:39-46) to the depth f3m_sort_depth gives for the TOTAL
- * point count; the sorted runs (records of f3m_record_words(d) 32-bit words per point: [input row, coordinates];
- * the keys follow from the coordinates and do not travel) are all-gathered, and every rank merges them into the
- * same plan.
- *   f3m_bounding_box_f32       per-dimension minimum and maximum of a shard (HOST arrays of d floats).
- *   f3m_sort_shard_f32         records_out (n records): the shard sorted; row_offset = input row of the shard's
- *                              first point in the whole set.
- *   f3m_plan_create_from_runs  records holds nruns runs, run r at record r * run_stride with run_counts[r] points
- *                              (HOST array); prm->math_mode must be the one the shards were sorted with.  The plan is that of f3m_plan_create on the whole set with Y = X,
- *                              except for the order of the points inside a finest sorted cell.  If the level loop
- *                              needs more levels than `depth` (strongly clustered points): F3M_ERR_UNSUPPORTED --
- *                              build the plan from the gathered points instead. */
+ * point count.  The levels and interaction lists follow from the number of points per finest sorted cell alone, so
+ * every rank builds them from the gathered cell counts (a few megabytes) while the sorted runs themselves (records of
+ * f3m_record_words(d) 32-bit words per point: [input row, coordinates]) are still being all-gathered, and merges
+ * the runs in afterwards.
+ *   f3m_bounding_box_f32              per-dimension minimum and maximum of a shard (HOST arrays of d floats).
+ *   f3m_sort_shard_f32                records_out (n records): the shard sorted; row_offset = input row of the
+ *                                     shard's first point in the whole set; cell_counts_out: 2^(d depth) counts.
+ *   f3m_plan_create_from_cell_counts  cell_counts: (nruns, 2^(d depth)) device array, row r = counts of run r.  The plan
+ *                                     is that of f3m_plan_create on the whole set with Y = X, except for the order of
+ *                                     the points inside a finest sorted cell (run by run).  If the level loop needs
+ *                                     more levels than `depth` (strongly clustered points): F3M_ERR_UNSUPPORTED --
+ *                                     build the plan from the gathered points instead.
+ *   f3m_plan_attach_runs              records: the gathered runs, run r at record r * run_stride.  Products can be
+ *                                     computed after this call. */
 int f3m_sort_depth(int64_t n_total, int32_t d, float min_points);
 int f3m_record_words(int32_t d);
 int f3m_bounding_box_f32(const float *X, int64_t n, int32_t d, float *min_out, float *max_out, void *stream);
 int f3m_sort_shard_f32(const float *X, int64_t n, int64_t row_offset, int32_t d, const float *origin, float edge0,
-                       int32_t math_mode, int32_t depth, void *records_out, void *stream);
-int f3m_plan_create_from_runs(f3m_plan **plan, const void *records, const int64_t *run_counts,
-                              int32_t nruns, int64_t run_stride, int32_t d, const float *origin, float edge0, int32_t depth,
-                              const f3m_params *prm, void *stream);
+                       int32_t math_mode, int32_t depth, void *records_out, int32_t *cell_counts_out, void *stream);
+int f3m_plan_create_from_cell_counts(f3m_plan **plan, const int32_t *cell_counts, int32_t nruns, int32_t d, const float *origin,
+                                     float edge0, int32_t depth, const f3m_params *prm, void *stream);
+int f3m_plan_attach_runs(f3m_plan *plan, const void *records, int64_t run_stride, void *stream);
 
 /* One product shared by several GPUs in phases, so that the exchange of the moments over NVLink runs while the
  * direct sums are computed (no counterpart in the reference: par_FFM_block runs independent block products,

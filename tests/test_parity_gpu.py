@@ -624,14 +624,20 @@ def test_plan_from_sorted_runs(name, cuda):
     stride = max(counts)
     words = _lib.lib().f3m_record_words(d)
     recs_all = torch.zeros(3 * stride, words, device=cuda, dtype=torch.int32)
+    cells = []
     for i in range(3):
-        r = engine.sort_shard(X[cuts[i]:cuts[i + 1]], cuts[i], origin, edge0, prm.math_mode, depth)
+        r, cnt = engine.sort_shard(X[cuts[i]:cuts[i + 1]], cuts[i], origin, edge0, prm.math_mode, depth)
         recs_all[i * stride:i * stride + counts[i]] = r
+        assert int(cnt.sum()) == counts[i]
+        cells.append(cnt)
     try:
-        plan = engine.Plan.from_runs(recs_all, counts, stride, d, origin, edge0, depth, prm)
+        plan = engine.Plan.from_cell_counts(torch.stack(cells), d, origin, edge0, depth, prm)
     except _lib.F3MError as e:
         assert e.status == 5 and ref.stats()["levels"] > depth     # deeper than the estimate: the documented refusal
         return
+    with pytest.raises(RuntimeError, match="sorted runs"):          # no product before the points are there
+        plan.apply(b)
+    plan.attach_runs(recs_all, stride)
     L = ref.stats()["levels"]
     assert plan.stats()["levels"] == L and plan.stats()["direct_pairs"] == ref.stats()["direct_pairs"]
     for l in range(1, L + 1):

@@ -9,7 +9,7 @@ N = M = 1e8 points i.i.d. Uniform[0, sqrt(12)]^3 (float32, seed 1), b ~ N(0,1) w
 lengthscale 1, 216 interpolation nodes (6 per dimension), min_points 1000, small_field_points 216.
 The data are synthetic (the reference's own sweeps draw the same distributions,
 experiments/experiments.py:41-66).  Other workloads, not run by default: c3 = 10-component Gaussian
-mixture (means U[-5,5]^3, std U[0.3,1]), lengthscale 0.5, 64 nodes (benchs_sparse/sparse_datasets.py:58-65
+mixture (means U[-5,5]^3, std U[0.3,1]), lengthscale 0.5, 216 nodes (benchs_sparse/sparse_datasets.py:58-65
 draws clustered data of this kind); c4 = N(0, I_d) in 4 or 5 dimensions with 8 columns.
 
 Prints ONE JSON line.  `value` = N*M / seconds with inputs resident in HBM; `e2e` = the same through the
@@ -48,7 +48,8 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4"])
-    ap.add_argument("--n", type=float, default=None, help="points (default: 1e8 for c2 and c3, 1e7 for c4)")
+    ap.add_argument("--n", "--points", dest="n", type=float, default=None,
+                    help="points (default: 1e8 for c2 and c3, 1e7 for c4); under torchrun write --points (its own parser claims --n)")
     ap.add_argument("--ls", type=float, default=None)
     ap.add_argument("--nodes", type=int, default=None, help="interpolation nodes per box (p^d)")
     ap.add_argument("--dim", type=int, default=None, help="c4: 4 or 5")
@@ -63,7 +64,7 @@ def parse():
     a.R = 8 if w == "c4" else 1
     a.n = a.n if a.n is not None else (1e7 if w == "c4" else 1e8)
     a.ls = a.ls if a.ls is not None else {"c2": 1.0, "c3": 0.5, "c4": 1.0}[w]
-    a.nodes = a.nodes if a.nodes is not None else {"c2": 216, "c3": 64, "c4": 3 ** a.d}[w]
+    a.nodes = a.nodes if a.nodes is not None else {"c2": 216, "c3": 216, "c4": 3 ** a.d}[w]
     return a
 
 
@@ -85,8 +86,9 @@ def draw_points(a, n, device, generator):
         return torch.empty(n, 3, device=device).uniform_(0, SQRT12, generator=generator)
     if a.workload == "c4":
         return torch.randn(n, a.d, device=device, generator=generator)
-    means = torch.rand(10, 3, device=device, generator=generator) * 10 - 5
-    std = torch.rand(10, device=device, generator=generator) * 0.7 + 0.3
+    gm = torch.Generator().manual_seed(7)     # the mixture itself is the same for every rank and every sample
+    means = (torch.rand(10, 3, generator=gm) * 10 - 5).to(device)
+    std = (torch.rand(10, generator=gm) * 0.7 + 0.3).to(device)
     comp = torch.randint(0, 10, (n,), device=device, generator=generator)
     X = torch.randn(n, 3, device=device, generator=generator)
     X.mul_(std[comp, None]).add_(means[comp])
@@ -317,6 +319,8 @@ def main():
         line["slice_rows"] = [int(v.item()) for v in rows_all]
         # error: every rank checks check_rows / world rows of its own shard against the float64 dense product
         n_check = max(1, a.check_rows // world)
+        torch.cuda.empty_cache()
+        engine.release_cached_memory()
         Xall = torch.empty(N, d, device=dev)
         ball = torch.empty(N, R, device=dev)
         counts = [(r + 1) * N // world - r * N // world for r in range(world)]

@@ -396,5 +396,10 @@ def measure_peaks(device=None) -> Dict:
     return {"gexp_per_s": a.value, "gfma_per_s": b.value}
 
 
+def release_cached_memory():
+    """Returns the device blocks the library keeps for reuse to the driver (f3m_release_cached_memory)."""
+    check(_lib.lib().f3m_release_cached_memory(), "f3m_release_cached_memory")
+
+
 def launch_count() -> int:
     return int(_lib.lib().f3m_launch_count())

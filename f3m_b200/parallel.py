@@ -104,6 +104,9 @@ def gather_runs(t_shard: torch.Tensor, counts: List[int], group=None, async_op: 
     return finish if async_op else (buf, mx)
 
 
+_TOO_DEEP = set()   # (N, d, min_points) of point sets whose tree went deeper than the shards are sorted: skip the attempt
+
+
 class EngineBackend:
     """The CUDA engine behind the phases of distributed_kmvm (a test may pass a stand-in with the same methods)."""
 
@@ -119,7 +122,7 @@ class EngineBackend:
         from . import engine
         from ._lib import F3MError
         dev, d, N = x_shard.device, x_shard.shape[1], sum(counts)
-        if min(counts) < 1:
+        if min(counts) < 1 or (N, d, float(params.min_points)) in _TOO_DEEP:
             return None
         lo, hi = engine.bounding_box(x_shard)
         box = torch.tensor([lo, [-v for v in hi]], device=dev, dtype=torch.float32)
@@ -152,6 +155,7 @@ class EngineBackend:
         except F3MError as e:
             recs_wait()
             if e.status == 5:     # F3M_ERR_UNSUPPORTED: deeper than the shards were sorted (the same on every rank)
+                _TOO_DEEP.add((N, d, float(params.min_points)))
                 return None
             raise
 
@@ -199,7 +203,7 @@ def distributed_kmvm(x_shard: torch.Tensor, b_shard: torch.Tensor, params, group
     R = b_shard.shape[1]
 
     b_wait = gather_shards(b_shard, counts, group, async_op=True)    # lands while the tree is built
-    plan = None
+    plan = X = None
     if world > 1 and hasattr(backend, "plan_from_shards"):
         plan = backend.plan_from_shards(x_shard, counts, rank, params, group, clock)
     if plan is None:
@@ -207,6 +211,16 @@ def distributed_kmvm(x_shard: torch.Tensor, b_shard: torch.Tensor, params, group
         clock.mark("gather_points")
         plan = backend.plan(X, params)
     clock.mark("tree_lists")
+    if dev.type == "cuda" and float(N) * (x_shard.shape[1] + R) * 4 > 4e9:
+        # Very large sets: what was only needed to build the plan (the gathered points or runs in torch's pool, the
+        # sort's buffers in the library's) goes back to the driver before the product's own arrays are sized.
+        X = None
+        if hasattr(plan, "X"):
+            plan.X = plan.Y = None
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        from . import engine as _engine
+        _engine.release_cached_memory()
     bounds = plan.partition_rows(R, world)
     if world > 1:
         # every rank computes the same cuts from the same plan; rank 0's copy is the one used, so that a difference

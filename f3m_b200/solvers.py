@@ -76,6 +76,17 @@ def _gaussian(A, B, ls):
     return torch.exp(-torch.cdist(A, B).pow(2) / (2 * ls * ls))
 
 
+def _gaussian_blocked(C, ls, dtype, rows=8192):
+    """K(C, C) in `dtype`, filled block of rows by block of rows (distances in float64) so that no second m x m array
+    exists while it is built."""
+    m = C.shape[0]
+    K = torch.empty(m, m, device=C.device, dtype=dtype)
+    Cd = C.double()
+    for s0 in range(0, m, rows):
+        K[s0:s0 + rows] = _gaussian(Cd[s0:s0 + rows], Cd, ls).to(dtype)
+    return K
+
+
 class nystrom_preconditioner:
     """P = lamb I + K_nm K_mm^-1 K_mn applied through the Woodbury identity (conjugate_gradient.py:91-109)."""
 
@@ -140,27 +151,30 @@ def PreConditionedConjugateGradientSolver(binding, preconditioner, kmvm_object, 
 
 
 def build_tridiagonalization_matrices(alphas, betas):
-    """Lanczos tridiagonal matrices from the CG coefficients, one per column (conjugate_gradient.py:155-170)."""
-    mats = []
-    for i in range(alphas.shape[1]):
-        a_prev = alphas[:, i].clone()
-        a_prev[0] = 0.0
-        b_prev = betas[:, i].clone()
-        b_prev[0] = 0.0
-        diag = 1 / alphas[:, i] + torch.nan_to_num(b_prev / a_prev, nan=0.0)
-        off = betas[1:, i] ** 0.5 / alphas[1:, i]
-        s = torch.diag(off, 1)
-        mats.append(torch.diag(diag) + s + s.t())
-    return torch.stack(mats, 0)
+    """Lanczos tridiagonal matrices of the CG run, one per column (conjugate_gradient.py:155-170): with step lengths
+    a_k and ratios b_k of one column, T has diagonal 1/a_k + b_{k-1}/a_{k-1} (second term absent for k = 0) and
+    off-diagonal sqrt(b_k)/a_k, k >= 1.  All columns are assembled at once as a batch."""
+    a, b = alphas.t(), betas.t()                                  # (columns, iterations)
+    k = a.shape[1]
+    diag = a.reciprocal()
+    if k > 1:
+        diag[:, 1:] += torch.nan_to_num(b[:, 1:] / a[:, 1:], nan=0.0)     # b and a of iteration k, as the reference pairs them
+        off = b[:, 1:].sqrt() / a[:, 1:]
+    T = torch.diag_embed(diag)
+    if k > 1:
+        T = T + torch.diag_embed(off, offset=1) + torch.diag_embed(off, offset=-1)
+    return T
 
 
 def calculate_log_kxx(T_list):
-    val, _ = torch.linalg.eigvalsh(T_list).max(1)
-    return val.log().mean().item()
+    """Mean over the columns of the log of the largest Ritz value (conjugate_gradient.py:143-147)."""
+    return torch.linalg.eigvalsh(T_list)[:, -1].log().mean().item()
 
 
 def get_GP_likelihood(alpha, y, alpha_mat, beta_mat):
-    return calculate_log_kxx(build_tridiagonalization_matrices(alpha_mat, beta_mat)) - torch.sum(alpha * y).item()
+    """conjugate_gradient.py:149-153: spectral term of the Lanczos matrices minus the data fit alpha . y."""
+    spectral = calculate_log_kxx(build_tridiagonalization_matrices(alpha_mat, beta_mat))
+    return spectral - float((alpha * y).sum())
 
 
 # ------------------------------------------------------------------------------------------------
@@ -184,8 +198,13 @@ class F3MGaussianKernel:
         self._key = None
 
     def _operators(self, X1, X2):
-        key = (X1.data_ptr(), X1._version, tuple(X1.shape), X2.data_ptr(), X2._version, tuple(X2.shape))
-        if self._key != key:
+        # The key holds the caller's tensors themselves (identity, not address: an address can be recycled by another
+        # tensor of the same shape once the first is freed) and every parameter the operators are built with.
+        key = (X1, X1._version, X2, X2._version, self.ls, self.min_points, self.interpolation_nr, self.var_compression,
+               self.eff_var_limit)
+        same = self._key is not None and len(self._key) == len(key) and all(
+            (a is b) if torch.is_tensor(a) else (a == b) for a, b in zip(self._key, key))
+        if not same:
             mp = self.min_points if self.min_points is not None else 4 ** X1.shape[1]
             kw = dict(ls=self.ls, min_points=mp, nr_of_interpolation=self.interpolation_nr, eff_var_limit=self.eff_var_limit,
                       var_compression=self.var_compression, small_field_points=self.interpolation_nr, device=self.device)
@@ -229,17 +248,28 @@ class Falkon:
         g = torch.Generator().manual_seed(self.seed)
         C = X[torch.randperm(n, generator=g)[:m].to(dev)].contiguous()
         ls, lam = self.kernel.ls, self.penalty
-        # preconditioner: K_mm = T^T T,  A^T A = T T^T / m + lambda I   (float64 factorisations, m x m)
-        Kmm = _gaussian(C.double(), C.double(), ls)
-        Kmm.diagonal().add_(self.jitter * m)
-        T = torch.linalg.cholesky(Kmm, upper=True)
-        A = torch.linalg.cholesky(T @ T.t() / m + lam * torch.eye(m, device=dev, dtype=torch.float64), upper=True)
-        del Kmm
-        solve = torch.linalg.solve_triangular
-        invT = lambda v: solve(T, v, upper=True)
-        invTt = lambda v: solve(T.t(), v, upper=False)
-        invA = lambda v: solve(A, v, upper=True)
-        invAt = lambda v: solve(A.t(), v, upper=False)
+        # preconditioner: K_mm = T^T T,  A^T A = T T^T / m + lambda I.  Two m x m factors are kept; they are float64 up
+        # to m = 20000 and float32 beyond (m = 1e5: 2 x 40 GB instead of 2 x 80 GB, which would leave no room for the
+        # products), and every m x m step reuses the buffer of its input.
+        fdt = torch.float64 if m <= 20000 else torch.float32
+        T = _gaussian_blocked(C, ls, fdt)
+        T.diagonal().add_(self.jitter * m)
+        torch.linalg.cholesky(T, upper=True, out=T)
+        T.triu_()
+        A = torch.empty_like(T)
+        torch.mm(T, T.t(), out=A)
+        A.div_(m)
+        A.diagonal().add_(lam)
+        torch.linalg.cholesky(A, upper=True, out=A)
+        A.triu_()
+        solve_tri = torch.linalg.solve_triangular
+
+        def solve(M_, v, upper):   # right-hand sides stay float64; the factor's precision is the preconditioner's
+            return solve_tri(M_, v.to(fdt), upper=upper).double()
+        invT = lambda v: solve(T, v, True)
+        invTt = lambda v: solve(T.t(), v, False)
+        invA = lambda v: solve(A, v, True)
+        invAt = lambda v: solve(A.t(), v, False)
 
         def op(beta):   # falkon_mmv (custom_conjugate_gradient_falkon.py:144-160)
             v = invA(beta)

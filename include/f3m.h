@@ -12,6 +12,11 @@
  * stream).  Work is enqueued on that stream; the call returns after the stream has been
  * synchronised, because list sizes are read back on the host while the tree is built.
  *
+ * Threading: calls that use one device must be serialised by the caller (one host thread at a time per
+ * device, or an external lock).  The library reuses device blocks it has released as soon as later work is
+ * enqueued on the same stream; a second host thread on another stream of the same device could be handed a
+ * block that queued kernels still read.  A plan must not be used from two host threads at once.
+ *
  * Each declaration names the interface of the reference implementation (MrHuff/F3M) that it
  * replaces, as path:line inside that repository.
  */

@@ -56,6 +56,9 @@ SIGNATURES = {
     "f3m_status_string": (C.c_char_p, [C.c_int]),
     "f3m_last_error": (C.c_char_p, []),
     "f3m_kmvm_f32": (C.c_int, [_P, _I64, _P, _I64, _P, _I32, _I32, C.POINTER(Params), _P, _P]),
+    "f3m_workspace_bytes": (C.c_size_t, [_I64, _I64, _I32, _I32, C.POINTER(Params)]),
+    "f3m_kmvm_ws_f32": (C.c_int, [_P, _I64, _P, _I64, _P, _I32, _I32, C.POINTER(Params), _P, _P, C.c_size_t, _P]),
+    "f3m_last_workspace_peak": (C.c_size_t, []),
     "f3m_kmvm_host_f32": (C.c_int, [_P, _I64, _P, _I64, _P, _I32, _I32, C.POINTER(Params), _P]),
     "f3m_plan_create": (C.c_int, [C.POINTER(_P), _P, _I64, _P, _I64, _I32, C.POINTER(Params), _P]),
     "f3m_plan_apply": (C.c_int, [_P, _P, _I32, _P, _P]),

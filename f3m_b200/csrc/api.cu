@@ -7,6 +7,7 @@
 #include <math.h>
 #include <algorithm>
 #include <mutex>
+#include <utility>
 #include <vector>
 #include "common.cuh"
 
@@ -35,7 +36,68 @@ size_t round_request(size_t bytes) {
 }
 }  // namespace
 
+// ---- caller-owned workspace ---------------------------------------------------------------------
+// While a thread runs an entry point that was given a workspace, every device buffer of the library comes out of
+// that memory: a first-fit list of free ranges, 256-byte granularity, neighbours merged on release.  Nothing is
+// taken from or returned to the driver.
+namespace {
+struct Arena {
+    char *base = nullptr;
+    size_t size = 0, used = 0, peak = 0;
+    std::vector<std::pair<size_t, size_t>> free_ranges;   // (offset, length), sorted by offset
+    void reset(void *p, size_t n) {
+        base = static_cast<char *>(p);
+        const size_t mis = (256 - (reinterpret_cast<uintptr_t>(p) & 255)) & 255;   // first 256-byte boundary inside
+        size = n > mis ? n - mis : 0;
+        base += mis;
+        used = peak = 0;
+        free_ranges.assign(1, {0, size / 256 * 256});
+    }
+    void *take(size_t bytes, size_t *granted) {
+        const size_t need = (bytes + 255) / 256 * 256;
+        for (size_t i = 0; i < free_ranges.size(); i++) {
+            if (free_ranges[i].second < need) continue;
+            const size_t off = free_ranges[i].first;
+            if (free_ranges[i].second == need) free_ranges.erase(free_ranges.begin() + i);
+            else { free_ranges[i].first += need; free_ranges[i].second -= need; }
+            used += need;
+            peak = std::max(peak, used);
+            *granted = need;
+            return base + off;
+        }
+        return nullptr;
+    }
+    bool owns(const void *p) const { return p >= base && p < base + size; }
+    void give(void *p, size_t len) {
+        const size_t off = static_cast<char *>(p) - base;
+        used -= len;
+        size_t i = 0;
+        while (i < free_ranges.size() && free_ranges[i].first < off) i++;
+        free_ranges.insert(free_ranges.begin() + i, {off, len});
+        if (i + 1 < free_ranges.size() && free_ranges[i].first + free_ranges[i].second == free_ranges[i + 1].first) {
+            free_ranges[i].second += free_ranges[i + 1].second;
+            free_ranges.erase(free_ranges.begin() + i + 1);
+        }
+        if (i > 0 && free_ranges[i - 1].first + free_ranges[i - 1].second == free_ranges[i].first) {
+            free_ranges[i - 1].second += free_ranges[i].second;
+            free_ranges.erase(free_ranges.begin() + i);
+        }
+    }
+};
+thread_local Arena *g_arena = nullptr;
+thread_local size_t g_last_ws_peak = 0;
+}  // namespace
+
 void *dev_alloc(size_t bytes, size_t *granted) {
+    if (g_arena) {
+        void *p = g_arena->take(bytes ? bytes : 1, granted);
+        if (!p) {
+            set_error("the workspace of %zu bytes is too small: %zu bytes are in use and %zu more were requested "
+                      "(f3m_workspace_bytes gives an estimate; clustered point sets need more)", g_arena->size, g_arena->used, bytes);
+            throw Fail{F3M_ERR_TOO_LARGE};
+        }
+        return p;
+    }
     const size_t need = round_request(bytes);
     int dev = 0;
     F3M_CUDA(cudaGetDevice(&dev));
@@ -76,6 +138,7 @@ void *dev_alloc(size_t bytes, size_t *granted) {
 }
 
 void dev_free(void *p, size_t granted) {
+    if (g_arena && g_arena->owns(p)) { g_arena->give(p, granted); return; }
     int dev = 0;
     cudaGetDevice(&dev);
     cudaPointerAttributes attr;
@@ -696,6 +759,36 @@ int f3m_kmvm_f32(const float *X, int64_t N, const float *Y, int64_t M, const flo
     st = f3m_plan_apply(pl, b, R, out, stream);
     f3m_plan_destroy(pl);
     return st;
+}
+
+size_t f3m_workspace_bytes(int64_t N, int64_t M, int32_t R, int32_t d, const f3m_params *prm) {
+    if (N < 1 || M < 1 || R < 1 || d < 1 || d > F3M_MAX_DIM || !prm) return 0;
+    const double n = (double)N, m = (double)M, pts = n + m;
+    const int RB = R == 1 ? 1 : 8, W = (d + RB + 3) / 4 * 4, RW = record_words(d);
+    const int p = nodes_per_dim(d, prm->nr_interpolation);
+    double P = 1;
+    for (int k = 0; k < d; k++) P *= p;
+    // boxes of the last level when the level loop stops at boxes of at most min_points points (evenly spread points)
+    const double boxes = std::max(1.0, pts * pow(2.0, d) / std::max(1.0f, prm->min_points));
+    const double sort_peak = pts * (12.0 + 4.0 * d + 8.0 + 8.0 * RW);                       // keys, records (twice), planes
+    const double tree = pts * (8.0 + 4.0 * d) + boxes * (pow(6.0, d) + 2.0 * pow(3.0, d)) * 12.0 + 64.0 * boxes;
+    const double product = 4.0 * R * (n + m) + 4.0 * W * (m + boxes) + 2.3 * boxes * P * RB * 4.0 + 8.0 * boxes;
+    return (size_t)(1.15 * std::max(sort_peak + pts * (8.0 + 4.0 * d), tree + product)) + ((size_t)64 << 20);
+}
+
+size_t f3m_last_workspace_peak(void) { return g_last_ws_peak; }
+
+int f3m_kmvm_ws_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R, int32_t d,
+                    const f3m_params *prm, float *out, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!workspace || workspace_bytes < 4096) return F3M_ERR_ARG;
+    Arena arena;
+    arena.reset(workspace, workspace_bytes);
+    struct Scope {   // every buffer of the call is gone before the arena is
+        Arena *prev;
+        explicit Scope(Arena *a) : prev(g_arena) { g_arena = a; }
+        ~Scope() { g_last_ws_peak = g_arena->peak; g_arena = prev; }
+    } scope(&arena);
+    return f3m_kmvm_f32(X, N, Y, M, b, R, d, prm, out, stream);
 }
 
 int f3m_kmvm_host_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R, int32_t d,

@@ -948,16 +948,16 @@ void dense_f64(const double *X, int64_t N, const double *Y, int64_t M, const dou
 static __device__ __align__(256) float g_static_scratch[F3M_STATIC_SCRATCH_FLOATS];
 
 static float *static_scratch_for_current_device() {
-    static float *ptr_of_device[64] = {nullptr};
+    static std::atomic<float *> ptr_of_device[64];   // zero-initialised; two threads may both look the address up, both get the same
     int dev = 0;
     F3M_CUDA(cudaGetDevice(&dev));
     F3M_REQUIRE(dev >= 0 && dev < 64, F3M_ERR_UNSUPPORTED, "device ordinal %d not supported by the static entry point", dev);
-    if (!ptr_of_device[dev]) {
-        float *p = nullptr;
+    float *p = ptr_of_device[dev].load(std::memory_order_acquire);
+    if (!p) {
         F3M_CUDA(cudaGetSymbolAddress((void **)&p, g_static_scratch));
-        ptr_of_device[dev] = p;
+        ptr_of_device[dev].store(p, std::memory_order_release);
     }
-    return ptr_of_device[dev];
+    return p;
 }
 
 template <int D>

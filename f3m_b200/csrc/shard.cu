@@ -316,20 +316,33 @@ __global__ void __launch_bounds__(256) box_work_kernel(int nbx, const int *__res
     if (w > 0.0) atomicAdd(&work[lower_bound_i32(off_fine, nb_fine, off_x[box])], (unsigned long long)llrint(w) + 1ull);
 }
 
-// one block: running sum of the work over the finest-level boxes, cuts where it passes k / nparts of the total
-__global__ void __launch_bounds__(1024) partition_kernel(int nb, const unsigned long long *__restrict__ work,
-                                                        const int *__restrict__ off, int nparts, long long *bounds) {
-    __shared__ unsigned long long part[1024];
-    __shared__ unsigned long long total_s;
-    const int per = (nb + 1023) / 1024;
-    const int j0 = min(nb, (int)threadIdx.x * per), j1 = min(nb, j0 + per);
+// sums of the work over tiles of PART_TILE consecutive finest-level boxes
+constexpr int PART_TILE = 4096;
+__global__ void __launch_bounds__(256) work_tile_sums(int nb, const unsigned long long *__restrict__ work, unsigned long long *tile_sum) {
+    __shared__ unsigned long long part[8];
+    const int j0 = blockIdx.x * PART_TILE;
     unsigned long long s = 0;
-    for (int j = j0; j < j1; j++) s += work[j];
-    part[threadIdx.x] = s;
+    for (int j = j0 + threadIdx.x; j < min(nb, j0 + PART_TILE); j += blockDim.x) s += work[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
     __syncthreads();
     if (threadIdx.x == 0) {
+        unsigned long long t = 0;
+        for (int w = 0; w < 8; w++) t += part[w];
+        tile_sum[blockIdx.x] = t;
+    }
+}
+
+// one block: running sum over the tiles, then inside the few tiles where it passes k / nparts of the total.  All sums
+// are integers, so every rank computes the same cuts from the same plan.
+__global__ void __launch_bounds__(1024) partition_kernel(int nb, int ntiles, const unsigned long long *__restrict__ work,
+                                                        unsigned long long *tile_sum, const int *__restrict__ off, int nparts,
+                                                        long long *bounds) {
+    __shared__ unsigned long long total_s;
+    if (threadIdx.x == 0) {
         unsigned long long run = 0;
-        for (int t = 0; t < 1024; t++) { const unsigned long long v = part[t]; part[t] = run; run += v; }
+        for (int t = 0; t < ntiles; t++) { const unsigned long long v = tile_sum[t]; tile_sum[t] = run; run += v; }   // exclusive, in place
         total_s = run;
         bounds[0] = 0;
         bounds[nparts] = off[nb];
@@ -345,14 +358,17 @@ __global__ void __launch_bounds__(1024) partition_kernel(int nb, const unsigned 
             }
         return;
     }
-    unsigned long long run = part[threadIdx.x];
-    for (int j = j0; j < j1; j++) {
-        const unsigned long long before = run;
-        run += work[j];
-        // cut k lies after box j when the running sum passes k * total / nparts inside this box (the sums are integers,
-        // so every rank computes the same cuts from the same plan)
-        const int k0 = (int)((double)before * nparts / (double)total), k1 = (int)((double)run * nparts / (double)total);
-        for (int k = k0 + 1; k <= k1 && k < nparts; k++) bounds[k] = off[j + 1];
+    for (int t = threadIdx.x; t < ntiles; t += blockDim.x) {
+        const unsigned long long before_tile = tile_sum[t], after_tile = t + 1 < ntiles ? tile_sum[t + 1] : total;
+        if ((int)((double)before_tile * nparts / (double)total) == (int)((double)after_tile * nparts / (double)total)) continue;
+        unsigned long long run = before_tile;
+        for (int j = t * PART_TILE; j < min(nb, (t + 1) * PART_TILE); j++) {
+            const unsigned long long before = run;
+            run += work[j];
+            // cut k lies after box j when the running sum passes k * total / nparts inside this box
+            const int k0 = (int)((double)before * nparts / (double)total), k1 = (int)((double)run * nparts / (double)total);
+            for (int k = k0 + 1; k <= k1 && k < nparts; k++) bounds[k] = off[j + 1];
+        }
     }
 }
 
@@ -387,7 +403,12 @@ void shard_partition(f3m_plan *pl, int R, int nparts, int64_t *h_bounds, cudaStr
     }
     DevBuf<long long> bounds;
     bounds.alloc((size_t)nparts + 1, s);
-    partition_kernel<<<1, 1024, 0, s>>>(lf.nb, work.p, lf.off.p, nparts, bounds.p);
+    const int ntiles = (lf.nb + PART_TILE - 1) / PART_TILE;
+    DevBuf<unsigned long long> tile_sum;
+    tile_sum.alloc((size_t)ntiles, s);
+    work_tile_sums<<<ntiles, 256, 0, s>>>(lf.nb, work.p, tile_sum.p);
+    F3M_LAUNCH_CHECK();
+    partition_kernel<<<1, 1024, 0, s>>>(lf.nb, ntiles, work.p, tile_sum.p, lf.off.p, nparts, bounds.p);
     F3M_LAUNCH_CHECK();
     std::vector<long long> h((size_t)nparts + 1);
     F3M_CUDA(cudaMemcpyAsync(h.data(), bounds.p, ((size_t)nparts + 1) * sizeof(long long), cudaMemcpyDeviceToHost, s));

@@ -341,6 +341,36 @@ def kmvm(X, Y, b, params: Params) -> torch.Tensor:
     return out
 
 
+def workspace_bytes(N: int, M: int, R: int, d: int, params: Params) -> int:
+    """Estimated bytes of temporaries of one product (f3m_workspace_bytes)."""
+    return int(_lib.lib().f3m_workspace_bytes(int(N), int(M), int(R), int(d), C.byref(params)))
+
+
+def kmvm_ws(X, Y, b, params: Params, workspace: torch.Tensor) -> torch.Tensor:
+    """One-shot product whose temporaries all come out of `workspace`, a CUDA tensor the caller owns
+    (f3m_kmvm_ws_f32): the library requests nothing from the driver during the call."""
+    same = is_shared(X, Y)
+    X = _as_f32(X)
+    Y = X if same else _as_f32(Y)
+    b = _as_f32(b)
+    if b.dim() == 1:
+        b = b[:, None]
+    _check_product_shapes(X, Y, b)
+    if not (X.is_cuda and Y.is_cuda and b.is_cuda and workspace.is_cuda and workspace.is_contiguous()):
+        raise ValueError("kmvm_ws needs CUDA tensors and a contiguous CUDA workspace")
+    out = torch.empty(X.shape[0], b.shape[1], device=X.device, dtype=torch.float32)
+    with torch.cuda.device(X.device):
+        st = _lib.lib().f3m_kmvm_ws_f32(X.data_ptr(), X.shape[0], Y.data_ptr(), Y.shape[0], b.data_ptr(), b.shape[1],
+                                        X.shape[1], C.byref(params), out.data_ptr(), workspace.data_ptr(),
+                                        workspace.numel() * workspace.element_size(), _stream_ptr(X.device))
+    check(st, "f3m_kmvm_ws_f32")
+    return out
+
+
+def last_workspace_peak() -> int:
+    return int(_lib.lib().f3m_last_workspace_peak())
+
+
 def kmvm_host(X, Y, b, params: Params, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Product with HOST tensors through f3m_kmvm_host_f32: H2D copies, product, D2H copy in one call."""
     same = is_shared(X, Y)

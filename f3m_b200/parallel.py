@@ -114,9 +114,14 @@ class EngineBackend:
         from . import engine
         return engine.Plan(X, None, params)
 
-    def plan_from_shards(self, x_shard: torch.Tensor, counts: List[int], rank: int, params, group, clock=None):
-        """The plan of all points with the sort shared by the ranks: global bounding cube (two tiny all-reduces), every
-        rank sorts its shard, the sorted runs are all-gathered and merged.  None when that form does not apply (the
+    def bounding_box(self, x_shard: torch.Tensor):
+        from . import engine
+        return engine.bounding_box(x_shard)
+
+    def plan_from_shards(self, x_shard: torch.Tensor, counts: List[int], rank: int, params, group, origin, top, clock=None):
+        """The plan of all points with the sort shared by the ranks: inside the global bounding cube (origin, top: the
+        per-dimension extremes over all ranks) every rank sorts its shard, levels and lists are built from the gathered
+        cell counts while the sorted runs travel, and the runs are merged in.  None when that form does not apply (the
         level loop would need more levels than the shards were sorted to): the caller gathers the points instead."""
         import numpy as np
         from . import engine
@@ -124,11 +129,7 @@ class EngineBackend:
         dev, d, N = x_shard.device, x_shard.shape[1], sum(counts)
         if min(counts) < 1 or (N, d, float(params.min_points)) in _TOO_DEEP:
             return None
-        lo, hi = engine.bounding_box(x_shard)
-        box = torch.tensor([lo, [-v for v in hi]], device=dev, dtype=torch.float32)
-        dist.all_reduce(box, op=dist.ReduceOp.MIN, group=group)
-        box = box.cpu().numpy()
-        origin, top = box[0], -box[1]
+        origin, top = np.asarray(origin, dtype=np.float32), np.asarray(top, dtype=np.float32)
         edge0 = float(np.float32((top - origin).max()) * np.float32(1.01))     # calculate_edge_X, float32
         if not (np.isfinite(edge0) and edge0 > 0):
             return None    # the single-GPU path reports degenerate or non-finite point sets
@@ -193,10 +194,18 @@ def distributed_kmvm(x_shard: torch.Tensor, b_shard: torch.Tensor, params, group
     clock = _Clock(dev, stats)
     if b_shard.dim() == 1:
         b_shard = b_shard[:, None]
-    n_local = torch.tensor([x_shard.shape[0]], device=dev, dtype=torch.int64)
-    all_n = [torch.zeros_like(n_local) for _ in range(world)]
-    dist.all_gather(all_n, n_local, group=group)
-    counts = torch.stack(all_n).flatten().tolist()
+    # one small all-gather brings the shard sizes and, for the shared sort, the shards' bounding boxes
+    d = x_shard.shape[1]
+    use_shards = world > 1 and hasattr(backend, "plan_from_shards") and x_shard.shape[0] > 0
+    head = [float(x_shard.shape[0])]
+    if hasattr(backend, "plan_from_shards"):
+        lo, hi = backend.bounding_box(x_shard) if x_shard.shape[0] > 0 else ([float("inf")] * d, [float("-inf")] * d)
+        head += list(lo) + list(hi)
+    mine = torch.tensor(head, device=dev, dtype=torch.float64)
+    table = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(table, mine, group=group)
+    table = torch.stack(table).cpu()
+    counts = [int(v) for v in table[:, 0].tolist()]
     N = sum(counts)
     in_lo = sum(counts[:rank])
     in_hi = in_lo + counts[rank]
@@ -204,8 +213,10 @@ def distributed_kmvm(x_shard: torch.Tensor, b_shard: torch.Tensor, params, group
 
     b_wait = gather_shards(b_shard, counts, group, async_op=True)    # lands while the tree is built
     plan = X = None
-    if world > 1 and hasattr(backend, "plan_from_shards"):
-        plan = backend.plan_from_shards(x_shard, counts, rank, params, group, clock)
+    if use_shards and min(counts) > 0:
+        origin = table[:, 1:1 + d].min(0).values.float().numpy()
+        top = table[:, 1 + d:1 + 2 * d].max(0).values.float().numpy()
+        plan = backend.plan_from_shards(x_shard, counts, rank, params, group, origin, top, clock)
     if plan is None:
         X = gather_shards(x_shard, counts, group)
         clock.mark("gather_points")

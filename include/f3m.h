@@ -96,6 +96,20 @@ const char *f3m_last_error(void);
 int f3m_kmvm_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R,
                  int32_t d, const f3m_params *prm, float *out, void *stream);
 
+/* The same product with every temporary taken from memory the CALLER owns (SURVEY of the reference's interface:
+ * FFM_XY allocates through torch, n_tree.cu:1061 and throughout; a host that hands out memory from its own
+ * allocator passes a slice of it here).  workspace: device memory of workspace_bytes bytes, free for the duration
+ * of the call; nothing is requested from or returned to the driver inside the call, apart from a per-device slot of
+ * 1 KB of flags and pinned read-back words that the library creates the first time a device is used.
+ * f3m_workspace_bytes estimates the need for evenly spread points (sort buffers, tree, lists, packed sources,
+ * moments); strongly clustered sets build deeper trees and need more.  A workspace that runs out ends the call
+ * with F3M_ERR_TOO_LARGE and a message that names the request; f3m_last_workspace_peak returns the high-water
+ * mark of this thread's last f3m_kmvm_ws_f32 call (bytes), for sizing after a trial run. */
+size_t f3m_workspace_bytes(int64_t N, int64_t M, int32_t R, int32_t d, const f3m_params *prm);
+int f3m_kmvm_ws_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R, int32_t d,
+                    const f3m_params *prm, float *out, void *workspace, size_t workspace_bytes, void *stream);
+size_t f3m_last_workspace_peak(void);
+
 /* Same product with HOST buffers: copies X, Y, b to the device, runs f3m_kmvm_f32 and copies the
  * result back, all inside the call.  This is what a caller holding CPU tensors pays end to end
  * (FFM.__init__/__matmul__ move X, Y, b to the device, experiments/FFM_classes.py:23-50). */

@@ -648,3 +648,35 @@ def test_plan_from_sorted_runs(name, cuda):
     perm = plan.array(0, 0, _lib.ARR_SORTED_INDEX)
     assert np.array_equal(np.sort(perm), np.arange(N))
     assert rel_l2(plan.apply(b).cpu(), full.cpu()) <= 2e-6
+
+
+def test_product_in_a_caller_owned_workspace(cuda):
+    """f3m_kmvm_ws_f32: every temporary comes out of a tensor the caller owns.  Same result as the allocating entry
+    point; the driver's free memory does not move during the call; a workspace that is too small is a clean error; the
+    size estimate covers evenly spread points, and the reported peak says how much was really used."""
+    from f3m_b200 import engine, _lib
+    g = torch.Generator().manual_seed(71)
+    for (n, m, d, R, P) in ((300000, None, 3, 1, 64), (60000, 40000, 2, 3, 36), (50000, None, 4, 8, 81)):
+        X = torch.rand(n, d, generator=g).to(cuda)
+        Y = None if m is None else torch.rand(m, d, generator=g).to(cuda)
+        b = torch.randn(n if m is None else m, R, generator=g).to(cuda)
+        prm = engine.make_params(0.7, 300.0, P, False, 0.15, P)
+        ref = engine.kmvm(X, Y, b, prm)
+        need = engine.workspace_bytes(n, m or n, R, d, prm)
+        ws = torch.empty(need, dtype=torch.uint8, device=cuda)
+        engine.kmvm_ws(X, Y, b, prm, ws)                      # first use of the device may create the per-device slot
+        torch.cuda.synchronize()
+        free0 = torch.cuda.mem_get_info()[0]
+        out = engine.kmvm_ws(X, Y, b, prm, ws)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free0           # nothing taken from or given back to the driver
+        assert rel_l2(out.cpu(), ref.cpu()) <= 2e-6
+        peak = engine.last_workspace_peak()
+        assert 0 < peak <= need
+        print(f"n={n} d={d} R={R}: workspace estimate {need / 1e6:.1f} MB, peak used {peak / 1e6:.1f} MB")
+        small = torch.empty(max(4096, peak // 3), dtype=torch.uint8, device=cuda)
+        with pytest.raises(_lib.F3MError) as e:
+            engine.kmvm_ws(X, Y, b, prm, small)
+        assert e.value.status == 7 and "workspace" in str(e.value)
+        again = engine.kmvm_ws(X, Y, b, prm, ws)                # the failed call left nothing behind
+        assert rel_l2(again.cpu(), ref.cpu()) <= 2e-6

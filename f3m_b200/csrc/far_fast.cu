@@ -810,6 +810,19 @@ __device__ __forceinline__ void leaf3_rows(const float *__restrict__ pts, int n,
     }
 }
 
+// the same from coordinates already in registers (the loads of a chunk are issued while the previous chunk is consumed)
+template <int PP>
+__device__ __forceinline__ void leaf3_rows_xyz(const float (&x)[3], const float (&c)[3], float factor, const NodeTab2 &nt,
+                                               float scale2, float *row) {
+    float L[PP];
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+        lagrange_pp<PP>(factor * (x[k] - c[k]), nt, L);
+#pragma unroll
+        for (int q = 0; q < PP; q++) row[8 * k + q] = (k == 2) ? scale2 * L[q] : L[q];
+    }
+}
+
 template <int PP>
 __global__ void __launch_bounds__(128) p2m_leaf3(const float *__restrict__ pts, int n, const float *__restrict__ bs, int R, int r0,
                                                 const int *__restrict__ off, const float *__restrict__ ctr, float factor,
@@ -836,11 +849,22 @@ __global__ void __launch_bounds__(128) p2m_leaf3(const float *__restrict__ pts, 
     for (int i = 0; i < PP; i++)
 #pragma unroll
         for (int j = 0; j < PP; j++) acc[i][j] = 0.f;
+    // the point of the next chunk is fetched while the streams consume the current one
+    float px[3] = {0.f, 0.f, 0.f}, pb = 0.f;
+    auto fetch = [&](int base) {
+        const int i = base + (int)threadIdx.x;
+        if (i < s1) {
+            px[0] = pts[i]; px[1] = pts[(size_t)n + i]; px[2] = pts[(size_t)2 * n + i];
+            pb = bs[(size_t)i * R + r0];
+        }
+    };
+    fetch(s0);
     for (int base = s0; base < s1; base += G::TP) {
         const int cnt = min(G::TP, s1 - base);
         __syncthreads();
         if ((int)threadIdx.x < cnt)   // the column value rides on the L2 row
-            leaf3_rows<PP>(pts, n, base + threadIdx.x, c, factor, nt, bs[(size_t)(base + threadIdx.x) * R + r0], rows + threadIdx.x * L3_RS);
+            leaf3_rows_xyz<PP>(px, c, factor, nt, pb, rows + threadIdx.x * L3_RS);
+        fetch(base + G::TP);
         __syncthreads();
         if (active)
             for (int j = stream; j < cnt; j += G::NSTREAM) {
@@ -902,10 +926,17 @@ __global__ void __launch_bounds__(128) l2p_leaf3(const float *__restrict__ pts, 
     for (int i1 = 0; i1 < PP; i1++)
 #pragma unroll
         for (int i0 = 0; i0 < PP; i0++) lc[i1][i0] = active ? __ldg(loc + (size_t)box * P + i0 + PP * i1 + PP * PP * m2) : 0.f;
+    float px[3] = {0.f, 0.f, 0.f};
+    auto fetch = [&](int base) {
+        const int i = base + (int)threadIdx.x;
+        if (i < s1) { px[0] = pts[i]; px[1] = pts[(size_t)n + i]; px[2] = pts[(size_t)2 * n + i]; }
+    };
+    fetch(s0);
     for (int base = s0; base < s1; base += G::TP) {
         const int cnt = min(G::TP, s1 - base);
         __syncthreads();
-        if ((int)threadIdx.x < cnt) leaf3_rows<PP>(pts, n, base + threadIdx.x, c, factor, nt, 1.f, rows + threadIdx.x * L3_RS);
+        if ((int)threadIdx.x < cnt) leaf3_rows_xyz<PP>(px, c, factor, nt, 1.f, rows + threadIdx.x * L3_RS);
+        fetch(base + G::TP);   // the next chunk's point, while the streams consume this one
         __syncthreads();
         if (active)
             for (int j = stream; j < cnt; j += G::NSTREAM) {

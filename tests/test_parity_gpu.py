@@ -395,6 +395,23 @@ def test_engine_vs_reference_live(n, m, ls, P, var_comp, cuda):
     torch.cuda.synchronize()
     prm = engine.make_params(ls, 1000.0, P, var_comp, 0.3, P)
     out = engine.kmvm(X, None if m is None else Y, b, prm)
+    # box offsets and the three pair lists of every level, bit for bit, at a size the fixtures do not reach
+    trace = ref.field_trace(X, Y, "cuda:0", float(ls), 1000.0, int(P), bool(var_comp), 0.3, int(P))
+    torch.cuda.synchronize()
+    plan = engine.Plan(X, None if m is None else Y, prm)
+    assert plan.stats()["levels"] == len(trace)
+    from f3m_b200 import _lib
+
+    def canon(t):
+        p_ = t.cpu().numpy().astype(np.int64).reshape(-1, 2)
+        return p_[np.lexsort((p_[:, 1], p_[:, 0]))]
+
+    for l, t in enumerate(trace, start=1):
+        for cls, ref_pairs in zip(("far", "small", "keep"), t[:3]):
+            assert np.array_equal(plan.pairs(l, cls), canon(ref_pairs)), f"{cls} list differs from the reference at level {l}"
+        assert np.array_equal(plan.array(l, 0, _lib.ARR_BOX_OFFSETS), t[5].cpu().numpy().astype(np.int32)), f"target box offsets, level {l}"
+        assert np.array_equal(plan.array(l, 1, _lib.ARR_BOX_OFFSETS), t[10].cpu().numpy().astype(np.int32)), f"source box offsets, level {l}"
+    plan.close()
     err = rel_l2(out.cpu(), out_ref.cpu())
     rows = torch.arange(2000, device=cuda)
     exact = engine.rbf_dense(X[rows].double(), Y.double(), b.double(), ls).cpu()

@@ -294,11 +294,15 @@ __global__ void __launch_bounds__(128, 5) m2l_fast(int nbx, int d, const int *__
 // One warp per target box: packed offsets of its far pairs (axis 0 most significant) and the row in
 // ascending order of them.  The source boxes of one row have distinct cells, hence distinct keys below
 // 16^3: the rank of a key is the number of set bits below it in a bitmap of the row.
-constexpr int ORD_WORDS = 128;   // 4096 keys
+// In four and five dimensions the rank key is the base-8 number of the offsets counted from the lowest one
+// that can occur (tabulated offset 4): 8^4 and 8^5 keys.  An offset outside that window is clamped; if two
+// pairs of a row then share a rank key the row keeps its list order (every order is correct, see above).
+template <int WPL>   // bitmap words per lane: 4 -> 4096 rank keys, 32 -> 32768
 __global__ void __launch_bounds__(128) far_order_kernel(int nbx, int d, const int *__restrict__ fptr, const int *__restrict__ fidx,
                                                        const int *__restrict__ cell_x, const int *__restrict__ cell_y,
                                                        Geom2 geo, uint32_t *okey, int *oidx, int *err,
                                                        const int *__restrict__ off_x, int row_begin, int row_end) {
+    constexpr int ORD_WORDS = 32 * WPL;
     __shared__ uint32_t bits[4][ORD_WORDS];
     __shared__ int below[4][ORD_WORDS];
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -307,43 +311,50 @@ __global__ void __launch_bounds__(128) far_order_kernel(int nbx, int d, const in
     if (off_x[bx + 1] <= row_begin || off_x[bx] >= row_end) return;   // no row of this box in the slice being computed
     const int e0 = fptr[bx], n = fptr[bx + 1] - e0;
     if (n == 0) return;
-    auto key_of = [&](int by) {
+    const bool compact = d > 3;
+    // key: one nibble per axis, last axis lowest, axis 0 on top; rkey: what the row is ordered by
+    auto key_of = [&](int by, uint32_t &rkey) {
         uint32_t key = 0;
+        rkey = 0;
         for (int k = 0; k < d; k++) {
             int o = cell_y[by * d + k] - cell_x[bx * d + k] - geo.dqmin[k];
             if (o < 0 || o >= NOFF2) { atomicExch(err, 2); o = 0; }
-            key |= (uint32_t)o << (4 * (d - 1 - k));   // last axis lowest, axis 0 on top
+            key |= (uint32_t)o << (4 * (d - 1 - k));
+            rkey = rkey * 8u + (uint32_t)min(max(o - 4, 0), 7);
         }
+        if (!compact) rkey = key;
         return key;
     };
     for (int q = lane; q < ORD_WORDS; q += 32) bits[w][q] = 0u;
     __syncwarp();
     for (int i = lane; i < n; i += 32) {
-        const uint32_t key = key_of(fidx[e0 + i]);
-        atomicOr(&bits[w][key >> 5], 1u << (key & 31u));
+        uint32_t rkey;
+        key_of(fidx[e0 + i], rkey);
+        atomicOr(&bits[w][rkey >> 5], 1u << (rkey & 31u));
     }
     __syncwarp();
-    // exclusive prefix of the word populations: 4 words per lane, then a warp scan
-    int c[4], tot = 0;
-#pragma unroll
-    for (int q = 0; q < 4; q++) { c[q] = __popc(bits[w][lane * 4 + q]); tot += c[q]; }
+    // exclusive prefix of the word populations: WPL words per lane, then a warp scan
+    int tot = 0;
+#pragma unroll 4
+    for (int q = 0; q < WPL; q++) tot += __popc(bits[w][lane * WPL + q]);
     int incl = tot;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) { int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
     int run = incl - tot;
-#pragma unroll
-    for (int q = 0; q < 4; q++) { below[w][lane * 4 + q] = run; run += c[q]; }
+#pragma unroll 4
+    for (int q = 0; q < WPL; q++) { below[w][lane * WPL + q] = run; run += __popc(bits[w][lane * WPL + q]); }
     const int distinct = __shfl_sync(0xffffffffu, incl, 31);
     __syncwarp();
-    if (distinct != n) {   // cannot happen for boxes of one level; keep the list order rather than lose pairs
-        if (lane == 0) atomicExch(err, 2);
-        for (int i = lane; i < n; i += 32) { int by = fidx[e0 + i]; okey[e0 + i] = key_of(by); oidx[e0 + i] = by; }
+    if (distinct != n) {   // cannot happen for d <= 3 (boxes of one level have distinct cells); keep the list order
+        if (lane == 0 && !compact) atomicExch(err, 2);
+        for (int i = lane; i < n; i += 32) { int by = fidx[e0 + i]; uint32_t rk; okey[e0 + i] = key_of(by, rk); oidx[e0 + i] = by; }
         return;
     }
     for (int i = lane; i < n; i += 32) {
         const int by = fidx[e0 + i];
-        const uint32_t key = key_of(by);
-        const int rank = below[w][key >> 5] + __popc(bits[w][key >> 5] & ((1u << (key & 31u)) - 1u));
+        uint32_t rkey;
+        const uint32_t key = key_of(by, rkey);
+        const int rank = below[w][rkey >> 5] + __popc(bits[w][rkey >> 5] & ((1u << (rkey & 31u)) - 1u));
         okey[e0 + rank] = key;
         oidx[e0 + rank] = by;
     }
@@ -552,6 +563,223 @@ __global__ void __launch_bounds__(128, PP <= 6 ? 4 : 2) m2l_nested(int nbx, cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// M2L, nested form for several columns and for d = 4, 5: one CTA per target box, every thread owns FPT
+// fibres of each axis and keeps the partial sums of ALL nesting levels in registers.  A far pair costs one
+// coalesced read of the source box's moments and the last-axis transform, with no shared-memory traffic;
+// shared memory is only used to re-lay the sums out for the next axis when a group of offsets closes.
+// ---------------------------------------------------------------------------------------------
+template <int PP, int DD, int RBB>
+struct RowCfg {
+    static constexpr int MS = mat_stride(PP);
+    static constexpr int P = cpow(PP, DD), PR = P * RBB, NF = PR / PP;
+    static constexpr int MAX_ACC = 64;   // accumulator registers of a thread over all levels
+    static constexpr int pick_threads() {
+        int best = 0;
+        long best_u = -1;
+        for (int nt = 32; nt <= 256; nt += 32) {
+            const int fpt = (NF + nt - 1) / nt;
+            if (DD * fpt * PP > MAX_ACC) continue;
+            const long u = (long)NF * 1000000 / ((long)fpt * nt);   // share of fibre slots that hold a fibre
+            if (u >= best_u) { best_u = u; best = nt; }
+        }
+        return best;
+    }
+    static constexpr int NT = pick_threads();
+    static constexpr int FPT = NT ? (NF + NT - 1) / NT : 1;
+    static constexpr int DEPTH = FPT * PP * 4 <= 40 ? 4 : 2;   // source boxes in flight per CTA (divides 32)
+    static constexpr size_t smem = ((size_t)DD * NOFF2 * MS + (size_t)PR) * sizeof(float);
+    static constexpr bool ok = NT > 0 && smem <= 160 * 1024;
+    template <int K>
+    static __device__ __forceinline__ int base(int f) {
+        constexpr int st = RBB * cpow(PP, K);
+        const int hi = f / st;
+        return hi * st * PP + (f - hi * st);
+    }
+};
+
+template <int PP>
+__device__ __forceinline__ void load_matrix(const float *Mk, float (&M)[mat_stride(PP)]) {
+    const float4 *M4 = reinterpret_cast<const float4 *>(Mk);
+#pragma unroll
+    for (int q = 0; q < mat_stride(PP) / 4; q++) {
+        float4 v = M4[q];
+        M[4 * q] = v.x; M[4 * q + 1] = v.y; M[4 * q + 2] = v.z; M[4 * q + 3] = v.w;
+    }
+}
+
+// Closes nesting level K: the sums over the last offsets (axes K..DD-1 already applied) go through shared memory
+// into the layout of axis K-1, that axis' matrix for the group's offset is applied, and the result is added to
+// level K-1; level K-1 closes too when the offsets above it change.
+template <int PP, int DD, int RBB, int K>
+__device__ __forceinline__ void rows_close(float (&acc)[DD][RowCfg<PP, DD, RBB>::FPT][PP], float *buf, const float *Tsm,
+                                           uint32_t prev, uint32_t key, bool final, int tid) {
+    using C = RowCfg<PP, DD, RBB>;
+    if constexpr (K >= 1) {
+        constexpr int stK = RBB * cpow(PP, K), stL = RBB * cpow(PP, K - 1);
+#pragma unroll
+        for (int r = 0; r < C::FPT; r++) {
+            const int f = tid + r * C::NT;
+            if (f < C::NF) {
+                const int base = C::template base<K>(f);
+#pragma unroll
+                for (int i = 0; i < PP; i++) { buf[base + i * stK] = acc[K][r][i]; acc[K][r][i] = 0.f; }
+            }
+        }
+        __syncthreads();
+        float M[C::MS];
+        load_matrix<PP>(Tsm + ((K - 1) * NOFF2 + ((prev >> (4 * (DD - K))) & 15u)) * C::MS, M);
+#pragma unroll
+        for (int r = 0; r < C::FPT; r++) {
+            const int f = tid + r * C::NT;
+            if (f < C::NF) {
+                const int base = C::template base<K - 1>(f);
+                float v[PP];
+#pragma unroll
+                for (int j = 0; j < PP; j++) v[j] = buf[base + j * stL];
+#pragma unroll
+                for (int i = 0; i < PP; i++) {
+                    float o = 0.f;
+#pragma unroll
+                    for (int j = 0; j < PP; j++) o = fmaf(M[i * PP + j], v[j], o);
+                    acc[K - 1][r][i] += o;
+                }
+            }
+        }
+        __syncthreads();
+        if constexpr (K >= 2) {
+            constexpr int sh = 4 * (DD - K + 1);   // nibbles of the axes K-1..DD-1
+            if (final || (key >> sh) != (prev >> sh)) rows_close<PP, DD, RBB, K - 1>(acc, buf, Tsm, prev, key, final, tid);
+        }
+    }
+}
+
+template <int PP, int DD, int RBB>
+__global__ void __launch_bounds__(RowCfg<PP, DD, RBB>::NT ? RowCfg<PP, DD, RBB>::NT : 32)
+m2l_rows(int nbx, const int *__restrict__ fptr, const uint32_t *__restrict__ okey, const int *__restrict__ oidx,
+         const int *__restrict__ off_x, int row_begin, int row_end, const float *__restrict__ T,
+         const float *__restrict__ mom, float *loc) {
+    using C = RowCfg<PP, DD, RBB>;
+    constexpr int MS = C::MS, PR = C::PR, NF = C::NF, NT = C::NT ? C::NT : 32, FPT = C::FPT;
+    constexpr int KA = DD - 1;   // axis applied per pair: its fibres are strided by NF, fibre f starts at element f
+    extern __shared__ __align__(16) float sm[];
+    const int bx = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+    const int e0 = fptr[bx], e1 = fptr[bx + 1];
+    if (e0 == e1) return;
+    if (off_x[bx + 1] <= row_begin || off_x[bx] >= row_end) return;
+    constexpr int ntab = DD * NOFF2 * MS;
+    float *Tsm = sm, *buf = sm + ntab;
+    for (int q = tid; q < ntab; q += NT) Tsm[q] = T[q];
+    float acc[DD][FPT][PP];
+#pragma unroll
+    for (int k = 0; k < DD; k++)
+#pragma unroll
+        for (int r = 0; r < FPT; r++)
+#pragma unroll
+            for (int i = 0; i < PP; i++) acc[k][r][i] = 0.f;
+    __syncthreads();
+    auto fetch = [&](int by, float (&v)[FPT][PP]) {
+        const float *src = mom + (size_t)by * PR;
+#pragma unroll
+        for (int r = 0; r < FPT; r++) {
+            const int f = tid + r * NT;
+#pragma unroll
+            for (int j = 0; j < PP; j++) v[r][j] = f < NF ? __ldg(src + f + j * NF) : 0.f;
+        }
+    };
+    // DEPTH source boxes are on their way while one is consumed; the row's keys and boxes are read 32 at a time, one
+    // per lane, the next 32 a chunk ahead (entries past the end of the row repeat its last pair and are never consumed)
+    constexpr int DEPTH = C::DEPTH;
+    float pre[DEPTH][FPT][PP];
+    uint32_t prev = 0xffffffffu;
+    int nxtidx = oidx[min(e0 + lane, e1 - 1)];
+    uint32_t nxtkey = okey[min(e0 + lane, e1 - 1)];
+#pragma unroll
+    for (int u = 0; u < DEPTH; u++) fetch(__shfl_sync(0xffffffffu, nxtidx, u), pre[u]);
+    for (int c = e0; c < e1; c += 32) {
+        const int cn = min(32, e1 - c);
+        const uint32_t mykey = nxtkey;
+        const int myidx = nxtidx;
+        nxtidx = oidx[min(c + 32 + lane, e1 - 1)];
+        nxtkey = okey[min(c + 32 + lane, e1 - 1)];
+        for (int t0 = 0; t0 < cn; t0 += DEPTH) {
+#pragma unroll
+            for (int u = 0; u < DEPTH; u++) {
+                const int t = t0 + u;
+                if (t < cn) {
+                    const uint32_t key = __shfl_sync(0xffffffffu, mykey, t);
+                    if (prev != 0xffffffffu && (key >> 4) != (prev >> 4))
+                        rows_close<PP, DD, RBB, KA>(acc, buf, Tsm, prev, key, false, tid);
+                    float M[MS];
+                    load_matrix<PP>(Tsm + (KA * NOFF2 + (key & 15u)) * MS, M);
+#pragma unroll
+                    for (int r = 0; r < FPT; r++)
+#pragma unroll
+                        for (int i = 0; i < PP; i++) {
+                            float o = 0.f;
+#pragma unroll
+                            for (int j = 0; j < PP; j++) o = fmaf(M[i * PP + j], pre[u][r][j], o);
+                            acc[KA][r][i] += o;
+                        }
+                    prev = key;
+                    const int ahead = t + DEPTH;
+                    const int a0 = __shfl_sync(0xffffffffu, myidx, ahead & 31), a1 = __shfl_sync(0xffffffffu, nxtidx, ahead & 31);
+                    fetch(ahead < 32 ? a0 : a1, pre[u]);
+                }
+            }
+        }
+    }
+    rows_close<PP, DD, RBB, KA>(acc, buf, Tsm, prev, prev, true, tid);
+    // level 0 holds the box's local expansion in the layout of axis 0
+    float *dst = loc + (size_t)bx * PR;
+#pragma unroll
+    for (int r = 0; r < FPT; r++) {
+        const int f = tid + r * NT;
+        if (f < NF) {
+            const int base = C::template base<0>(f);
+#pragma unroll
+            for (int i = 0; i < PP; i++) dst[base + i * RBB] = acc[0][r][i];
+        }
+    }
+}
+
+// Host side of m2l_rows: the kernel exists for the (nodes, dimension, columns) whose accumulators fit the registers.
+template <int PP, int DD, int RBB>
+static bool m2l_rows_launch_one(bool probe, int nbx, const int *fptr, const uint32_t *okey, const int *oidx, const int *offx, int rb,
+                                int re, const float *T, const float *mom, float *loc, cudaStream_t s) {
+    using C = RowCfg<PP, DD, RBB>;
+    if constexpr (C::ok) {
+        if (probe) return true;
+        F3M_CUDA(cudaFuncSetAttribute(m2l_rows<PP, DD, RBB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::smem));
+        m2l_rows<PP, DD, RBB><<<nbx, C::NT, C::smem, s>>>(nbx, fptr, okey, oidx, offx, rb, re, T, mom, loc);
+        return true;
+    } else
+        return false;
+}
+
+template <int PP, int RBB>
+static bool m2l_rows_dispatch(bool probe, int d, int nbx, const int *fptr, const uint32_t *okey, const int *oidx, const int *offx,
+                              int rb, int re, const float *T, const float *mom, float *loc, cudaStream_t s) {
+    switch (d) {
+    case 2: return m2l_rows_launch_one<PP, 2, RBB>(probe, nbx, fptr, okey, oidx, offx, rb, re, T, mom, loc, s);
+    case 3: return m2l_rows_launch_one<PP, 3, RBB>(probe, nbx, fptr, okey, oidx, offx, rb, re, T, mom, loc, s);
+    case 4: return m2l_rows_launch_one<PP, 4, RBB>(probe, nbx, fptr, okey, oidx, offx, rb, re, T, mom, loc, s);
+    case 5: return m2l_rows_launch_one<PP, 5, RBB>(probe, nbx, fptr, okey, oidx, offx, rb, re, T, mom, loc, s);
+    default: return false;
+    }
+}
+
+template <int PP, int RBB>
+static bool rows_form_available(int d) {
+    return m2l_rows_dispatch<PP, RBB>(true, d, 0, nullptr, nullptr, nullptr, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr);
+}
+
+template <int PP, int RBB>
+static void launch_m2l_rows(int d, int nbx, const int *fptr, const uint32_t *okey, const int *oidx, const int *offx, int rb, int re,
+                            const float *T, const float *mom, float *loc, cudaStream_t s) {
+    m2l_rows_dispatch<PP, RBB>(false, d, nbx, fptr, okey, oidx, offx, rb, re, T, mom, loc, s);
+}
+
 // M2M: one CTA per parent box, warps share the children
 template <int PP>
 __global__ void __launch_bounds__(128) m2m_fast(int nbp, int d, const int *__restrict__ child_start,
@@ -663,7 +891,10 @@ __global__ void __launch_bounds__(256) p2m_leaf(const float *__restrict__ pts, i
     const int s0 = a + (int)(((long long)len * blockIdx.y) / nsplit), s1 = a + (int)(((long long)len * (blockIdx.y + 1)) / nsplit);
     if (s0 >= s1) return;
     const int PR = P * RB, C = P / PP;
-    for (int q = threadIdx.x; q < PR; q += NTH) accsm[q] = 0.f;
+    // the PP x RB block of one combination starts an odd number of floats after the previous one: the lanes of a
+    // warp (consecutive combinations) then add to different banks
+    constexpr int CS = (PP * RB) | 1;
+    for (int q = threadIdx.x; q < C * CS; q += NTH) accsm[q] = 0.f;
     float c[MAXD];
     for (int k = 0; k < d; k++) c[k] = ctr[box * d + k];
     const int G = C >= NTH ? 1 : NTH / C;             // point groups
@@ -715,14 +946,15 @@ __global__ void __launch_bounds__(256) p2m_leaf(const float *__restrict__ pts, i
 #pragma unroll
                 for (int i = 0; i < PP; i++)
 #pragma unroll
-                    for (int r = 0; r < RB; r++) atomicAdd(&accsm[(cc * PP + i) * RB + r], acc[i][r]);
+                    for (int r = 0; r < RB; r++) atomicAdd(&accsm[cc * CS + i * RB + r], acc[i][r]);
             }
         }
     }
     __syncthreads();
     float *dst = mom + (size_t)box * PR;
-    if (nsplit == 1) for (int q = threadIdx.x; q < PR; q += NTH) dst[q] = accsm[q];
-    else for (int q = threadIdx.x; q < PR; q += NTH) atomicAdd(dst + q, accsm[q]);
+    constexpr int BLK = PP * RB;
+    if (nsplit == 1) for (int q = threadIdx.x; q < PR; q += NTH) dst[q] = accsm[q + (q / BLK) * (CS - BLK)];
+    else for (int q = threadIdx.x; q < PR; q += NTH) atomicAdd(dst + q, accsm[q + (q / BLK) * (CS - BLK)]);
 }
 
 template <int PP, int RB>
@@ -1094,7 +1326,7 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
         else
             F3M_CUDA(cudaMemsetAsync(pl->moments_out, 0, (size_t)ly.nb * PR * sizeof(float), s));
         int nsplit = std::max(1, std::min(64, (ly.max_count + 8191) / 8192));
-        size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
+        size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR + (size_t)(P / PP)) * sizeof(float);
         F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         pl->last.begin(ST_P2M, s);
         if (RB == 1 && d == 3) {
@@ -1147,7 +1379,7 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
         if (!pl->ext_mom) {
             int nsplit = std::max(1, std::min(64, (ly.max_count + 8191) / 8192));
             if (nsplit > 1) mom[L].zero();
-            size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR) * sizeof(float);
+            size_t smem = ((size_t)d * PP * 129 + (size_t)128 * RB + (size_t)PR + (size_t)(P / PP)) * sizeof(float);
             F3M_CUDA(cudaFuncSetAttribute(p2m_leaf<PP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             if (RB == 1 && d == 3) {
                 const int wy = pl->same ? 0 : 1;
@@ -1221,16 +1453,25 @@ static void far_fast_block(f3m_plan *pl, const float *bs, int R, int r0, float *
                 cy = celly.p;
             }
             const bool nested = RB == 1 && (d == 2 || d == 3) && cfg.nf <= 64;
-            if (nested) {
+            const bool rows = !nested && rows_form_available<PP, RB>(d);
+            if (nested || rows) {
                 if (!ll.far_ordered) {
                     ll.far_okey.alloc((size_t)ll.far.count, s);
                     ll.far_oidx.alloc((size_t)ll.far.count, s);
-                    far_order_kernel<<<(lx.nb + 3) / 4, 128, 0, s>>>(lx.nb, d, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, geo,
-                                                                    ll.far_okey.p, ll.far_oidx.p, pl->d_flags, lx.off.p, rb, re);
+                    if (d <= 4)
+                        far_order_kernel<4><<<(lx.nb + 3) / 4, 128, 0, s>>>(lx.nb, d, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, geo,
+                                                                           ll.far_okey.p, ll.far_oidx.p, pl->d_flags, lx.off.p, rb, re);
+                    else
+                        far_order_kernel<32><<<(lx.nb + 3) / 4, 128, 0, s>>>(lx.nb, d, ll.far.ptr.p, ll.far.idx.p, cellx.p, cy, geo,
+                                                                            ll.far_okey.p, ll.far_oidx.p, pl->d_flags, lx.off.p, rb, re);
                     F3M_LAUNCH_CHECK();
                     // kept for later products of this plan only when every box was ordered
                     ll.far_ordered = rb <= 0 && re >= n_x;
                 }
+            }
+            if (rows) {
+                launch_m2l_rows<PP, RB>(d, lx.nb, ll.far.ptr.p, ll.far_okey.p, ll.far_oidx.p, lx.off.p, rb, re, T.p, momp[l], loc[l].p, s);
+            } else if (nested) {
                 const size_t smem_n = tab + (size_t)4 * P * sizeof(float);   // tables + one buffer per warp
                 if (d == 3) {
                     F3M_CUDA(cudaFuncSetAttribute(m2l_nested<PP, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_n));

@@ -269,7 +269,9 @@ __global__ void __launch_bounds__(256) pack_pairs_box(const float *__restrict__ 
     }
 }
 
-constexpr int SP2 = 192;   // source pairs per shared-memory tile
+// source pairs per shared-memory tile: 6 KB for one column, 12 KB for eight (so that shared memory does not limit the
+// CTAs per SM below what the registers allow)
+template <int RB> __host__ __device__ constexpr int sp2_of() { return RB >= 4 ? 96 : 192; }
 
 // POLY = 0: every exponential on the MUFU pipe.  POLY = 2 or 3: PNUM of every PDEN source pairs use the
 // polynomial of that degree instead (the host enables it only when the exponent is provably small).
@@ -282,9 +284,15 @@ __device__ __forceinline__ void near_tile_x2(const float *__restrict__ xpts, int
     constexpr int W = row_width(D, RB);
     float x[TI][D], tot[TI][RB];
     int ti[TI];
+    // one target per thread and at most 16 targets: the warp splits into G lane groups that hold the same targets and
+    // take every G-th source pair (their sums are added by shuffles at the end), so that no lane idles
+    const int nt = t1 - t0;
+    const int lg = (TI == 1) ? (nt > 16 ? 5 : (nt > 8 ? 4 : (nt > 4 ? 3 : 2))) : 5;
+    const int G = (TI == 1) ? 32 >> lg : 1, grp = (TI == 1) ? (int)threadIdx.x >> lg : 0;
+    const int tlane = (TI == 1) ? (int)threadIdx.x & ((1 << lg) - 1) : (int)threadIdx.x;
 #pragma unroll
     for (int u = 0; u < TI; u++) {
-        ti[u] = t0 + threadIdx.x + u * NT2;
+        ti[u] = t0 + tlane + u * NT2;
         int ii = ti[u] < t1 ? ti[u] : t0;
 #pragma unroll
         for (int k = 0; k < D; k++) x[u][k] = xpts[(size_t)k * n_x + ii];
@@ -313,6 +321,7 @@ __device__ __forceinline__ void near_tile_x2(const float *__restrict__ xpts, int
 #pragma unroll
             for (int r = 0; r < RB; r++) acc[u][r] = pack2(0.f, 0.f);
         }
+        constexpr int SP2 = sp2_of<RB>();
         for (int base = 0; base < npairs; base += SP2) {
             const int np = min(SP2, npairs - base);
             __syncthreads();
@@ -320,8 +329,9 @@ __device__ __forceinline__ void near_tile_x2(const float *__restrict__ xpts, int
             float4 *sdst = reinterpret_cast<float4 *>(smem);
             for (int q = threadIdx.x; q < np * (2 * W / 4); q += NT2) sdst[q] = __ldg(g + q);
             __syncthreads();
-            auto body = [&](int j, bool poly) {
+            auto body = [&](int jl, bool poly) {   // jl: the lane group's jl-th pair of the tile
                 f32x2 col[W];
+                const int j = (TI == 1) ? jl * G + grp : jl;
                 const ulonglong2 *src = reinterpret_cast<const ulonglong2 *>(smem + j * 2 * W);
 #pragma unroll
                 for (int q = 0; q < W / 2; q++) {
@@ -347,17 +357,18 @@ __device__ __forceinline__ void near_tile_x2(const float *__restrict__ xpts, int
                 }
             };
             int j = 0;
+            const int npl = (TI == 1) ? (np - grp + G - 1) / G : np;   // pairs of this lane group
             if (POLY) {
 #pragma unroll 1
-                for (; j + PDEN <= np; j += PDEN) {
+                for (; j + PDEN <= npl; j += PDEN) {
 #pragma unroll
                     for (int q = 0; q < PDEN; q++) body(j + q, ((q + 1) * PNUM) / PDEN != (q * PNUM) / PDEN);
                 }
             } else {
 #pragma unroll 4
-                for (; j + 1 <= np; j++) body(j, false);
+                for (; j + 1 <= npl; j++) body(j, false);
             }
-            for (; j < np; j++) body(j, false);
+            for (; j < npl; j++) body(j, false);
         }
 #pragma unroll
         for (int u = 0; u < TI; u++)
@@ -368,17 +379,174 @@ __device__ __forceinline__ void near_tile_x2(const float *__restrict__ xpts, int
                 tot[u][r] = fmaf(fx[u], lo + hi, tot[u][r]);
             }
     }
+    if (TI == 1) {
+        for (int o = 1 << lg; o < 32; o <<= 1)
+#pragma unroll
+            for (int r = 0; r < RB; r++) tot[0][r] += __shfl_xor_sync(0xffffffffu, tot[0][r], o);
+    }
 #pragma unroll
     for (int u = 0; u < TI; u++)
-        if (ti[u] < t1) {
+        if (ti[u] < t1 && grp == 0) {
 #pragma unroll
             for (int r = 0; r < RB; r++)
                 if (r0 + r < R) out[(size_t)ti[u] * R + r0 + r] += tot[u][r];
         }
 }
 
-// TI = targets per thread.  MIXED: a tile of at most 32 targets (small boxes) runs the one-target form, which does half
-// the work; the host picks this variant only when such tiles exist.
+
+// 16-byte asynchronous copy global -> shared (completion tracked per thread in commit groups)
+__device__ __forceinline__ void cp_async16(float *smem_dst, const float *gsrc) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// A tile of at most 32 targets (small boxes: clustered data, four and five dimensions), one warp.  Two things differ
+// from near_tile_x2.  (1) With TS <= 16 targets (TS a power of two) the warp splits into 32 / TS lane groups that hold
+// the same targets and take every (32 / TS)-th source pair; the groups' sums are added by shuffles at the end, so no
+// lane idles.  (2) Source boxes of a dozen points give a handful of pair iterations each, too few to hide the chain
+// list entry -> box offsets -> packed rows behind: the shared-memory tile is two half tiles, the rows of the next chunk
+// arrive by asynchronous copies while the current one is consumed, and the offsets and centres of the two boxes after
+// it are already in registers.
+template <int D, int RB, int POLY, int PNUM, int PDEN>
+__device__ __forceinline__ void near_tile_x2_small(const float *__restrict__ xpts, int n_x, const int *__restrict__ ptr,
+                                                   const int *__restrict__ idx, const int *__restrict__ off_y,
+                                                   const float *__restrict__ ctr_y, const float *__restrict__ packed,
+                                                   float scale, int R, int r0, float *out, float pc0, float pc1, float pc2,
+                                                   float pc3, float *smem, int box, int t0, int t1) {
+    constexpr int W = row_width(D, RB);
+    constexpr int SPH = sp2_of<RB>() / 2;   // source pairs per half tile
+    constexpr int V4 = 2 * W / 4;           // 16-byte pieces of a pair block
+    const int lane = threadIdx.x;
+    const int nt = t1 - t0;
+    const int lg = nt > 16 ? 5 : (nt > 8 ? 4 : (nt > 4 ? 3 : 2));
+    const int TS = 1 << lg, G = 32 >> lg;
+    const int g = lane >> lg;
+    const int ti = t0 + (lane & (TS - 1));
+    float x[D], tot[RB];
+    {
+        const int ii = ti < t1 ? ti : t0;
+#pragma unroll
+        for (int k = 0; k < D; k++) x[k] = xpts[(size_t)k * n_x + ii];
+#pragma unroll
+        for (int r = 0; r < RB; r++) tot[r] = 0.f;
+    }
+    const f32x2 c1 = pack2(pc1, pc1), c2 = pack2(pc2, pc2), c3 = pack2(pc3, pc3), one = pack2(pc0, pc0);
+    const int e0 = ptr[box], e1 = ptr[box + 1];
+    if (e0 == e1) return;
+    struct Src {
+        int npairs;
+        const float *rows;
+        float ctr[D];
+    };
+    auto load_src = [&](int by, Src &sb) {
+        const int s0 = off_y[by];
+        sb.npairs = (off_y[by + 1] - s0 + 1) >> 1;
+        sb.rows = packed + (size_t)pair_row_start(s0, by) * W;
+#pragma unroll
+        for (int k = 0; k < D; k++) sb.ctr[k] = __ldg(ctr_y + by * D + k);
+    };
+    auto issue_copy = [&](float *dst, const Src &sb, int base) {
+        const int pieces = min(SPH, sb.npairs - base) * V4;
+        const float *src = sb.rows + (size_t)base * 2 * W;
+        for (int q = lane; q < pieces; q += NT2) cp_async16(dst + 4 * q, src + 4 * q);
+    };
+    Src cur, n1, n2;
+    load_src(idx[e0], cur);
+    n1 = cur; n2 = cur;
+    if (e0 + 1 < e1) load_src(idx[e0 + 1], n1);
+    if (e0 + 2 < e1) load_src(idx[e0 + 2], n2);
+    int by3 = e0 + 3 < e1 ? idx[e0 + 3] : 0;
+    issue_copy(smem, cur, 0);
+    cp_async_commit();
+    int e = e0, base = 0, pb = 0;
+    f32x2 xr[D], acc[RB];
+    float fx = 0.f;
+    while (true) {
+        const bool more_in_box = base + SPH < cur.npairs;
+        const bool have_next = more_in_box || e + 1 < e1;
+        float *bufc = smem + pb * (SPH * 2 * W), *bufn = smem + (pb ^ 1) * (SPH * 2 * W);
+        if (have_next) {
+            if (more_in_box) issue_copy(bufn, cur, base + SPH);
+            else issue_copy(bufn, n1, 0);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();   // everything but the group just committed has landed
+        __syncthreads();
+        if (base == 0) {
+            float nx = 0.f;
+#pragma unroll
+            for (int k = 0; k < D; k++) {
+                const float v = scale * (x[k] - cur.ctr[k]);
+                nx = fmaf(-v, v, nx);
+                xr[k] = pack2(v, v);
+            }
+            fx = ex2_approx(nx);
+#pragma unroll
+            for (int r = 0; r < RB; r++) acc[r] = pack2(0.f, 0.f);
+        }
+        const int np = min(SPH, cur.npairs - base);
+        int q = 0;
+#pragma unroll 2
+        for (int j = g; j < np; j += G) {
+            f32x2 col[W];
+            const ulonglong2 *src = reinterpret_cast<const ulonglong2 *>(bufc + j * 2 * W);
+#pragma unroll
+            for (int c = 0; c < W / 2; c++) {
+                const ulonglong2 v = src[c];
+                col[2 * c] = v.x;
+                col[2 * c + 1] = v.y;
+            }
+            f32x2 t = mul2(xr[0], col[0]);
+#pragma unroll
+            for (int k = 1; k < D; k++) t = fma2(xr[k], col[k], t);
+            f32x2 ev;
+            if (POLY && ((q + 1) * PNUM) / PDEN != (q * PNUM) / PDEN) {
+                ev = (POLY == 2) ? fma2(fma2(c2, t, c1), t, one) : fma2(fma2(fma2(c3, t, c2), t, c1), t, one);
+            } else {
+                float ta, tb;
+                unpack2(t, ta, tb);
+                ev = pack2(ex2_approx(ta), ex2_approx(tb));
+            }
+#pragma unroll
+            for (int r = 0; r < RB; r++) acc[r] = fma2(ev, col[D + r], acc[r]);
+            if (POLY && ++q == PDEN) q = 0;
+        }
+        if (!more_in_box) {
+#pragma unroll
+            for (int r = 0; r < RB; r++) {
+                float lo, hi;
+                unpack2(acc[r], lo, hi);
+                tot[r] = fmaf(fx, lo + hi, tot[r]);
+            }
+        }
+        __syncthreads();   // the copy issued in the next round overwrites the half tile read here
+        if (more_in_box) base += SPH;
+        else {
+            if (++e >= e1) break;
+            base = 0;
+            cur = n1;
+            n1 = n2;
+            if (e + 2 < e1) load_src(by3, n2);
+            by3 = e + 3 < e1 ? idx[e + 3] : 0;
+        }
+        pb ^= 1;
+    }
+    cp_async_wait<0>();
+    for (int o = TS; o < 32; o <<= 1)
+#pragma unroll
+        for (int r = 0; r < RB; r++) tot[r] += __shfl_xor_sync(0xffffffffu, tot[r], o);
+    if (g == 0 && ti < t1) {
+#pragma unroll
+        for (int r = 0; r < RB; r++)
+            if (r0 + r < R) out[(size_t)ti * R + r0 + r] += tot[r];
+    }
+}
+
+// TI = targets per thread.  MIXED: a tile of at most 32 targets runs a one-target form, which does half the work (the
+// pipelined one for small boxes); the host picks this variant only when such tiles exist.
 template <int D, int RB, int POLY, int PNUM, int PDEN, bool MIXED>
 __global__ void __launch_bounds__(NT2, RB == 1 ? 32 : (RB <= 4 ? 20 : 12)) near_kernel_x2(const float *__restrict__ xpts, int n_x, const int *__restrict__ off_x,
                                                      int nbx, const int *__restrict__ tile_off,
@@ -388,13 +556,19 @@ __global__ void __launch_bounds__(NT2, RB == 1 ? 32 : (RB <= 4 ? 20 : 12)) near_
                                                      float *out, float pc0, float pc1, float pc2, float pc3, int row_begin,
                                                      int row_end) {
     constexpr int W = row_width(D, RB);
-    __shared__ __align__(16) float smem[SP2 * 2 * W];
+    __shared__ __align__(16) float smem[sp2_of<RB>() * 2 * W];
     int box, t0, t1;
     item_to_tile(blockIdx.x, tile_off, nbx, off_x, row_begin, row_end, box, t0, t1);
-    if (MIXED && t1 - t0 <= NT2)
-        near_tile_x2<D, RB, POLY, PNUM, PDEN, 1>(xpts, n_x, ptr, idx, off_y, ctr_y, packed, scale, R, r0, out, pc0, pc1, pc2, pc3, smem,
-                                                 box, t0, t1);
-    else
+    if (MIXED && t1 - t0 <= NT2) {
+        // a box of at most 32 points has neighbours of its own kind (same level, same local density): short source boxes,
+        // where the pipelined form pays; the last tile of a large box meets large source boxes and keeps the plain loop
+        if (RB >= 4 && off_x[box + 1] - off_x[box] <= NT2)   // one column: measured slower than the plain loop on clustered data
+            near_tile_x2_small<D, RB, POLY, PNUM, PDEN>(xpts, n_x, ptr, idx, off_y, ctr_y, packed, scale, R, r0, out, pc0, pc1, pc2,
+                                                        pc3, smem, box, t0, t1);
+        else
+            near_tile_x2<D, RB, POLY, PNUM, PDEN, 1>(xpts, n_x, ptr, idx, off_y, ctr_y, packed, scale, R, r0, out, pc0, pc1, pc2, pc3,
+                                                     smem, box, t0, t1);
+    } else
         near_tile_x2<D, RB, POLY, PNUM, PDEN, TI2>(xpts, n_x, ptr, idx, off_y, ctr_y, packed, scale, R, r0, out, pc0, pc1, pc2, pc3, smem,
                                                    box, t0, t1);
 }

@@ -86,7 +86,7 @@ __device__ __forceinline__ void tile_accumulate(const float *__restrict__ smem, 
 // (rows outside [row_begin, row_end) belong to another slice of the targets and are not touched)
 __device__ __forceinline__ void item_to_tile(int item, const int *__restrict__ tile_off, int nbx,
                                              const int *__restrict__ off_x, int row_begin, int row_end, int &box, int &t0,
-                                             int &t1) {
+                                             int &t1, int full_tile = 0) {
     int lo = 0, hi = nbx;   // largest b with tile_off[b] <= item
     while (hi - lo > 1) {
         int mid = (lo + hi) >> 1;
@@ -95,7 +95,14 @@ __device__ __forceinline__ void item_to_tile(int item, const int *__restrict__ t
     box = lo;
     const int tile = item - tile_off[box], ntiles = tile_off[box + 1] - tile_off[box];
     const int a = max(off_x[box], row_begin), nb = min(off_x[box + 1], row_end) - a;
-    t0 = a + (int)(((long long)nb * tile) / ntiles);          // tiles of one box are equally full
+    // full_tile > 0 (a kernel whose tiles of at most full_tile / 2 rows cost half): when the rows left over by full tiles
+    // are at most half a tile, the box is cut into full tiles and that short one; otherwise its tiles are equally full
+    if (full_tile > 0 && nb - (ntiles - 1) * full_tile <= full_tile / 2) {
+        t0 = a + tile * full_tile;
+        t1 = min(t0 + full_tile, a + nb);
+        return;
+    }
+    t0 = a + (int)(((long long)nb * tile) / ntiles);
     t1 = a + (int)(((long long)nb * (tile + 1)) / ntiles);
 }
 
@@ -558,7 +565,7 @@ __global__ void __launch_bounds__(NT2, RB == 1 ? 32 : (RB <= 4 ? 20 : 12)) near_
     constexpr int W = row_width(D, RB);
     __shared__ __align__(16) float smem[sp2_of<RB>() * 2 * W];
     int box, t0, t1;
-    item_to_tile(blockIdx.x, tile_off, nbx, off_x, row_begin, row_end, box, t0, t1);
+    item_to_tile(blockIdx.x, tile_off, nbx, off_x, row_begin, row_end, box, t0, t1, MIXED ? NT2 * TI2 : 0);
     if (MIXED && t1 - t0 <= NT2) {
         // a box of at most 32 points has neighbours of its own kind (same level, same local density): short source boxes,
         // where the pipelined form pays; the last tile of a large box meets large source boxes and keeps the plain loop
@@ -576,7 +583,7 @@ __global__ void __launch_bounds__(NT2, RB == 1 ? 32 : (RB <= 4 ? 20 : 12)) near_
 #include "near_mma.cuh"
 
 // tiles[b] = tiles of the rows of target box b inside [row_begin, row_end) (0 when the box has no pairs or no row
-// there); *n_small counts the boxes whose single tile holds at most 32 targets
+// there); *n_small counts the boxes whose last tile holds at most 32 targets
 __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__restrict__ off_x, const int *__restrict__ ptr,
                                                          int row_begin, int row_end, int tile_pts, int *tiles, int *n_small) {
     int b = blockIdx.x * blockDim.x + threadIdx.x;
@@ -586,7 +593,7 @@ __global__ void __launch_bounds__(256) near_tiles_per_box(int nbx, const int *__
         const int len = min(off_x[b + 1], row_end) - max(off_x[b], row_begin);
         if (len > 0) {
             t = (len + tile_pts - 1) / tile_pts;
-            if (n_small && len <= 32) atomicAdd(n_small, 1);
+            if (n_small && (len - 1) % tile_pts < 32) atomicAdd(n_small, 1);   // its last tile holds at most 32 targets
         }
     }
     tiles[b] = t;

@@ -96,8 +96,8 @@ const char *f3m_last_error(void);
 int f3m_kmvm_f32(const float *X, int64_t N, const float *Y, int64_t M, const float *b, int32_t R,
                  int32_t d, const f3m_params *prm, float *out, void *stream);
 
-/* The same product with every temporary taken from memory the CALLER owns (SURVEY of the reference's interface:
- * FFM_XY allocates through torch, n_tree.cu:1061 and throughout; a host that hands out memory from its own
+/* The same product with every temporary taken from memory the CALLER owns (the reference's FFM_XY allocates
+ * through torch, n_tree.cu:1061 and throughout; a host that hands out memory from its own
  * allocator passes a slice of it here).  workspace: device memory of workspace_bytes bytes, free for the duration
  * of the call; nothing is requested from or returned to the driver inside the call, apart from a per-device slot of
  * 1 KB of flags and pinned read-back words that the library creates the first time a device is used.
